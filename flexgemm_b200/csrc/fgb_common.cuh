@@ -1,0 +1,38 @@
+// Shared host/device helpers of the flexgemm_b200 library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/flexgemm_b200.h"
+
+namespace fgb {
+
+constexpr uint32_t kInvalid = 0xFFFFFFFFu;
+constexpr int kMapBlock = 256;  // voxels per CTA in the map / compaction kernels
+
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? FGB_OK : FGB_E_CUDA_BASE + static_cast<int>(e); }
+
+// Launch-error check that does not synchronise.
+inline int launch_status() { return cuda_status(cudaPeekAtLastError()); }
+
+__device__ __forceinline__ void report(int32_t* status, int32_t code) {
+  if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+inline int elem_bytes(int dtype) {
+  switch (dtype) {
+    case FGB_F16:
+    case FGB_BF16:
+      return 2;
+    case FGB_F32_TF32:
+    case FGB_F32_IEEE:
+      return 4;
+    default:
+      return 0;
+  }
+}
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+}  // namespace fgb

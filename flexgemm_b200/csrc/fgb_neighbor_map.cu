@@ -1,0 +1,298 @@
+// GPU hash table over (b,x,y,z) voxel coordinates and the submanifold-conv
+// neighbour map built from it.
+//
+// Table layout (private to this file; it never leaves the library):
+//   32-bit keys: one 64-bit word per slot, (key << 32) | row, empty = ~0.
+//                One CAS inserts key and value together and one 8-byte load
+//                answers a probe.
+//   64-bit keys: uint64 keys[slots] followed by uint32 rows[slots].
+// Open addressing with linear probing; the slot is the Murmur3 finaliser of
+// the key mapped to [0, slots) by a multiply-high.
+//
+// The lookup kernel flattens (voxel, offset) pairs in the order the map is
+// stored, so consecutive threads write consecutive map words and no staging or
+// pre-fill of the map is needed.  While the row is in flight the kernel also
+// derives everything the later passes need from it: the per-voxel validity
+// mask (gray code), its Gray-to-binary decode, and per-(offset, block) valid
+// counts that a small scan turns into the offsets of the wgrad pair lists.
+#include "fgb_common.cuh"
+
+namespace fgb {
+
+__device__ __forceinline__ uint32_t fmix32(uint32_t k) {
+  k ^= k >> 16;
+  k *= 0x85ebca6bu;
+  k ^= k >> 13;
+  k *= 0xc2b2ae35u;
+  k ^= k >> 16;
+  return k;
+}
+__device__ __forceinline__ uint32_t fmix64_hi(uint64_t k) {
+  k ^= k >> 33;
+  k *= 0xff51afd7ed558ccdULL;
+  k ^= k >> 33;
+  k *= 0xc4ceb9fe1a85ec53ULL;
+  k ^= k >> 33;
+  return static_cast<uint32_t>(k >> 32) ^ static_cast<uint32_t>(k);
+}
+
+template <int kKeyBits>
+struct Table;
+
+template <>
+struct Table<32> {
+  unsigned long long* slots_;
+  uint32_t n_;
+  __device__ __forceinline__ uint32_t home(uint64_t key) const { return __umulhi(fmix32(static_cast<uint32_t>(key)), n_); }
+  // returns false when every slot was visited without finding room
+  __device__ __forceinline__ bool insert(uint64_t key, uint32_t row) const {
+    const unsigned long long word = (static_cast<unsigned long long>(static_cast<uint32_t>(key)) << 32) | row;
+    uint32_t s = home(key);
+    for (uint32_t i = 0; i < n_; ++i) {
+      unsigned long long prev = atomicCAS(&slots_[s], ~0ULL, word);
+      if (prev == ~0ULL || static_cast<uint32_t>(prev >> 32) == static_cast<uint32_t>(key)) return true;
+      if (++s >= n_) s = 0;
+    }
+    return false;
+  }
+  __device__ __forceinline__ uint32_t find(uint64_t key) const {
+    uint32_t s = home(key);
+    for (uint32_t i = 0; i < n_; ++i) {
+      unsigned long long w = __ldg(&slots_[s]);
+      if (w == ~0ULL) return kInvalid;
+      if (static_cast<uint32_t>(w >> 32) == static_cast<uint32_t>(key)) return static_cast<uint32_t>(w);
+      if (++s >= n_) s = 0;
+    }
+    return kInvalid;
+  }
+};
+
+template <>
+struct Table<64> {
+  unsigned long long* keys_;
+  uint32_t* rows_;
+  uint32_t n_;
+  __device__ __forceinline__ uint32_t home(uint64_t key) const { return __umulhi(fmix64_hi(key), n_); }
+  __device__ __forceinline__ bool insert(uint64_t key, uint32_t row) const {
+    uint32_t s = home(key);
+    for (uint32_t i = 0; i < n_; ++i) {
+      unsigned long long prev = atomicCAS(&keys_[s], ~0ULL, static_cast<unsigned long long>(key));
+      if (prev == ~0ULL) {
+        rows_[s] = row;
+        return true;
+      }
+      if (prev == key) return true;
+      if (++s >= n_) s = 0;
+    }
+    return false;
+  }
+  __device__ __forceinline__ uint32_t find(uint64_t key) const {
+    uint32_t s = home(key);
+    for (uint32_t i = 0; i < n_; ++i) {
+      unsigned long long k = __ldg(&keys_[s]);
+      if (k == ~0ULL) return kInvalid;
+      if (k == key) return __ldg(&rows_[s]);
+      if (++s >= n_) s = 0;
+    }
+    return kInvalid;
+  }
+};
+
+template <int kKeyBits>
+__device__ __forceinline__ Table<kKeyBits> make_table(void* mem, uint32_t slots);
+template <>
+__device__ __forceinline__ Table<32> make_table<32>(void* mem, uint32_t slots) {
+  return Table<32>{static_cast<unsigned long long*>(mem), slots};
+}
+template <>
+__device__ __forceinline__ Table<64> make_table<64>(void* mem, uint32_t slots) {
+  auto* keys = static_cast<unsigned long long*>(mem);
+  return Table<64>{keys, reinterpret_cast<uint32_t*>(keys + slots), slots};
+}
+
+struct Grid3 {
+  int W, H, D;
+  __device__ __forceinline__ uint64_t key(int b, int x, int y, int z) const {
+    return ((static_cast<uint64_t>(b) * W + x) * H + y) * static_cast<uint64_t>(D) + z;
+  }
+};
+
+// one thread per voxel, 16-byte coordinate loads
+template <int kKeyBits>
+__global__ void __launch_bounds__(kMapBlock) hash_insert_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g,
+                                                                void* table_mem, uint32_t slots, int32_t* status) {
+  const uint32_t i = blockIdx.x * kMapBlock + threadIdx.x;
+  if (i >= n) return;
+  const int4 c = __ldg(&coords[i]);
+  const auto table = make_table<kKeyBits>(table_mem, slots);
+  if (!table.insert(g.key(c.x, c.y, c.z, c.w), i)) report(status, FGB_S_TABLE_FULL);
+}
+
+struct Stencil {
+  int Kw, Kh, Kd, Dw, Dh, Dd, V;
+};
+
+// One CTA per 256 voxels; thread t handles the flattened (voxel, offset) items
+// t, t+256, ... of the CTA, i.e. exactly the words t, t+256, ... of the CTA's
+// slice of the map.
+template <int kKeyBits>
+__global__ void __launch_bounds__(kMapBlock)
+    subm_lookup_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, Stencil st, void* table_mem, uint32_t slots,
+                       uint32_t* __restrict__ nbr, int32_t* __restrict__ gray_out, int32_t* __restrict__ binary_out,
+                       uint32_t* __restrict__ block_counts, uint32_t nblk) {
+  __shared__ int4 s_coord[kMapBlock];
+  __shared__ uint32_t s_gray[kMapBlock];
+  __shared__ uint32_t s_count[32];
+  const uint32_t n0 = blockIdx.x * kMapBlock;
+  const uint32_t nv = min(static_cast<uint32_t>(kMapBlock), n - n0);
+  const int t = threadIdx.x;
+  if (t < nv) s_coord[t] = __ldg(&coords[n0 + t]);
+  s_gray[t] = 0;
+  if (t < 32) s_count[t] = 0;
+  __syncthreads();
+
+  const auto table = make_table<kKeyBits>(table_mem, slots);
+  const int V = st.V;
+  const int KhKd = st.Kh * st.Kd;
+  const int centre = V >> 1;  // all kernel extents are odd
+  const uint32_t items = nv * V;
+  uint32_t* out = nbr + static_cast<size_t>(n0) * V;
+  for (uint32_t item = t; item < items; item += kMapBlock) {
+    const uint32_t lv = item / V;
+    const int v = item - lv * V;
+    uint32_t val;
+    if (v == centre) {
+      val = n0 + lv;
+    } else {
+      const int4 c = s_coord[lv];
+      const int kx = v / KhKd, ky = (v / st.Kd) % st.Kh, kz = v % st.Kd;
+      const int x = c.y + (kx - st.Kw / 2) * st.Dw;
+      const int y = c.z + (ky - st.Kh / 2) * st.Dh;
+      const int z = c.w + (kz - st.Kd / 2) * st.Dd;
+      val = kInvalid;
+      if (x >= 0 && x < g.W && y >= 0 && y < g.H && z >= 0 && z < g.D) val = table.find(g.key(c.x, x, y, z));
+    }
+    out[item] = val;
+    if (val != kInvalid) {
+      atomicOr(&s_gray[lv], 1u << v);
+      atomicAdd(&s_count[v], 1u);
+    }
+  }
+  __syncthreads();
+  if (t < nv) {
+    const uint32_t gray = s_gray[t];
+    uint32_t binary = gray;  // Gray -> binary: prefix xor from the top bit down
+    binary ^= binary >> 1;
+    binary ^= binary >> 2;
+    binary ^= binary >> 4;
+    binary ^= binary >> 8;
+    binary ^= binary >> 16;
+    gray_out[n0 + t] = static_cast<int32_t>(gray);
+    binary_out[n0 + t] = static_cast<int32_t>(binary);
+  }
+  if (t < V) block_counts[static_cast<size_t>(t) * nblk + blockIdx.x] = s_count[t];
+}
+
+// CTA v turns block_counts[v, :] into exclusive offsets in place and leaves the
+// total of offset v in seg[v + 1].
+__global__ void __launch_bounds__(1024) block_scan_kernel(uint32_t* __restrict__ block_counts, uint32_t nblk, uint32_t* __restrict__ seg) {
+  __shared__ uint32_t s_warp[32];
+  __shared__ uint32_t s_carry;
+  uint32_t* row = block_counts + static_cast<size_t>(blockIdx.x) * nblk;
+  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+  if (t == 0) s_carry = 0;
+  __syncthreads();
+  for (uint32_t base = 0; base < nblk; base += 1024) {
+    const uint32_t i = base + t;
+    const uint32_t x = i < nblk ? row[i] : 0u;
+    uint32_t inc = x;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      uint32_t y = __shfl_up_sync(0xffffffffu, inc, d);
+      if (lane >= d) inc += y;
+    }
+    if (lane == 31) s_warp[w] = inc;
+    __syncthreads();
+    if (w == 0) {
+      uint32_t ws = s_warp[lane];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        uint32_t y = __shfl_up_sync(0xffffffffu, ws, d);
+        if (lane >= d) ws += y;
+      }
+      s_warp[lane] = ws;  // inclusive over warps
+    }
+    __syncthreads();
+    const uint32_t carry = s_carry;
+    const uint32_t warp_excl = w == 0 ? 0u : s_warp[w - 1];
+    if (i < nblk) row[i] = carry + warp_excl + inc - x;
+    __syncthreads();
+    if (t == 1023) s_carry = carry + s_warp[31];
+    __syncthreads();
+  }
+  if (t == 0) seg[blockIdx.x + 1] = s_carry;
+}
+
+__global__ void seg_prefix_kernel(uint32_t* seg, int V) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    uint32_t acc = 0;
+    seg[0] = 0;
+    for (int v = 1; v <= V; ++v) {
+      acc += seg[v];
+      seg[v] = acc;
+    }
+  }
+}
+
+template <int kKeyBits>
+static int build_impl(const int32_t* coords, uint32_t n, Grid3 g, Stencil st, void* table, uint32_t slots, uint32_t* nbr,
+                      int32_t* gray, int32_t* binary, uint32_t* block_counts, uint32_t* seg, int32_t* status, cudaStream_t s) {
+  const uint32_t nblk = static_cast<uint32_t>(ceil_div(n, kMapBlock));
+  hash_insert_kernel<kKeyBits><<<nblk, kMapBlock, 0, s>>>(reinterpret_cast<const int4*>(coords), n, g, table, slots, status);
+  subm_lookup_kernel<kKeyBits><<<nblk, kMapBlock, 0, s>>>(reinterpret_cast<const int4*>(coords), n, g, st, table, slots, nbr, gray,
+                                                         binary, block_counts, nblk);
+  block_scan_kernel<<<st.V, 1024, 0, s>>>(block_counts, nblk, seg);
+  seg_prefix_kernel<<<1, 32, 0, s>>>(seg, st.V);
+  return launch_status();
+}
+
+}  // namespace fgb
+
+extern "C" int64_t fgb_hash_table_bytes(int64_t slots, int key_bits) {
+  if (slots < 0 || slots >= (int64_t(1) << 31)) return FGB_E_SIZE;
+  if (key_bits == 32) return slots * 8;
+  if (key_bits == 64) return slots * 12;
+  return FGB_E_DTYPE;
+}
+
+extern "C" int64_t fgb_map_num_blocks(int64_t n) { return n < 0 ? FGB_E_SIZE : fgb::ceil_div(n, fgb::kMapBlock); }
+
+extern "C" int fgb_subm_build_neighbor_map(const int32_t* coords, int64_t n, int W, int H, int D, int Kw, int Kh, int Kd, int Dw,
+                                           int Dh, int Dd, void* table, int64_t slots, int key_bits, uint32_t* neighbor_map,
+                                           int32_t* gray_code, int32_t* binary_code, uint32_t* block_counts,
+                                           uint32_t* valid_signal_seg, int32_t* status, void* stream) {
+  using namespace fgb;
+  if (n < 0 || n >= (int64_t(1) << 32) - 1) return FGB_E_SIZE;
+  if (W <= 0 || H <= 0 || D <= 0) return FGB_E_SIZE;
+  if (Kw <= 0 || Kh <= 0 || Kd <= 0 || !(Kw & 1) || !(Kh & 1) || !(Kd & 1)) return FGB_E_SIZE;
+  if (Dw <= 0 || Dh <= 0 || Dd <= 0) return FGB_E_SIZE;
+  const int64_t V = int64_t(Kw) * Kh * Kd;
+  if (V > 32) return FGB_E_SIZE;
+  if (key_bits != 32 && key_bits != 64) return FGB_E_DTYPE;
+  if (slots < n || slots >= (int64_t(1) << 31)) return FGB_E_SIZE;
+  if (valid_signal_seg == nullptr) return FGB_E_NULL;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n == 0) return cuda_status(cudaMemsetAsync(valid_signal_seg, 0, (V + 1) * sizeof(uint32_t), s));
+  if (!coords || !table || !neighbor_map || !gray_code || !binary_code || !block_counts) return FGB_E_NULL;
+  if (reinterpret_cast<uintptr_t>(coords) & 15) return FGB_E_ALIGN;
+  if (reinterpret_cast<uintptr_t>(table) & 7) return FGB_E_ALIGN;
+  int rc = cuda_status(cudaMemsetAsync(table, 0xFF, static_cast<size_t>(fgb_hash_table_bytes(slots, key_bits)), s));
+  if (rc != FGB_OK) return rc;
+  const Grid3 g{W, H, D};
+  const Stencil st{Kw, Kh, Kd, Dw, Dh, Dd, static_cast<int>(V)};
+  if (key_bits == 32)
+    return build_impl<32>(coords, static_cast<uint32_t>(n), g, st, table, static_cast<uint32_t>(slots), neighbor_map, gray_code,
+                          binary_code, block_counts, valid_signal_seg, status, s);
+  return build_impl<64>(coords, static_cast<uint32_t>(n), g, st, table, static_cast<uint32_t>(slots), neighbor_map, gray_code,
+                        binary_code, block_counts, valid_signal_seg, status, s);
+}

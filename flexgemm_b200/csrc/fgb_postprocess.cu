@@ -1,0 +1,216 @@
+// Post-processing of the neighbour map for the masked implicit GEMM:
+// sorted row order, wgrad pair lists, per-tile offset masks and their list form.
+#include <cub/device/device_radix_sort.cuh>
+
+#include "fgb_common.cuh"
+
+namespace fgb {
+
+// ------------------------------------------------------------------ sorted_idx
+__global__ void iota_i64_kernel(int64_t* out, int64_t n) {
+  const int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+  if (i < n) out[i] = i;
+}
+
+struct SortPlan {
+  size_t keys_out_off, vals_in_off, temp_off, temp_bytes, total;
+};
+
+static int sort_plan(int64_t n, SortPlan* p) {
+  auto align = [](size_t x) { return (x + 255) & ~size_t(255); };
+  p->keys_out_off = 0;
+  p->vals_in_off = align(size_t(n) * sizeof(int32_t));
+  p->temp_off = p->vals_in_off + align(size_t(n) * sizeof(int64_t));
+  p->temp_bytes = 0;
+  cudaError_t e = cub::DeviceRadixSort::SortPairs(nullptr, p->temp_bytes, static_cast<const int32_t*>(nullptr),
+                                                  static_cast<int32_t*>(nullptr), static_cast<const int64_t*>(nullptr),
+                                                  static_cast<int64_t*>(nullptr), n, 0, 32, nullptr);
+  if (e != cudaSuccess) return cuda_status(e);
+  p->total = p->temp_off + align(p->temp_bytes);
+  return FGB_OK;
+}
+
+// ------------------------------------------------------------------ pair lists
+// One CTA per 256 voxels (the blocking of the lookup kernel, whose per-block
+// counts were scanned into block_offsets).  The CTA's slice of the map is
+// staged in shared memory with coalesced loads; rank inside the CTA comes from
+// warp ballots, so every offset's list keeps ascending row order.
+__global__ void __launch_bounds__(kMapBlock)
+    valid_signal_kernel(const uint32_t* __restrict__ nbr, const int32_t* __restrict__ gray, uint32_t n, int V,
+                        const uint32_t* __restrict__ block_offsets, uint32_t nblk, const uint32_t* __restrict__ seg,
+                        uint32_t* __restrict__ vs_i, uint32_t* __restrict__ vs_o) {
+  extern __shared__ uint32_t s_map[];     // [256 * V]
+  __shared__ uint32_t s_wcount[32][8];    // valid rows per (offset, warp), then exclusive prefix
+  __shared__ uint32_t s_base[32];         // list position of the CTA's first pair, per offset
+  const uint32_t n0 = blockIdx.x * kMapBlock;
+  const uint32_t nv = min(static_cast<uint32_t>(kMapBlock), n - n0);
+  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+  const uint32_t words = nv * V;
+  const uint32_t* src = nbr + static_cast<size_t>(n0) * V;
+  for (uint32_t i = t; i < words; i += kMapBlock) s_map[i] = __ldg(&src[i]);
+  const uint32_t g = t < nv ? static_cast<uint32_t>(__ldg(&gray[n0 + t])) : 0u;
+  if (t < V) s_base[t] = seg[t] + block_offsets[static_cast<size_t>(t) * nblk + blockIdx.x];
+  for (int v = 0; v < V; ++v) {
+    const uint32_t b = __ballot_sync(0xffffffffu, (g >> v) & 1u);
+    if (lane == 0) s_wcount[v][w] = __popc(b);
+  }
+  __syncthreads();
+  if (t < V) {
+    uint32_t acc = 0;
+    for (int i = 0; i < 8; ++i) {
+      uint32_t c = s_wcount[t][i];
+      s_wcount[t][i] = acc;
+      acc += c;
+    }
+  }
+  __syncthreads();
+  for (int v = 0; v < V; ++v) {
+    const bool ok = (g >> v) & 1u;
+    const uint32_t b = __ballot_sync(0xffffffffu, ok);
+    if (ok) {
+      const uint32_t pos = s_base[v] + s_wcount[v][w] + __popc(b & ((1u << lane) - 1u));
+      vs_o[pos] = n0 + t;
+      vs_i[pos] = s_map[t * V + v];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ tile masks
+// one warp per tile of `block` sorted rows
+__global__ void tile_mask_kernel(const int32_t* __restrict__ gray, const int64_t* __restrict__ sorted_idx, int64_t n, int block,
+                                 int64_t ntiles, uint32_t* __restrict__ masks) {
+  const int64_t tile = (blockIdx.x * int64_t(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (tile >= ntiles) return;
+  uint32_t m = 0;
+  const int64_t r0 = tile * block;
+  for (int i = lane; i < block; i += 32) {
+    const int64_t r = r0 + i;
+    if (r < n) m |= static_cast<uint32_t>(__ldg(&gray[__ldg(&sorted_idx[r])]));
+  }
+  m = __reduce_or_sync(0xffffffffu, m);
+  if (lane == 0) masks[tile] = m;
+}
+
+// single CTA: seg = exclusive scan of popcounts, then expand the set bits
+__global__ void __launch_bounds__(1024)
+    valid_kernel_kernel(const uint32_t* __restrict__ masks, uint32_t nblk, int32_t* __restrict__ vk, int32_t* __restrict__ seg) {
+  __shared__ uint32_t s_warp[32];
+  __shared__ uint32_t s_carry;
+  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+  if (t == 0) {
+    s_carry = 0;
+    seg[0] = 0;
+  }
+  __syncthreads();
+  for (uint32_t base = 0; base < nblk; base += 1024) {
+    const uint32_t i = base + t;
+    uint32_t m = i < nblk ? __ldg(&masks[i]) : 0u;
+    const uint32_t x = __popc(m);
+    uint32_t inc = x;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      uint32_t y = __shfl_up_sync(0xffffffffu, inc, d);
+      if (lane >= d) inc += y;
+    }
+    if (lane == 31) s_warp[w] = inc;
+    __syncthreads();
+    if (w == 0) {
+      uint32_t ws = s_warp[lane];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        uint32_t y = __shfl_up_sync(0xffffffffu, ws, d);
+        if (lane >= d) ws += y;
+      }
+      s_warp[lane] = ws;
+    }
+    __syncthreads();
+    const uint32_t carry = s_carry;
+    const uint32_t end = carry + (w == 0 ? 0u : s_warp[w - 1]) + inc;
+    if (i < nblk) {
+      seg[i + 1] = static_cast<int32_t>(end);
+      uint32_t pos = end - x;
+      while (m) {
+        const int bit = __ffs(m) - 1;
+        vk[pos++] = bit;
+        m &= m - 1;
+      }
+    }
+    __syncthreads();
+    if (t == 1023) s_carry = carry + s_warp[31];
+    __syncthreads();
+  }
+}
+
+}  // namespace fgb
+
+extern "C" int64_t fgb_pp_sorted_idx_workspace_bytes(int64_t n) {
+  if (n < 0 || n >= (int64_t(1) << 31)) return FGB_E_SIZE;
+  fgb::SortPlan p;
+  int rc = fgb::sort_plan(n, &p);
+  return rc == FGB_OK ? static_cast<int64_t>(p.total) : -int64_t(rc < 0 ? -rc : rc);
+}
+
+extern "C" int fgb_pp_sorted_idx(const int32_t* binary_code, int64_t n, int key_bits, int64_t* sorted_idx, void* workspace,
+                                 int64_t workspace_bytes, void* stream) {
+  using namespace fgb;
+  if (n < 0 || n >= (int64_t(1) << 31)) return FGB_E_SIZE;
+  if (key_bits < 1 || key_bits > 32) return FGB_E_SIZE;
+  if (n == 0) return FGB_OK;
+  if (!binary_code || !sorted_idx || !workspace) return FGB_E_NULL;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return FGB_E_ALIGN;
+  SortPlan p;
+  int rc = sort_plan(n, &p);
+  if (rc != FGB_OK) return rc;
+  if (workspace_bytes < static_cast<int64_t>(p.total)) return FGB_E_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char* ws = static_cast<char*>(workspace);
+  auto* keys_out = reinterpret_cast<int32_t*>(ws + p.keys_out_off);
+  auto* vals_in = reinterpret_cast<int64_t*>(ws + p.vals_in_off);
+  iota_i64_kernel<<<static_cast<unsigned>(ceil_div(n, 256)), 256, 0, s>>>(vals_in, n);
+  size_t temp = p.temp_bytes;
+  // Codes with fewer than 32 significant bits are non-negative, so sorting the
+  // low key_bits bits orders them as signed integers; with 32 bits the signed
+  // key type does.
+  cudaError_t e = cub::DeviceRadixSort::SortPairs(ws + p.temp_off, temp, binary_code, keys_out, vals_in, sorted_idx, n, 0,
+                                                  key_bits, s);
+  if (e != cudaSuccess) return cuda_status(e);
+  return launch_status();
+}
+
+extern "C" int fgb_pp_valid_signal(const uint32_t* neighbor_map, const int32_t* gray_code, int64_t n, int V,
+                                   const uint32_t* block_offsets, const uint32_t* valid_signal_seg, uint32_t* valid_signal_i,
+                                   uint32_t* valid_signal_o, void* stream) {
+  using namespace fgb;
+  if (n < 0 || n >= (int64_t(1) << 32) - 1 || V < 1 || V > 32) return FGB_E_SIZE;
+  if (n == 0) return FGB_OK;
+  if (!neighbor_map || !gray_code || !block_offsets || !valid_signal_seg || !valid_signal_i || !valid_signal_o) return FGB_E_NULL;
+  const uint32_t nblk = static_cast<uint32_t>(ceil_div(n, kMapBlock));
+  const size_t smem = size_t(kMapBlock) * V * sizeof(uint32_t);
+  valid_signal_kernel<<<nblk, kMapBlock, smem, static_cast<cudaStream_t>(stream)>>>(
+      neighbor_map, gray_code, static_cast<uint32_t>(n), V, block_offsets, nblk, valid_signal_seg, valid_signal_i, valid_signal_o);
+  return launch_status();
+}
+
+extern "C" int fgb_pp_tile_masks(const int32_t* gray_code, const int64_t* sorted_idx, int64_t n, int block, uint32_t* tile_masks,
+                                 void* stream) {
+  using namespace fgb;
+  if (n < 0 || block < 8 || block > 1024 || (block & (block - 1))) return FGB_E_SIZE;
+  if (n == 0) return FGB_OK;
+  if (!gray_code || !sorted_idx || !tile_masks) return FGB_E_NULL;
+  const int64_t ntiles = ceil_div(n, block);
+  tile_mask_kernel<<<static_cast<unsigned>(ceil_div(ntiles * 32, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      gray_code, sorted_idx, n, block, ntiles, tile_masks);
+  return launch_status();
+}
+
+extern "C" int fgb_pp_valid_kernel(const uint32_t* tile_masks, int64_t nblk, int32_t* valid_kernel, int32_t* valid_kernel_seg,
+                                   void* stream) {
+  using namespace fgb;
+  if (nblk < 0 || nblk > (int64_t(1) << 24)) return FGB_E_SIZE;
+  if (!valid_kernel_seg) return FGB_E_NULL;
+  if (nblk > 0 && (!tile_masks || !valid_kernel)) return FGB_E_NULL;
+  valid_kernel_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(tile_masks, static_cast<uint32_t>(nblk), valid_kernel,
+                                                                         valid_kernel_seg);
+  return launch_status();
+}

@@ -1,0 +1,252 @@
+"""Tensor-level wrappers over the C ABI (``include/flexgemm_b200.h``).
+
+These play the role of the reference's ``flex_gemm.kernels.cuda`` pybind
+module (flex_gemm/kernels/cuda/ext.cpp:10-36) and of its Triton wrappers for
+the submanifold path: they allocate outputs with torch, pass raw pointers and
+the current CUDA stream to the library, and never compute anything themselves.
+"""
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .. import _cabi
+from . import config
+
+_DTYPES = {torch.float16: _cabi.F16, torch.bfloat16: _cabi.BF16}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype in _DTYPES:
+        return _DTYPES[dtype]
+    if dtype == torch.float32:
+        return _cabi.F32_TF32 if config.allow_tf32 else _cabi.F32_IEEE
+    raise TypeError(f"unsupported feature dtype {dtype}: expected float16, bfloat16 or float32")
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise NotImplementedError(f"{name} must be a CUDA tensor: flexgemm_b200 has no CPU implementation")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+# --------------------------------------------------------------------------
+# per-(device, stream) scratch and the device status word
+# --------------------------------------------------------------------------
+_scratch: Dict[tuple, torch.Tensor] = {}
+_status: Dict[int, torch.Tensor] = {}
+
+
+def workspace(device: torch.device, tag: str, nbytes: int) -> torch.Tensor:
+    """A reusable 256-byte aligned scratch buffer of at least ``nbytes`` bytes.
+    Buffers are keyed by stream so that work on one stream never shares scratch
+    with work on another."""
+    key = (device.index, _stream(device), tag)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() * 8 < nbytes:
+        buf = torch.empty(max(int(nbytes) + 7, 256) // 8, dtype=torch.int64, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def release_workspaces() -> None:
+    _scratch.clear()
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[idx]
+
+
+def check_status(device: torch.device) -> None:
+    """Read (synchronising) and clear the device status word; raise if a kernel
+    recorded a soft error."""
+    word = status_word(device)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        what = {_cabi.S_TABLE_FULL: "hash table full (raise the hashmap ratio)",
+                _cabi.S_WAIT_TIMEOUT: "a bounded barrier wait ran out inside a kernel"}.get(code, f"code {code}")
+        raise RuntimeError(f"flexgemm_b200 device-side error: {what}")
+
+
+# --------------------------------------------------------------------------
+# neighbour map and post-processing
+# --------------------------------------------------------------------------
+def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table: torch.Tensor, key_bits: int,
+                            slots: int) -> Dict[str, torch.Tensor]:
+    """Hash build + lookup.  Returns neighbor_map [N,V] uint32, gray_code and
+    binary_code [N] int32, block_offsets [V*nblk] uint32, valid_signal_seg [V+1] uint32."""
+    _require_cuda(coords, "coords")
+    lib = _cabi.lib()
+    dev = coords.device
+    n = coords.shape[0]
+    _, _, W, H, D = [int(s) for s in shape]
+    V = int(ksize[0]) * int(ksize[1]) * int(ksize[2])
+    nblk = _cabi.check_size(lib.fgb_map_num_blocks(n), "fgb_map_num_blocks")
+    out = {
+        "neighbor_map": torch.empty((n, V), dtype=torch.uint32, device=dev),
+        "gray_code": torch.empty(n, dtype=torch.int32, device=dev),
+        "binary_code": torch.empty(n, dtype=torch.int32, device=dev),
+        "block_offsets": torch.empty(max(V * nblk, 1), dtype=torch.uint32, device=dev),
+        "valid_signal_seg": torch.empty(V + 1, dtype=torch.uint32, device=dev),
+    }
+    rc = lib.fgb_subm_build_neighbor_map(
+        _ptr(coords), n, W, H, D, int(ksize[0]), int(ksize[1]), int(ksize[2]),
+        int(dilation[0]), int(dilation[1]), int(dilation[2]),
+        table.data_ptr(), int(slots), int(key_bits),
+        _ptr(out["neighbor_map"]), _ptr(out["gray_code"]), _ptr(out["binary_code"]),
+        out["block_offsets"].data_ptr(), out["valid_signal_seg"].data_ptr(),
+        status_word(dev).data_ptr(), _stream(dev))
+    _cabi.check(rc, "fgb_subm_build_neighbor_map")
+    return out
+
+
+def sorted_idx_from_binary(binary_code: torch.Tensor, key_bits: int) -> torch.Tensor:
+    """int64 stable argsort of the binary code (radix sort over ``key_bits`` bits)."""
+    lib = _cabi.lib()
+    dev = binary_code.device
+    n = binary_code.shape[0]
+    out = torch.empty(n, dtype=torch.int64, device=dev)
+    if n == 0:
+        return out
+    nbytes = _cabi.check_size(lib.fgb_pp_sorted_idx_workspace_bytes(n), "fgb_pp_sorted_idx_workspace_bytes")
+    ws = workspace(dev, "sort", nbytes)
+    rc = lib.fgb_pp_sorted_idx(binary_code.data_ptr(), n, int(key_bits), out.data_ptr(), ws.data_ptr(), ws.numel() * 8, _stream(dev))
+    _cabi.check(rc, "fgb_pp_sorted_idx")
+    return out
+
+
+def valid_signal(neighbor_map: torch.Tensor, gray_code: torch.Tensor, block_offsets: torch.Tensor,
+                 valid_signal_seg: torch.Tensor, num_pairs: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(valid_signal_i, valid_signal_o), uint32 [num_pairs] each."""
+    lib = _cabi.lib()
+    dev = neighbor_map.device
+    n, V = neighbor_map.shape
+    vs_i = torch.empty(num_pairs, dtype=torch.uint32, device=dev)
+    vs_o = torch.empty(num_pairs, dtype=torch.uint32, device=dev)
+    rc = lib.fgb_pp_valid_signal(_ptr(neighbor_map), _ptr(gray_code), n, V, block_offsets.data_ptr(),
+                                 valid_signal_seg.data_ptr(), _ptr(vs_i), _ptr(vs_o), _stream(dev))
+    _cabi.check(rc, "fgb_pp_valid_signal")
+    return vs_i, vs_o
+
+
+def tile_masks(gray_code: torch.Tensor, sorted_idx: torch.Tensor, block: int) -> torch.Tensor:
+    lib = _cabi.lib()
+    dev = gray_code.device
+    n = gray_code.shape[0]
+    nblk = (n + block - 1) // block
+    out = torch.empty(nblk, dtype=torch.uint32, device=dev)
+    rc = lib.fgb_pp_tile_masks(_ptr(gray_code), _ptr(sorted_idx), n, int(block), _ptr(out), _stream(dev))
+    _cabi.check(rc, "fgb_pp_tile_masks")
+    return out
+
+
+def valid_kernel(masks: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """List form of the tile masks: (valid_kernel int32 [sum popcount],
+    valid_kernel_seg int32 [nblk+1]).  Synchronises once to size the list, as
+    the reference does (migemm_neighmap_pp.cu:356)."""
+    lib = _cabi.lib()
+    dev = masks.device
+    nblk = masks.shape[0]
+    seg = torch.empty(nblk + 1, dtype=torch.int32, device=dev)
+    vk = torch.empty(max(nblk * 32, 1), dtype=torch.int32, device=dev)
+    rc = lib.fgb_pp_valid_kernel(_ptr(masks), nblk, vk.data_ptr(), seg.data_ptr(), _stream(dev))
+    _cabi.check(rc, "fgb_pp_valid_kernel")
+    total = int(seg[-1].item())
+    return vk[:total].clone(), seg
+
+
+# --------------------------------------------------------------------------
+# conv kernels
+# --------------------------------------------------------------------------
+def conv_tile_rows() -> int:
+    return int(_cabi.lib().fgb_conv_tile_rows())
+
+
+def conv_fprop(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks) -> torch.Tensor:
+    """feats [N,Ci], weight_cvc [Co,V,Ci] -> out [N,Co]."""
+    lib = _cabi.lib()
+    dev = feats.device
+    n, Ci = feats.shape
+    Co, V, _ = weight_cvc.shape
+    code = dtype_code(feats.dtype)
+    out = torch.empty((n, Co), dtype=feats.dtype, device=dev)
+    nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(0, Ci, Co, V, code, 1), "fgb_conv_workspace_bytes")
+    ws = workspace(dev, "fprop", nbytes) if nbytes else None
+    rc = lib.fgb_subm_conv_fprop(_ptr(feats), weight_cvc.data_ptr(), _ptr(bias), _ptr(neighbor_map), _ptr(sorted_idx),
+                                 _ptr(masks), _ptr(out), n, Ci, Co, V, code, _ptr(ws), ws.numel() * 8 if ws is not None else 0,
+                                 status_word(dev).data_ptr(), _stream(dev))
+    _cabi.check(rc, "fgb_subm_conv_fprop")
+    return out
+
+
+def conv_dgrad(grad_out, weight_cvc, neighbor_map, sorted_idx, masks) -> torch.Tensor:
+    """grad_out [N,Co], weight_cvc [Co,V,Ci] -> grad_feats [N,Ci]."""
+    lib = _cabi.lib()
+    dev = grad_out.device
+    n, Co = grad_out.shape
+    _, V, Ci = weight_cvc.shape
+    code = dtype_code(grad_out.dtype)
+    out = torch.empty((n, Ci), dtype=grad_out.dtype, device=dev)
+    nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(1, Ci, Co, V, code, 1), "fgb_conv_workspace_bytes")
+    ws = workspace(dev, "dgrad", nbytes)
+    rc = lib.fgb_subm_conv_dgrad(_ptr(grad_out), weight_cvc.data_ptr(), _ptr(neighbor_map), _ptr(sorted_idx), _ptr(masks),
+                                 _ptr(out), n, Ci, Co, V, code, ws.data_ptr(), ws.numel() * 8,
+                                 status_word(dev).data_ptr(), _stream(dev))
+    _cabi.check(rc, "fgb_subm_conv_dgrad")
+    return out
+
+
+def conv_wgrad(grad_out, feats, vs_i, vs_o, vs_seg, splitk: Optional[int] = None, want_f32: bool = False,
+               want_dtype: bool = True):
+    """-> (grad_weight [Co,V,Ci] in the feature dtype or None, fp32 copy or None)."""
+    lib = _cabi.lib()
+    dev = feats.device
+    n, Ci = feats.shape
+    Co = grad_out.shape[1]
+    V = vs_seg.shape[0] - 1
+    code = dtype_code(feats.dtype)
+    if splitk is None:
+        splitk = lib.fgb_wgrad_default_splitk(int(vs_i.shape[0]), Ci, Co, V, code)
+        if splitk < 1:
+            _cabi.check(splitk, "fgb_wgrad_default_splitk")
+    gw = torch.empty((Co, V, Ci), dtype=feats.dtype, device=dev) if want_dtype else None
+    gw32 = torch.empty((Co, V, Ci), dtype=torch.float32, device=dev) if want_f32 else None
+    nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(2, Ci, Co, V, code, splitk), "fgb_conv_workspace_bytes")
+    ws = workspace(dev, "wgrad", nbytes)
+    rc = lib.fgb_subm_conv_wgrad(_ptr(grad_out), _ptr(feats), _ptr(vs_i), _ptr(vs_o), vs_seg.data_ptr(), _ptr(gw), _ptr(gw32),
+                                 n, Ci, Co, V, code, int(splitk), ws.data_ptr(), ws.numel() * 8,
+                                 status_word(dev).data_ptr(), _stream(dev))
+    _cabi.check(rc, "fgb_subm_conv_wgrad")
+    return gw, gw32
+
+
+def bias_grad(grad_out, want_f32: bool = False, want_dtype: bool = True):
+    lib = _cabi.lib()
+    dev = grad_out.device
+    n, Co = grad_out.shape
+    code = dtype_code(grad_out.dtype)
+    gb = torch.empty(Co, dtype=grad_out.dtype, device=dev) if want_dtype else None
+    gb32 = torch.empty(Co, dtype=torch.float32, device=dev) if want_f32 else None
+    nbytes = _cabi.check_size(lib.fgb_bias_grad_workspace_bytes(Co), "fgb_bias_grad_workspace_bytes")
+    ws = workspace(dev, "bias", nbytes)
+    rc = lib.fgb_subm_conv_bias_grad(_ptr(grad_out), _ptr(gb), _ptr(gb32), n, Co, code, ws.data_ptr(), ws.numel() * 8, _stream(dev))
+    _cabi.check(rc, "fgb_subm_conv_bias_grad")
+    return gb, gb32
+
+
+def cast_from_f32(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    out = torch.empty(src.shape, dtype=dtype, device=src.device)
+    code = _DTYPES.get(dtype, _cabi.F32_TF32)
+    rc = _cabi.lib().fgb_cast_from_f32(_ptr(src), _ptr(out), src.numel(), code, _stream(src.device))
+    _cabi.check(rc, "fgb_cast_from_f32")
+    return out

@@ -1,0 +1,209 @@
+/*
+ * flexgemm_b200 -- C ABI of the sm_100a submanifold-conv3d backend.
+ *
+ * Every function takes plain integers and device pointers and launches on the
+ * given CUDA stream (pass the cudaStream_t as a void*).  The library allocates
+ * nothing: outputs, tables and workspaces are owned by the caller (the entry
+ * points whose name ends in _bytes tell how much to provide).  Nothing
+ * synchronises the stream.
+ *
+ * Return value: 0 on success, a negative FGB_E_* code when the arguments are
+ * rejected before any launch, or 1000 + cudaError_t when a launch failed.
+ * Soft errors detected on the device (a hash probe or a barrier wait that ran
+ * out of iterations) do not trap: the kernel records a non-zero code in the
+ * caller's `status` word (int32 in device memory, zeroed by the caller) and
+ * finishes; read it at the next synchronisation point.
+ *
+ * The citations name the interface of FlexGEMM (paths inside its source tree)
+ * that each entry point stands in for.
+ */
+#ifndef FLEXGEMM_B200_H_
+#define FLEXGEMM_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FGB_OK 0
+#define FGB_E_NULL (-1)       /* a required pointer is null            */
+#define FGB_E_SIZE (-2)       /* a size or count is out of range       */
+#define FGB_E_DTYPE (-3)      /* unsupported dtype / key width         */
+#define FGB_E_ALIGN (-4)      /* pointer or channel count misaligned   */
+#define FGB_E_WORKSPACE (-5)  /* workspace too small                   */
+#define FGB_E_DRIVER (-6)     /* CUDA driver entry point unavailable   */
+#define FGB_E_CUDA_BASE 1000  /* 1000 + cudaError_t                    */
+
+/* device-side status codes (written to *status) */
+#define FGB_S_TABLE_FULL 1    /* hash insert found no free slot        */
+#define FGB_S_WAIT_TIMEOUT 2  /* a bounded barrier wait ran out        */
+
+/* element types of features / weights */
+#define FGB_F16 0
+#define FGB_BF16 1
+#define FGB_F32_TF32 2  /* fp32 storage, TF32 tensor-core math (allow_tf32 = True)  */
+#define FGB_F32_IEEE 3  /* fp32 storage, fp32-accurate math   (allow_tf32 = False) */
+
+const char* fgb_version(void);
+const char* fgb_error_string(int code);
+
+/* ------------------------------------------------------------------------
+ * Hash table + neighbour map
+ * --------------------------------------------------------------------- */
+
+/* Bytes of table storage for `slots` slots.  key_bits is 32 when
+ * B*W*H*D < 2^32 and 64 otherwise -- the same rule as init_hashmap
+ * (flex_gemm/ops/utils.py:4-19).  Returns a negative code on bad arguments. */
+int64_t fgb_hash_table_bytes(int64_t slots, int key_bits);
+
+/* Number of 256-voxel blocks the map kernels use for `n` voxels (sizes the
+ * block_offsets array below). */
+int64_t fgb_map_num_blocks(int64_t n);
+
+/* Builds the table from `coords` and fills the [n, V] neighbour map,
+ * V = Kw*Kh*Kd: neighbor_map[i, v] is the row of the voxel at
+ * coords[i] + (k - K/2) * dilation for v = (kx*Kh + ky)*Kd + kz, or
+ * 0xffffffff.  Also writes the per-voxel validity mask gray_code[i] (bit v set
+ * iff valid), its Gray-to-binary decode binary_code[i], block_offsets
+ * [V * nblk] (for offset v and 256-voxel block k, the number of valid pairs of
+ * offset v in the blocks before k) and valid_signal_seg[V + 1] (exclusive
+ * prefix of the per-offset totals; its last entry is the pair count L).
+ *
+ * Stands in for hashmap_build_submanifold_conv_neighbour_map
+ * (flex_gemm/kernels/cuda/spconv/subm_neighbor_map.cu:104-162, with
+ * hashmap_insert_3d_idx_as_val, kernels/cuda/hash/hash.cu:369-449) and for the
+ * gray/binary pass of neighbor_map_post_process_for_masked_implicit_gemm_1
+ * (kernels/cuda/spconv/migemm_neighmap_pp.cu:19-44, 85-154).
+ *
+ * coords: int32 [n,4] (b,x,y,z), 16-byte aligned.  table: fgb_hash_table_bytes
+ * bytes; its content on entry is ignored.  slots >= n.  V <= 32. */
+int fgb_subm_build_neighbor_map(const int32_t* coords, int64_t n,
+                                int W, int H, int D,
+                                int Kw, int Kh, int Kd,
+                                int Dw, int Dh, int Dd,
+                                void* table, int64_t slots, int key_bits,
+                                uint32_t* neighbor_map,
+                                int32_t* gray_code, int32_t* binary_code,
+                                uint32_t* block_offsets, uint32_t* valid_signal_seg,
+                                int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Post-processing for the masked implicit GEMM
+ * --------------------------------------------------------------------- */
+
+/* Workspace bytes for fgb_pp_sorted_idx. */
+int64_t fgb_pp_sorted_idx_workspace_bytes(int64_t n);
+
+/* sorted_idx (int64 [n]) = a stable argsort of binary_code (signed int32,
+ * only bits [0, key_bits) differ).  Stands in for torch::argsort(binary_code)
+ * in migemm_neighmap_pp.cu:79, 221. */
+int fgb_pp_sorted_idx(const int32_t* binary_code, int64_t n, int key_bits,
+                      int64_t* sorted_idx, void* workspace, int64_t workspace_bytes,
+                      void* stream);
+
+/* Pair lists for wgrad: grouped by offset v, ascending output row inside a
+ * group: valid_signal_o[p] = row, valid_signal_i[p] = neighbor_map[row, v].
+ * `block_offsets` and `valid_signal_seg` are the arrays written by
+ * fgb_subm_build_neighbor_map.  The lists need valid_signal_seg[V] entries.
+ * Stands in for the cumsum + gather_idx_val_seg_from_prefix_sum_kernel part of
+ * neighbor_map_post_process_for_masked_implicit_gemm_1
+ * (migemm_neighmap_pp.cu:157-178, 224-240). */
+int fgb_pp_valid_signal(const uint32_t* neighbor_map, const int32_t* gray_code,
+                        int64_t n, int V,
+                        const uint32_t* block_offsets, const uint32_t* valid_signal_seg,
+                        uint32_t* valid_signal_i, uint32_t* valid_signal_o,
+                        void* stream);
+
+/* tile_masks[t] = OR of gray_code[sorted_idx[r]] over the rows r of tile t
+ * (tile = `block` consecutive sorted rows, a power of two in [8, 1024]).
+ * This is reduced_code of reduce_code_kernel (migemm_neighmap_pp.cu:246-296);
+ * the conv kernels below consume it directly. */
+int fgb_pp_tile_masks(const int32_t* gray_code, const int64_t* sorted_idx, int64_t n,
+                      int block, uint32_t* tile_masks, void* stream);
+
+/* Expands tile masks to the reference's list form:
+ * valid_kernel_seg (int32 [nblk+1]) = exclusive prefix of popcounts,
+ * valid_kernel (int32, capacity nblk*32) = ascending set-bit positions.
+ * Stands in for neighbor_map_post_process_for_masked_implicit_gemm_2
+ * (migemm_neighmap_pp.cu:299-368).  Single pass, one CTA; nblk <= 2^24. */
+int fgb_pp_valid_kernel(const uint32_t* tile_masks, int64_t nblk,
+                        int32_t* valid_kernel, int32_t* valid_kernel_seg, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Masked implicit GEMM: fprop, dgrad, wgrad  (tcgen05 / TMEM, tile M = 128)
+ * --------------------------------------------------------------------- */
+
+/* Rows per tile used by the conv kernels: tile_masks passed to them must have
+ * been built with block == fgb_conv_tile_rows(). */
+int fgb_conv_tile_rows(void);
+
+/* out[r, :] = bias + sum_v feats[neighbor_map[r, v], :] * weight[:, v, :]^T
+ * for every row r, visiting only the offsets set in the row's tile mask.
+ * feats [n, Ci], weight [Co, V, Ci], bias [Co] or null, out [n, Co]; all of
+ * element type `dtype`, rows 16-byte aligned (Ci, Co multiples of 8 for 16-bit
+ * types, of 4 for fp32).
+ * Stands in for sparse_submanifold_conv_fwd_masked_implicit_gemm_splitk
+ * (flex_gemm/kernels/triton/spconv/
+ *  sparse_submanifold_conv_fwd_masked_implicit_gemm_splitk.py:21-172).
+ * `workspace` is needed only for FGB_F32_IEEE (fgb_conv_workspace_bytes). */
+int fgb_subm_conv_fprop(const void* feats, const void* weight, const void* bias,
+                        const uint32_t* neighbor_map, const int64_t* sorted_idx,
+                        const uint32_t* tile_masks,
+                        void* out, int64_t n, int Ci, int Co, int V, int dtype,
+                        void* workspace, int64_t workspace_bytes,
+                        int32_t* status, void* stream);
+
+/* grad_feats[r, :] = sum_v grad_out[neighbor_map[r, v], :] * weight[:, V-1-v, :]
+ * grad_out [n, Co], weight [Co, V, Ci], grad_feats [n, Ci].  The workspace
+ * holds the re-laid-out weight [Ci, V, Co] (fgb_conv_workspace_bytes).
+ * Stands in for sparse_submanifold_conv_bwd_input_masked_implicit_gemm_splitk
+ * (…/sparse_submanifold_conv_bwd_masked_implicit_gemm_splitk.py:23-100, 205-251). */
+int fgb_subm_conv_dgrad(const void* grad_out, const void* weight,
+                        const uint32_t* neighbor_map, const int64_t* sorted_idx,
+                        const uint32_t* tile_masks,
+                        void* grad_feats, int64_t n, int Ci, int Co, int V, int dtype,
+                        void* workspace, int64_t workspace_bytes,
+                        int32_t* status, void* stream);
+
+/* Workspace bytes for fprop (pass = 0), dgrad (pass = 1) and wgrad (pass = 2,
+ * with the given split count). */
+int64_t fgb_conv_workspace_bytes(int pass, int Ci, int Co, int V, int dtype, int splitk);
+
+/* Split count the library would pick for wgrad on the current device. */
+int fgb_wgrad_default_splitk(int64_t n_pairs, int Ci, int Co, int V, int dtype);
+
+/* grad_weight[co, v, ci] = sum_{p in segment v} grad_out[valid_signal_o[p], co]
+ *                                              * feats[valid_signal_i[p], ci]
+ * Each offset's pair range is cut into `splitk` parts whose fp32 partial sums
+ * go to the workspace and are then added up in a fixed order (deterministic).
+ * grad_weight (element type `dtype`) and/or grad_weight_f32 may be null; the
+ * fp32 copy is what a multi-GPU caller hands to its all-reduce.
+ * Stands in for sparse_submanifold_conv_bwd_weight_masked_implicit_gemm_splitk
+ * (…/sparse_submanifold_conv_bwd_masked_implicit_gemm_splitk.py:107-182, 274-317). */
+int fgb_subm_conv_wgrad(const void* grad_out, const void* feats,
+                        const uint32_t* valid_signal_i, const uint32_t* valid_signal_o,
+                        const uint32_t* valid_signal_seg,
+                        void* grad_weight, float* grad_weight_f32,
+                        int64_t n, int Ci, int Co, int V, int dtype, int splitk,
+                        void* workspace, int64_t workspace_bytes,
+                        int32_t* status, void* stream);
+
+/* grad_bias[c] = sum_r grad_out[r, c] accumulated in fp32; writes grad_bias
+ * (element type `dtype`) and/or grad_bias_f32, either may be null.
+ * Stands in for grad_output.sum(0)
+ * (…/sparse_submanifold_conv_bwd_masked_implicit_gemm_splitk.py:365-366).
+ * workspace: fgb_bias_grad_workspace_bytes(Co). */
+int64_t fgb_bias_grad_workspace_bytes(int Co);
+int fgb_subm_conv_bias_grad(const void* grad_out, void* grad_bias, float* grad_bias_f32,
+                            int64_t n, int Co, int dtype,
+                            void* workspace, int64_t workspace_bytes, void* stream);
+
+/* dst (element type `dtype`) = src (fp32), count elements: the cast applied to
+ * an all-reduced fp32 gradient. */
+int fgb_cast_from_f32(const float* src, void* dst, int64_t count, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLEXGEMM_B200_H_ */

@@ -1,0 +1,121 @@
+"""CPU-side checks: the library loads, exports what the header declares, and
+rejects bad arguments before launching anything."""
+import os
+import re
+
+import pytest
+import torch
+
+from flexgemm_b200 import _build, _cabi
+from flexgemm_b200.ops import spconv
+from flexgemm_b200.ops.spconv import SubMConv3dFunction
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    _build.build()
+    return _cabi.lib()
+
+
+def test_header_and_binding_agree(lib):
+    header = open(os.path.join(ROOT, "include", "flexgemm_b200.h")).read()
+    declared = set(re.findall(r"\b(fgb_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(_cabi.EXPORTS)
+    for name in declared:
+        assert hasattr(lib, name), name
+
+
+def test_version_and_errors(lib):
+    assert b"sm_100a" in lib.fgb_version()
+    assert _cabi.error_string(0) == "ok"
+    assert "null" in _cabi.error_string(-1)
+    with pytest.raises(ValueError):
+        _cabi.check(-2, "x")
+    with pytest.raises(RuntimeError):
+        _cabi.check(1001, "x")
+
+
+def test_size_queries(lib):
+    assert lib.fgb_hash_table_bytes(1000, 32) == 8000
+    assert lib.fgb_hash_table_bytes(1000, 64) == 12000
+    assert lib.fgb_hash_table_bytes(1000, 16) < 0
+    assert lib.fgb_hash_table_bytes(-1, 32) < 0
+    assert lib.fgb_map_num_blocks(0) == 0
+    assert lib.fgb_map_num_blocks(257) == 2
+    assert lib.fgb_conv_tile_rows() == 128
+    assert lib.fgb_conv_workspace_bytes(0, 64, 64, 27, _cabi.F16, 1) == 0
+    assert lib.fgb_conv_workspace_bytes(1, 64, 32, 27, _cabi.F16, 1) == 64 * 32 * 27 * 2
+    assert lib.fgb_conv_workspace_bytes(2, 64, 32, 27, _cabi.F16, 4) == 64 * 32 * 27 * 4 * 4
+    assert lib.fgb_conv_workspace_bytes(2, 64, 32, 27, 9, 4) < 0
+    assert lib.fgb_bias_grad_workspace_bytes(256) > 0
+
+
+def test_argument_validation_without_launch(lib):
+    # all of these return before touching the device
+    assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 2, 3, 3, 1, 1, 1, 0, 20, 32, 0, 0, 0, 0, 0, 0, 0) == -2  # even kernel
+    assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 3, 3, 5, 1, 1, 1, 0, 20, 32, 0, 0, 0, 0, 0, 0, 0) == -2  # V > 32
+    assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 5, 32, 0, 0, 0, 0, 0, 0, 0) == -2   # slots < n
+    assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 20, 48, 0, 0, 0, 0, 0, 0, 0) == -3  # key width
+    assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 20, 32, 0, 0, 0, 0, 0, 0, 0) == -1  # null seg
+    assert lib.fgb_pp_tile_masks(0, 0, 10, 100, 0, 0) == -2   # not a power of two
+    assert lib.fgb_subm_conv_fprop(0, 0, 0, 0, 0, 0, 0, 10, 64, 64, 27, _cabi.F16, 0, 0, 0, 0) == -1
+    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 16, 10, 60, 64, 27, _cabi.F16, 0, 0, 0, 0) == -4  # Ci % 8
+    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 16, 10, 64, 64, 27, 7, 0, 0, 0, 0) == -3
+    assert lib.fgb_subm_conv_wgrad(16, 16, 16, 16, 16, 16, 0, 10, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -5  # workspace
+
+
+def test_python_surface_matches_reference_names():
+    for name in ("Algorithm", "ALGORITHM", "HASHMAP_RATIO", "set_algorithm", "set_hashmap_ratio", "SubMConv3dFunction",
+                 "SubMConv3dNeighborCache", "sparse_submanifold_conv3d"):
+        assert hasattr(spconv, name), name
+    for name in ("_compute_neighbor_cache", "_compute_neighbor_cache_torch", "_sparse_submanifold_conv_forward",
+                 "_sparse_submanifold_conv_backward"):
+        assert hasattr(SubMConv3dFunction, name), name
+    assert spconv.ALGORITHM == spconv.Algorithm.MASKED_IMPLICIT_GEMM_SPLITK
+    with pytest.raises(ValueError):
+        spconv.set_algorithm("winograd")
+    with pytest.raises(ValueError):
+        spconv.set_hashmap_ratio(0.5)
+
+
+def test_cpu_tensors_are_rejected_not_emulated():
+    coords = torch.zeros((4, 4), dtype=torch.int32)
+    with pytest.raises(NotImplementedError):
+        SubMConv3dFunction._compute_neighbor_cache(coords, torch.Size((1, 8, 4, 4, 4)), (3, 3, 3), (1, 1, 1), True)
+    with pytest.raises(AssertionError):
+        SubMConv3dFunction._compute_neighbor_cache(coords.long(), torch.Size((1, 8, 4, 4, 4)), (3, 3, 3), (1, 1, 1), True)
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(_cabi, "_lib", None)
+    monkeypatch.setenv("FLEXGEMM_B200_LIB", "/nonexistent/libflexgemm_b200.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _cabi.lib()
+
+
+def test_explicit_algorithm_on_cpu_matches_golden():
+    """The library-GEMM cross-check path (Algorithm.EXPLICIT_GEMM) against the
+    reference-generated fixture."""
+    import numpy as np
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "conv_explicit.npz"))
+    name = "r8_c16_c24_f32"
+    t = {k: torch.from_numpy(gold[f"{name}/{k}"]) for k in
+         ("coords", "feats", "weight", "bias", "out", "grad_out", "grad_feats", "grad_weight", "grad_bias")}
+    shape = torch.Size(gold[name + "/shape"].tolist())
+    old = spconv.ALGORITHM
+    spconv.set_algorithm(spconv.Algorithm.EXPLICIT_GEMM)
+    try:
+        cache = SubMConv3dFunction._compute_neighbor_cache_torch(t["coords"], shape, (3, 3, 3), (1, 1, 1))
+        f = t["feats"].clone().requires_grad_(True)
+        w = t["weight"].clone().requires_grad_(True)
+        b = t["bias"].clone().requires_grad_(True)
+        out, _ = spconv.sparse_submanifold_conv3d(f, t["coords"], shape, w, b, cache)
+        out.backward(t["grad_out"])
+    finally:
+        spconv.set_algorithm(old)
+    assert torch.allclose(out, t["out"], atol=1e-5)
+    assert torch.allclose(f.grad, t["grad_feats"], atol=1e-5)
+    assert torch.allclose(w.grad, t["grad_weight"], atol=1e-4)
+    assert torch.allclose(b.grad, t["grad_bias"], atol=1e-4)

@@ -1,0 +1,275 @@
+"""GPU parity tests: every call goes through the C ABI (via the thin tensor
+wrappers) and is compared with the CPU oracle and the golden fixtures.
+
+Bars: integer outputs bit-exact (``sorted_idx``: a permutation under which the
+binary code is non-decreasing, because the reference's argsort is unstable);
+16-bit features and gradients within max|x - ref| <= 1e-2 * max|ref|; fp32 with
+TF32 within the same bound; fp32 with TF32 disabled within 1e-4 relative."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import submconv_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.fixture(scope="module")
+def K():
+    from flexgemm_b200.kernels import cuda
+    return cuda
+
+
+@pytest.fixture(autouse=True)
+def _masked_algorithm():
+    from flexgemm_b200.kernels import config
+    from flexgemm_b200.ops import spconv
+    spconv.set_algorithm(spconv.Algorithm.MASKED_IMPLICIT_GEMM_SPLITK)
+    spconv.set_hashmap_ratio(2.0)
+    config.allow_tf32 = True
+    yield
+    config.allow_tf32 = True
+
+
+DEV = torch.device("cuda:0")
+
+
+def u32(t):
+    return t.detach().cpu().view(torch.int32).numpy().view(np.uint32)
+
+
+def build_cache(coords_np, shape, ksize=(3, 3, 3), dil=(1, 1, 1), needs_grad=True):
+    from flexgemm_b200.ops.spconv import SubMConv3dFunction
+    coords = torch.from_numpy(np.ascontiguousarray(coords_np)).to(DEV)
+    return SubMConv3dFunction._compute_neighbor_cache(coords, torch.Size([int(s) for s in shape]), ksize, dil, needs_grad)
+
+
+def check_cache(cache, ref, V, needs_grad=True, blocks=(128, 32)):
+    nbr = u32(cache["neighbor_map"])
+    assert np.array_equal(nbr, ref["neighbor_map"])
+    assert np.array_equal(cache["gray_code"].cpu().numpy(), ref["gray_code"])
+    sidx = cache["sorted_idx"].cpu().numpy()
+    assert cache["sorted_idx"].dtype == torch.int64
+    assert orc.is_valid_sorted_idx(sidx, ref["binary_code"])
+    if needs_grad:
+        assert np.array_equal(u32(cache["valid_signal_seg"]), ref["valid_signal_seg"])
+        assert np.array_equal(u32(cache["valid_signal_i"]), ref["valid_signal_i"])
+        assert np.array_equal(u32(cache["valid_signal_o"]), ref["valid_signal_o"])
+    for b in blocks:
+        vk, seg = orc.valid_kernel(ref["gray_code"], sidx, b)
+        assert np.array_equal(u32(cache.tile_masks(b)), orc.tile_masks(ref["gray_code"], sidx, b))
+        assert np.array_equal(cache.valid_kernel_callback(b).cpu().numpy(), vk)
+        assert np.array_equal(cache.valid_kernel_seg_callback(b).cpu().numpy(), seg)
+
+
+# ----------------------------------------------------------------------------
+# neighbour map + post-processing: bit-exact
+# ----------------------------------------------------------------------------
+MAPS = np.load(os.path.join(GOLD, "neighbor_maps.npz"))
+
+
+@pytest.mark.parametrize("name", sorted({k.split("/")[0] for k in MAPS.files}))
+def test_neighbor_map_golden(name, K):
+    coords = MAPS[name + "/coords"]
+    shape = MAPS[name + "/shape"]
+    ks, dil = tuple(int(x) for x in MAPS[name + "/ksize"]), tuple(int(x) for x in MAPS[name + "/dilation"])
+    cache = build_cache(coords, shape, ks, dil)
+    assert np.array_equal(u32(cache["neighbor_map"]), MAPS[name + "/neighbor_map"])
+    check_cache(cache, orc.neighbor_cache(coords, shape, ks, dil), ks[0] * ks[1] * ks[2])
+
+
+@pytest.mark.parametrize("res,batch", [(32, 1), (64, 2), (128, 1)])
+def test_cache_vs_oracle_shells(res, batch, K):
+    scales = tuple(1.0 - 0.15 * i for i in range(batch))
+    coords = orc.shell_coords(res, batch=batch, scales=scales)
+    shape = (batch, 0, res, res, res)
+    for needs_grad in (True, False):
+        cache = build_cache(coords, shape, needs_grad=needs_grad)
+        assert ("valid_signal_i" in cache) == needs_grad
+        check_cache(cache, orc.neighbor_cache(coords, shape), 27, needs_grad)
+
+
+def test_cache_64bit_keys(K):
+    """B*W*H*D >= 2^32 selects the 64-bit key table; voxels placed near the far
+    corner of the last sample so that keys really exceed 32 bits."""
+    rng = np.random.default_rng(5)
+    base = orc.shell_coords(16)
+    parts = []
+    for b, off in ((0, 0), (7, 1024 - 16)):
+        c = base.copy()
+        c[:, 0] = b
+        c[:, 1:] += off
+        parts.append(c)
+    coords = np.concatenate(parts)
+    coords = np.ascontiguousarray(coords[rng.permutation(coords.shape[0])])
+    shape = (8, 0, 1024, 1024, 1024)
+    from flexgemm_b200.ops.utils import hashmap_key_bits
+    assert hashmap_key_bits(shape) == 64
+    check_cache(build_cache(coords, shape), orc.neighbor_cache(coords, shape), 27)
+
+
+def test_cache_tight_table_and_unsorted(K):
+    from flexgemm_b200.ops import spconv
+    rng = np.random.default_rng(9)
+    coords = orc.shell_coords(32)
+    coords = np.ascontiguousarray(coords[rng.permutation(coords.shape[0])])
+    spconv.set_hashmap_ratio(1.0)  # every slot used: probes wrap around
+    check_cache(build_cache(coords, (1, 0, 32, 32, 32)), orc.neighbor_cache(coords, (1, 0, 32, 32, 32)), 27)
+
+
+def test_cache_deterministic(K):
+    coords = orc.shell_coords(64)
+    a = build_cache(coords, (1, 0, 64, 64, 64))
+    b = build_cache(coords, (1, 0, 64, 64, 64))
+    for k in ("neighbor_map", "gray_code", "sorted_idx", "valid_signal_i", "valid_signal_o", "valid_signal_seg"):
+        assert torch.equal(a[k], b[k]), k
+
+
+def test_empty_and_tiny_inputs(K):
+    cache = build_cache(np.zeros((0, 4), np.int32), (1, 0, 8, 8, 8))
+    assert cache["neighbor_map"].shape == (0, 27)
+    assert cache["valid_signal_i"].shape == (0,)
+    assert np.array_equal(u32(cache["valid_signal_seg"]), np.zeros(28, np.uint32))
+    one = np.array([[0, 3, 3, 3]], np.int32)
+    check_cache(build_cache(one, (1, 0, 8, 8, 8)), orc.neighbor_cache(one, (1, 0, 8, 8, 8)), 27)
+
+
+# ----------------------------------------------------------------------------
+# features and gradients
+# ----------------------------------------------------------------------------
+def rel_err(got, want):
+    return (got.detach().cpu().double() - want.double()).abs().max().item() / max(want.double().abs().max().item(), 1e-30)
+
+
+def run_conv(coords, feats, weight, bias, shape, grad_out=None, cache=None):
+    from flexgemm_b200.ops import spconv
+    f = feats.to(DEV).requires_grad_(True)
+    w = weight.to(DEV).requires_grad_(True)
+    b = bias.to(DEV).requires_grad_(True) if bias is not None else None
+    out, cache = spconv.sparse_submanifold_conv3d(f, coords.to(DEV), torch.Size(shape), w, b, cache)
+    if grad_out is None:
+        out.sum().backward()
+    else:
+        out.backward(grad_out.to(DEV))
+    torch.cuda.synchronize()
+    from flexgemm_b200.kernels import cuda
+    cuda.check_status(DEV)
+    return out, f.grad, w.grad, (b.grad if b is not None else None), cache
+
+
+def oracle_conv(coords, feats, weight, bias, shape, grad_out=None):
+    nbr = orc.neighbor_map(coords.numpy(), shape)
+    f, w = feats.double(), weight.double()
+    b = bias.double() if bias is not None else None
+    out = orc.conv_forward(f, nbr, w, b)
+    g = torch.ones_like(out) if grad_out is None else grad_out.double()
+    gin, gw, gb = orc.conv_backward(g, f, nbr, w, has_bias=bias is not None)
+    return out, gin, gw, gb
+
+
+CONV_CASES = [
+    # res, ci, co, dtype, batch, tolerance
+    (16, 64, 64, "float16", 1, 1e-2),
+    (32, 64, 64, "float16", 1, 1e-2),
+    (32, 128, 256, "float16", 1, 1e-2),
+    (32, 256, 128, "bfloat16", 1, 1e-2),
+    (24, 32, 48, "float16", 2, 1e-2),
+    (16, 72, 40, "float16", 1, 1e-2),     # channel counts that are not multiples of 64
+    (32, 32, 32, "float32", 1, 1e-2),     # TF32
+    (16, 320, 512, "float16", 1, 1e-2),   # more than one output-channel tile / accumulator group
+    (64, 256, 256, "float16", 1, 1e-2),
+]
+
+
+@pytest.mark.parametrize("res,ci,co,dtype,batch,tol", CONV_CASES)
+def test_conv_fwd_bwd_vs_oracle(res, ci, co, dtype, batch, tol, K):
+    scales = tuple(1.0 - 0.2 * i for i in range(batch))
+    coords, feats, weight, bias, shape = orc.make_problem(res, ci, co, dtype, seed=res + ci + co, batch=batch, scales=scales)
+    g = torch.Generator().manual_seed(1)
+    grad_out = torch.randn(coords.shape[0], co, generator=g).to(feats.dtype)
+    got = run_conv(coords, feats, weight, bias, shape, grad_out)
+    want = oracle_conv(coords, feats, weight, bias, shape, grad_out)
+    for name, a, b in zip(("out", "grad_feats", "grad_weight", "grad_bias"), got[:4], want):
+        assert a.dtype == feats.dtype and a.shape == b.shape, name
+        assert rel_err(a, b) <= tol, (name, rel_err(a, b))
+
+
+CONV = np.load(os.path.join(GOLD, "conv_explicit.npz"))
+
+
+@pytest.mark.parametrize("name", ["r16_c32_c32_f32", "r12_c64_c32_f16", "r8_c16_c24_f32"])
+def test_conv_vs_reference_golden(name, K):
+    """Against outputs of the reference's own explicit path (fixture)."""
+    t = {k: torch.from_numpy(CONV[f"{name}/{k}"]) for k in
+         ("coords", "feats", "weight", "bias", "out", "grad_out", "grad_feats", "grad_weight", "grad_bias")}
+    shape = CONV[name + "/shape"].tolist()
+    got = run_conv(t["coords"], t["feats"], t["weight"], t["bias"], shape, t["grad_out"])
+    for key, a in zip(("out", "grad_feats", "grad_weight", "grad_bias"), got[:4]):
+        assert rel_err(a, t[key]) <= 1e-2, (key, rel_err(a, t[key]))
+
+
+def test_conv_without_bias_and_cache_reuse(K):
+    coords, feats, weight, _, shape = orc.make_problem(16, 64, 64, "float16", seed=21)
+    out, gin, gw, gb, cache = run_conv(coords, feats, weight, None, shape)
+    want = oracle_conv(coords, feats, weight, None, shape)
+    assert gb is None
+    assert rel_err(out, want[0]) <= 1e-2 and rel_err(gin, want[1]) <= 1e-2 and rel_err(gw, want[2]) <= 1e-2
+    out2, gin2, gw2, _, cache2 = run_conv(coords, feats, weight, None, shape, cache=cache)
+    assert cache2 is cache
+    assert torch.equal(out, out2) and torch.equal(gin, gin2) and torch.equal(gw, gw2)  # deterministic
+
+
+def test_no_grad_forward_builds_inference_cache(K):
+    from flexgemm_b200.ops import spconv
+    coords, feats, weight, bias, shape = orc.make_problem(16, 64, 64, "float16", seed=22)
+    with torch.no_grad():
+        out, cache = spconv.sparse_submanifold_conv3d(feats.to(DEV), coords.to(DEV), torch.Size(shape), weight.to(DEV), bias.to(DEV))
+    assert "valid_signal_i" not in cache
+    assert rel_err(out, oracle_conv(coords, feats, weight, bias, shape)[0]) <= 1e-2
+
+
+def test_all_implicit_algorithms_agree(K):
+    from flexgemm_b200.ops import spconv
+    coords, feats, weight, bias, shape = orc.make_problem(16, 64, 64, "float16", seed=23)
+    outs = []
+    for alg in (spconv.Algorithm.IMPLICIT_GEMM, spconv.Algorithm.IMPLICIT_GEMM_SPLITK, spconv.Algorithm.MASKED_IMPLICIT_GEMM,
+                spconv.Algorithm.MASKED_IMPLICIT_GEMM_SPLITK, spconv.Algorithm.EXPLICIT_GEMM):
+        spconv.set_algorithm(alg)
+        outs.append(run_conv(coords, feats, weight, bias, shape)[:4])
+    want = oracle_conv(coords, feats, weight, bias, shape)
+    for o in outs:
+        for a, b in zip(o, want):
+            assert rel_err(a, b) <= 1e-2
+    for o in outs[1:4]:
+        for a, b in zip(o, outs[0]):
+            assert torch.equal(a, b)
+
+
+def test_linearity_at_benchmark_size(K):
+    """Size-independent property at the headline size (RES=256, C=256 fp16):
+    conv(a + b) == conv(a) + conv(b) without bias, and the centre-only weight
+    reproduces a plain matmul of the features."""
+    from flexgemm_b200.ops import spconv
+    coords = torch.from_numpy(orc.shell_coords(256)).to(DEV)
+    n = coords.shape[0]
+    shape = torch.Size((1, 256, 256, 256, 256))
+    g = torch.Generator(device="cpu").manual_seed(3)
+    a = torch.randn(n, 256, generator=g).half().to(DEV)
+    b = torch.randn(n, 256, generator=g).half().to(DEV)
+    w = (torch.randn(256, 3, 3, 3, 256, generator=g) / (27 * 256) ** 0.5).half().to(DEV)
+    with torch.no_grad():
+        ya, cache = spconv.sparse_submanifold_conv3d(a, coords, shape, w)
+        yb, _ = spconv.sparse_submanifold_conv3d(b, coords, shape, w, None, cache)
+        yab, _ = spconv.sparse_submanifold_conv3d((a.float() + b.float()).half(), coords, shape, w, None, cache)
+        scale = yab.float().abs().max().item()
+        assert (yab.float() - ya.float() - yb.float()).abs().max().item() <= 2e-2 * scale
+        wc = torch.zeros_like(w)
+        wc[:, 1, 1, 1, :] = w[:, 1, 1, 1, :]
+        yc, _ = spconv.sparse_submanifold_conv3d(a, coords, shape, wc, None, cache)
+        ref = a.float() @ w[:, 1, 1, 1, :].float().t()
+        assert (yc.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item()
+    K.check_status(DEV)
