@@ -122,8 +122,12 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
   uint8_t* stages = smem + kCtrlBytes + kNbrTileBytes;
   const int stage_bytes = kATileBytes + p.bn * 128;
 
-  // a kernel that already reported a soft error makes the rest of the grid a no-op
-  if (p.status != nullptr && *reinterpret_cast<volatile const int32_t*>(p.status) != 0) return;
+  // A kernel that already reported a soft error makes the rest of the grid a
+  // no-op.  One thread reads the word so that the whole CTA takes the same branch.
+  __shared__ int s_skip;
+  if (threadIdx.x == 0) s_skip = p.status != nullptr && *reinterpret_cast<volatile const int32_t*>(p.status) != 0;
+  __syncthreads();
+  if (s_skip) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t n_tile = blockIdx.x % p.n_tiles_n;
   const uint32_t m_tile = blockIdx.x / p.n_tiles_n;

@@ -150,13 +150,18 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 //   8-row groups are 1024 B apart (SBO = 1024); LBO is not used.
 // MN-major operand (rows = K index, 128 B = 64 x 16-bit of M or N per row):
 //   8-row groups along K are SBO apart, 64-element groups along M/N are LBO apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// MN-major operand of 32-bit elements (tf32): the only layout the tensor core
+//   accepts is kSwizzle128B32 -- rows of 128 B whose four 32-byte chunks are
+//   XOR-swizzled with (row & 3); 4-row groups along K are SBO apart.
+enum : uint32_t { kSwizzle128B = 2, kSwizzle128B32 = 1 };
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t layout = kSwizzle128B) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
+  d |= static_cast<uint64_t>(layout) << 61;
   return d;
 }
 

@@ -71,6 +71,10 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
   constexpr bool kTF32 = (kElem == 4);
   constexpr int kUmmaK = 32 / kElem;      // 16 for 16-bit types, 8 for tf32
   constexpr int kChunkElems = 128 / kElem;
+  // MN-major operands: 16-bit types use the plain 128-byte swizzle (8-row K groups, 1024 B apart);
+  // tf32 needs the 32-byte-based variant (4-row K groups, 512 B apart)
+  constexpr uint32_t kLayout = kElem == 2 ? kSwizzle128B : kSwizzle128B32;
+  constexpr uint32_t kSbo = kElem == 2 ? 1024 : 512;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   WgradSmem* ctl = reinterpret_cast<WgradSmem*>(smem);
@@ -79,8 +83,12 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
   const int a_bytes = p.a_chunks * chunk_bytes;
   const int stage_bytes = (p.a_chunks + p.b_chunks) * chunk_bytes;
 
-  // a kernel that already reported a soft error makes the rest of the grid a no-op
-  if (p.status != nullptr && *reinterpret_cast<volatile const int32_t*>(p.status) != 0) return;
+  // A kernel that already reported a soft error makes the rest of the grid a
+  // no-op.  One thread reads the word so that the whole CTA takes the same branch.
+  __shared__ int s_skip;
+  if (threadIdx.x == 0) s_skip = p.status != nullptr && *reinterpret_cast<volatile const int32_t*>(p.status) != 0;
+  __syncthreads();
+  if (s_skip) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // work item
   uint32_t bid = blockIdx.x;
@@ -155,7 +163,9 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
         const bool ok = gidx != kInvalid && col_bytes < (is_b ? b_row_bytes : a_row_bytes);
         const char* base = is_b ? p.x : p.gout;
         const char* src = ok ? base + size_t(gidx) * (is_b ? b_row_bytes : a_row_bytes) + col_bytes : base;
-        const uint32_t dst = st_base + (is_b ? a_bytes : 0) + c * chunk_bytes + row * 128 + ((piece ^ (row & 7)) << 4);
+        // 16-bit types: 16-byte pieces swizzled by (row & 7); tf32: 32-byte pieces swizzled by (row & 3)
+        const int swz = kElem == 2 ? ((piece ^ (row & 7)) << 4) : (((((piece >> 1) ^ (row & 3)) << 1) | (piece & 1)) << 4);
+        const uint32_t dst = st_base + (is_b ? a_bytes : 0) + c * chunk_bytes + row * 128 + swz;
         cp_async_16(dst, src, ok ? 16u : 0u);
       }
       cp_async_commit();
@@ -214,9 +224,9 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
         const int chunks_per_m = 128 / kChunkElems;  // 128-byte chunks per 128 accumulator rows
         for (int ks = 0; ks < p.kb / kUmmaK; ++ks) {
           const uint32_t koff = ks * kUmmaK * 128;  // kUmmaK pair rows of 128 bytes
-          const uint64_t db = make_smem_desc(b_addr + koff, chunk_bytes, 1024);
+          const uint64_t db = make_smem_desc(b_addr + koff, chunk_bytes, kSbo, kLayout);
           for (int mt = 0; mt < p.mt; ++mt) {
-            const uint64_t da = make_smem_desc(a_addr + mt * chunks_per_m * chunk_bytes + koff, chunk_bytes, 1024);
+            const uint64_t da = make_smem_desc(a_addr + mt * chunks_per_m * chunk_bytes + koff, chunk_bytes, kSbo, kLayout);
             umma_ss<kTF32>(tmem_base + mt * p.bn, da, db, p.idesc, accumulate);
           }
           accumulate = 1;
