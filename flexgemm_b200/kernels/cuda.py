@@ -42,6 +42,16 @@ def _stream(device) -> int:
 _scratch: Dict[tuple, torch.Tensor] = {}
 _status: Dict[int, torch.Tensor] = {}
 
+# Number of this library's own kernels launched so far (CUB's radix-sort kernels
+# inside fgb_pp_sorted_idx are not counted).  Each wrapper adds the fixed number
+# of kernels its C entry point launches.
+launch_count = 0
+
+
+def _count(k: int) -> None:
+    global launch_count
+    launch_count += k
+
 
 def workspace(device: torch.device, tag: str, nbytes: int) -> torch.Tensor:
     """A reusable 256-byte aligned scratch buffer of at least ``nbytes`` bytes.
@@ -107,6 +117,7 @@ def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table:
         out["block_offsets"].data_ptr(), out["valid_signal_seg"].data_ptr(),
         status_word(dev).data_ptr(), _stream(dev))
     _cabi.check(rc, "fgb_subm_build_neighbor_map")
+    _count(4)
     return out
 
 
@@ -122,6 +133,7 @@ def sorted_idx_from_binary(binary_code: torch.Tensor, key_bits: int) -> torch.Te
     ws = workspace(dev, "sort", nbytes)
     rc = lib.fgb_pp_sorted_idx(binary_code.data_ptr(), n, int(key_bits), out.data_ptr(), ws.data_ptr(), ws.numel() * 8, _stream(dev))
     _cabi.check(rc, "fgb_pp_sorted_idx")
+    _count(1)
     return out
 
 
@@ -136,6 +148,7 @@ def valid_signal(neighbor_map: torch.Tensor, gray_code: torch.Tensor, block_offs
     rc = lib.fgb_pp_valid_signal(_ptr(neighbor_map), _ptr(gray_code), n, V, block_offsets.data_ptr(),
                                  valid_signal_seg.data_ptr(), _ptr(vs_i), _ptr(vs_o), _stream(dev))
     _cabi.check(rc, "fgb_pp_valid_signal")
+    _count(1)
     return vs_i, vs_o
 
 
@@ -147,6 +160,7 @@ def tile_masks(gray_code: torch.Tensor, sorted_idx: torch.Tensor, block: int) ->
     out = torch.empty(nblk, dtype=torch.uint32, device=dev)
     rc = lib.fgb_pp_tile_masks(_ptr(gray_code), _ptr(sorted_idx), n, int(block), _ptr(out), _stream(dev))
     _cabi.check(rc, "fgb_pp_tile_masks")
+    _count(1)
     return out
 
 
@@ -161,6 +175,7 @@ def valid_kernel(masks: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     vk = torch.empty(max(nblk * 32, 1), dtype=torch.int32, device=dev)
     rc = lib.fgb_pp_valid_kernel(_ptr(masks), nblk, vk.data_ptr(), seg.data_ptr(), _stream(dev))
     _cabi.check(rc, "fgb_pp_valid_kernel")
+    _count(1)
     total = int(seg[-1].item())
     return vk[:total].clone(), seg
 
@@ -186,6 +201,7 @@ def conv_fprop(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks) -> torc
                                  _ptr(masks), _ptr(out), n, Ci, Co, V, code, _ptr(ws), ws.numel() * 8 if ws is not None else 0,
                                  status_word(dev).data_ptr(), _stream(dev))
     _cabi.check(rc, "fgb_subm_conv_fprop")
+    _count(1)
     return out
 
 
@@ -203,6 +219,7 @@ def conv_dgrad(grad_out, weight_cvc, neighbor_map, sorted_idx, masks) -> torch.T
                                  _ptr(out), n, Ci, Co, V, code, ws.data_ptr(), ws.numel() * 8,
                                  status_word(dev).data_ptr(), _stream(dev))
     _cabi.check(rc, "fgb_subm_conv_dgrad")
+    _count(2)
     return out
 
 
@@ -227,6 +244,7 @@ def conv_wgrad(grad_out, feats, vs_i, vs_o, vs_seg, splitk: Optional[int] = None
                                  n, Ci, Co, V, code, int(splitk), ws.data_ptr(), ws.numel() * 8,
                                  status_word(dev).data_ptr(), _stream(dev))
     _cabi.check(rc, "fgb_subm_conv_wgrad")
+    _count(2)
     return gw, gw32
 
 
@@ -241,6 +259,7 @@ def bias_grad(grad_out, want_f32: bool = False, want_dtype: bool = True):
     ws = workspace(dev, "bias", nbytes)
     rc = lib.fgb_subm_conv_bias_grad(_ptr(grad_out), _ptr(gb), _ptr(gb32), n, Co, code, ws.data_ptr(), ws.numel() * 8, _stream(dev))
     _cabi.check(rc, "fgb_subm_conv_bias_grad")
+    _count(2)
     return gb, gb32
 
 
@@ -249,4 +268,5 @@ def cast_from_f32(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     code = _DTYPES.get(dtype, _cabi.F32_TF32)
     rc = _cabi.lib().fgb_cast_from_f32(_ptr(src), _ptr(out), src.numel(), code, _stream(src.device))
     _cabi.check(rc, "fgb_cast_from_f32")
+    _count(1)
     return out
