@@ -36,6 +36,8 @@ _PROTOTYPES = {
     "fgb_bias_grad_workspace_bytes": (c_int64, [c_int]),
     "fgb_subm_conv_bias_grad": (c_int, [_P, _P, _P, c_int64, c_int, c_int, _P, c_int64, _P]),
     "fgb_cast_from_f32": (c_int, [_P, _P, c_int64, c_int, _P]),
+    "fgb_noalloc_max_channels": (c_int, []),
+    "fgb_subm_conv_bias_grad_noalloc": (c_int, [_P, _P, _P, c_int64, c_int, c_int, _P]),
 }
 
 EXPORTS = tuple(sorted(_PROTOTYPES))

@@ -19,6 +19,8 @@ extern "C" const char* fgb_error_string(int code) {
       return "workspace too small";
     case FGB_E_DRIVER:
       return "CUDA driver entry point unavailable or tensor map rejected";
+    case FGB_E_STATIC_LIMIT:
+      return "size exceeds the built-in scratch of the no-allocation entry point";
     default:
       break;
   }

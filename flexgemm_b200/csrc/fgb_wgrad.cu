@@ -18,6 +18,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
 #include <type_traits>
 
 #include "fgb_common.cuh"
@@ -440,6 +441,75 @@ extern "C" int fgb_subm_conv_bias_grad(const void* grad_out, void* grad_bias, fl
   if (workspace_bytes < fgb_bias_grad_workspace_bytes(Co)) return FGB_E_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* partial = static_cast<float*>(workspace);
+  const int nblk = static_cast<int>(n < kBiasBlocks ? (n > 0 ? n : 1) : kBiasBlocks);
+  const unsigned fblocks = static_cast<unsigned>(ceil_div(Co, 256));
+  switch (dtype) {
+    case FGB_F16:
+      bias_partial_kernel<__half><<<nblk, 256, 0, s>>>(static_cast<const __half*>(grad_out), n, Co, partial);
+      bias_final_kernel<__half><<<fblocks, 256, 0, s>>>(partial, nblk, Co, static_cast<__half*>(grad_bias), grad_bias_f32);
+      break;
+    case FGB_BF16:
+      bias_partial_kernel<__nv_bfloat16><<<nblk, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(grad_out), n, Co, partial);
+      bias_final_kernel<__nv_bfloat16><<<fblocks, 256, 0, s>>>(partial, nblk, Co, static_cast<__nv_bfloat16*>(grad_bias), grad_bias_f32);
+      break;
+    default:
+      bias_partial_kernel<float><<<nblk, 256, 0, s>>>(static_cast<const float*>(grad_out), n, Co, partial);
+      bias_final_kernel<float><<<fblocks, 256, 0, s>>>(partial, nblk, Co, static_cast<float*>(grad_bias), grad_bias_f32);
+  }
+  return launch_status();
+}
+
+// ------------------------------------------------------------------ bias gradient without caller scratch
+// Some callers may not allocate device memory at all: a host runtime that hands
+// its plug-ins a fixed arena and forbids further allocations, or a service
+// loop that cannot afford the device-wide synchronisation cudaMalloc implies.
+// For them the partial sums of the bias gradient live in a buffer that is part
+// of the library image itself.  Every GPU that loads the library carries these
+// kBiasBlocks * kNoAllocMaxCo * 4 bytes (4.6 MiB) until the process exits.
+constexpr int kNoAllocMaxCo = 2048;
+static __device__ __align__(256) float g_bias_partials[size_t(fgb::kBiasBlocks) * kNoAllocMaxCo];
+
+namespace {
+// In host code `g_bias_partials` is only a handle for the runtime, not an
+// address a kernel can use; the device address differs per GPU and is asked
+// for once per device, with that device current.
+int bias_partials_address(float** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static float* addr[kMaxDevices] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fgb::cuda_status(e);
+  if (dev < 0 || dev >= kMaxDevices) return FGB_E_SIZE;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_bias_partials);
+    if (e != cudaSuccess) return fgb::cuda_status(e);
+    if (p == nullptr) return FGB_E_DRIVER;
+    addr[dev] = static_cast<float*>(p);
+  }
+  *out = addr[dev];
+  return FGB_OK;
+}
+}  // namespace
+
+extern "C" int fgb_noalloc_max_channels(void) { return kNoAllocMaxCo; }
+
+extern "C" int fgb_subm_conv_bias_grad_noalloc(const void* grad_out, void* grad_bias, float* grad_bias_f32, int64_t n, int Co,
+                                               int dtype, void* stream) {
+  using namespace fgb;
+  const int eb = elem_bytes(dtype);
+  if (eb == 0) return FGB_E_DTYPE;
+  if (n < 0 || Co <= 0) return FGB_E_SIZE;
+  if (Co > kNoAllocMaxCo) return FGB_E_STATIC_LIMIT;
+  if (n > 0 && !grad_out) return FGB_E_NULL;
+  float* partial = nullptr;
+  int rc = bias_partials_address(&partial);
+  if (rc != FGB_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // Nothing has to be cleared between calls: the first kernel overwrites every
+  // partial sum that the second one reads (nblk rows of Co floats).
   const int nblk = static_cast<int>(n < kBiasBlocks ? (n > 0 ? n : 1) : kBiasBlocks);
   const unsigned fblocks = static_cast<unsigned>(ceil_div(Co, 256));
   switch (dtype) {

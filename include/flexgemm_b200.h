@@ -33,6 +33,7 @@ extern "C" {
 #define FGB_E_ALIGN (-4)      /* pointer or channel count misaligned   */
 #define FGB_E_WORKSPACE (-5)  /* workspace too small                   */
 #define FGB_E_DRIVER (-6)     /* CUDA driver entry point unavailable   */
+#define FGB_E_STATIC_LIMIT (-7) /* larger than a no-allocation entry point's built-in scratch */
 #define FGB_E_CUDA_BASE 1000  /* 1000 + cudaError_t                    */
 
 /* device-side status codes (written to *status) */
@@ -198,6 +199,31 @@ int64_t fgb_bias_grad_workspace_bytes(int Co);
 int fgb_subm_conv_bias_grad(const void* grad_out, void* grad_bias, float* grad_bias_f32,
                             int64_t n, int Co, int dtype,
                             void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Bias gradient for callers that cannot allocate device memory.
+ * (No counterpart in the reference: its bias gradient is a torch reduction that
+ * allocates freely.)
+ *
+ * Same result as fgb_subm_conv_bias_grad, but the caller passes no workspace:
+ * the fp32 partial sums live in a fixed buffer inside the library image
+ * (592 * 2048 floats = 4.6 MiB, resident on every GPU that loads the library,
+ * for the life of the process).  Meant for hosts that give a plug-in a fixed
+ * arena and forbid cudaMalloc, and for loops that cannot tolerate the
+ * device-wide synchronisation an allocation implies.  The call itself performs
+ * no cudaMalloc / cudaFree and uses no allocating library routine.
+ *
+ *  - Co must be <= fgb_noalloc_max_channels() (2048); larger returns
+ *    FGB_E_STATIC_LIMIT and launches nothing.
+ *  - The first call on each device looks up the buffer's device address
+ *    (cudaGetSymbolAddress, with that device current).  Make that first call
+ *    before starting any stream capture.
+ *  - All calls on a device share the one buffer, and it keeps whatever the last
+ *    call left in it.  Nothing needs clearing (each call overwrites every value
+ *    it later reads), but two calls that overlap on the GPU -- different
+ *    streams without an ordering between them -- race on it.  Serialise them. */
+int fgb_noalloc_max_channels(void);
+int fgb_subm_conv_bias_grad_noalloc(const void* grad_out, void* grad_bias, float* grad_bias_f32,
+                                    int64_t n, int Co, int dtype, void* stream);
 
 /* dst (element type `dtype`) = src (fp32), count elements: the cast applied to
  * an all-reduced fp32 gradient. */
