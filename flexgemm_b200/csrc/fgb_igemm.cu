@@ -9,7 +9,9 @@
 // Warp roles (192 threads):
 //   warps 0-3  gather the activation rows of the tile into a 128B-swizzled
 //              K-major shared-memory stage with 16-byte cp.async (zero fill for
-//              missing neighbours and past the channel count), and afterwards
+//              missing neighbours and past the channel count); each thread's
+//              copies arrive on the stage's mbarrier when they land, so up to
+//              all stages are in flight; afterwards the same warps
 //              run the epilogue (tcgen05.ld -> +bias -> convert -> row store);
 //   warp 4     one lane streams the dense weight tile [BN x 128 B] of the
 //              current (offset, slice) with a tiled TMA load;
@@ -30,7 +32,6 @@ namespace fgb {
 
 constexpr int kTileM = 128;
 constexpr int kStages = 4;
-constexpr int kLag = 2;                 // cp.async groups a gather thread keeps in flight
 constexpr int kIgemmThreads = 192;
 constexpr int kCtrlBytes = 1024;        // barriers, TMEM holder, abort flag, sorted rows
 constexpr int kNbrTileBytes = kTileM * 32 * 4;
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&ctl->full[s], 5);   // 4 gather warps + the TMA lane's expect_tx arrive
+      mbar_init(&ctl->full[s], 129);  // 128 gather threads (on completion of their copies) + the TMA lane's expect_tx arrive
       mbar_init(&ctl->empty[s], 1);  // one tcgen05.commit
     }
     mbar_init(&ctl->acc_full, 1);
@@ -193,20 +194,8 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
           const char* src = ok ? p.x + size_t(idx[j]) * p.row_bytes + col : p.x;
           cp_async_16(a_base + r * 128 + ((chunk ^ (r & 7)) << 4), src, ok ? 16u : 0u);
         }
-        cp_async_commit();
-        if (it >= kLag) {
-          cp_async_wait<kLag>();
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&ctl->full[(it - kLag) % kStages]);
-        }
+        cp_async_arrive(&ctl->full[s]);
       }
-    }
-    cp_async_wait<0>();
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) {
-      for (int j = max(total - kLag, 0); j < total; ++j) mbar_arrive(&ctl->full[j % kStages]);
     }
 
     // -------------------------------------------------------------- epilogue

@@ -89,6 +89,12 @@ __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fe
 __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
 }
+// Arrive on `bar` once every cp.async this thread has issued so far has landed
+// in shared memory.  The arrival is one of the barrier's expected count
+// (.noinc), so the issuing thread never blocks on its own copies.
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

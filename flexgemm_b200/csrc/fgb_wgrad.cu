@@ -18,6 +18,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -27,7 +28,6 @@
 namespace fgb {
 
 constexpr int kWgThreads = 192;
-constexpr int kWgLag = 1;  // cp.async groups kept in flight per gather thread
 constexpr int kWgMaxStages = 8;
 
 struct WgradParams {
@@ -49,6 +49,7 @@ struct WgradParams {
   int b_chunks;
   uint32_t idesc;
   uint32_t tmem_cols;
+  int order;  // CTA order: 0 = offset-major, 1 = split-major
   int32_t* status;
 };
 
@@ -92,13 +93,23 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
   if (s_skip) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // work item
+  // Split-major order: CTAs that run at the same time work on the same slice of
+  // the pair lists of all offsets.  The lists are sorted by output row and a
+  // neighbour's row is close to its voxel's row, so the slice touches a narrow
+  // band of rows of both gathered matrices and that band stays in L2.
   uint32_t bid = blockIdx.x;
   const int ci_tile = bid % p.ci_tiles;
   bid /= p.ci_tiles;
   const int co_group = bid % p.co_groups;
   bid /= p.co_groups;
-  const int split = bid % p.splitk;
-  const int v = bid / p.splitk;
+  int v, split;
+  if (p.order == 1) {
+    v = bid % p.V;
+    split = bid / p.V;
+  } else {
+    split = bid % p.splitk;
+    v = bid / p.splitk;
+  }
   const int co0 = co_group * p.mt * 128;
   const int ci0 = ci_tile * p.bn;
 
@@ -113,7 +124,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&ctl->full[s], 4);
+      mbar_init(&ctl->full[s], 128);  // every gather thread, on completion of its copies
       mbar_init(&ctl->empty[s], 1);
     }
     mbar_init(&ctl->acc_full, 1);
@@ -169,21 +180,9 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
         const uint32_t dst = st_base + (is_b ? a_bytes : 0) + c * chunk_bytes + row * 128 + swz;
         cp_async_16(dst, src, ok ? 16u : 0u);
       }
-      cp_async_commit();
+      cp_async_arrive(&ctl->full[s]);
       if (j < p.kb) ctl->idx[buf ^ 1][which][j] = next_idx;
       named_barrier_sync(1, 128);
-      if (it >= kWgLag) {
-        cp_async_wait<kWgLag>();
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl->full[(it - kWgLag) % p.stages]);
-      }
-    }
-    cp_async_wait<0>();
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) {
-      for (int j = max(total - kWgLag, 0); j < total; ++j) mbar_arrive(&ctl->full[j % p.stages]);
     }
 
     // -------------------------------------------------------------- epilogue
@@ -277,25 +276,63 @@ __global__ void __launch_bounds__(256) cast_from_f32_kernel(const float* __restr
 
 // ------------------------------------------------------------------ bias gradient
 constexpr int kBiasBlocks = 592;  // 4 per SM on a 148-SM part
+// partial[b, c] = sum of column c over the rows of block b.  When the row is a
+// whole number of 16-byte vectors, a thread owns one vector column and every
+// (256 / vectors-per-row)-th row of the block, and the row groups are added up
+// through shared memory; otherwise one thread per column walks the rows.
 template <typename T>
 __global__ void __launch_bounds__(256) bias_partial_kernel(const T* __restrict__ g, int64_t n, int Co, float* __restrict__ partial) {
+  constexpr int kVec = 16 / sizeof(T);
+  __shared__ float s_acc[256 * kVec];
   const int64_t rows_per = (n + gridDim.x - 1) / gridDim.x;
   const int64_t r0 = blockIdx.x * rows_per, r1 = min(n, r0 + rows_per);
-  for (int c = threadIdx.x; c < Co; c += 256) {
-    float acc = 0.f;
-    for (int64_t r = r0; r < r1; ++r) acc += static_cast<float>(g[r * Co + c]);
-    partial[size_t(blockIdx.x) * Co + c] = acc;
+  const int ncg = Co / kVec;
+  if (Co % kVec == 0 && ncg <= 256 && 256 % ncg == 0 && (reinterpret_cast<uintptr_t>(g) & 15) == 0) {
+    const int cg = threadIdx.x % ncg, rg = threadIdx.x / ncg, nrg = 256 / ncg;
+    float acc[kVec];
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) acc[i] = 0.f;
+    for (int64_t r = r0 + rg; r < r1; r += nrg) {
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(g + r * Co) + cg);
+      const T* e = reinterpret_cast<const T*>(&w);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) acc[i] += static_cast<float>(e[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) s_acc[threadIdx.x * kVec + i] = acc[i];
+    __syncthreads();
+    for (int c = threadIdx.x; c < Co; c += 256) {
+      float sum = 0.f;
+      for (int k = 0; k < nrg; ++k) sum += s_acc[(k * ncg + c / kVec) * kVec + c % kVec];  // fixed order
+      partial[size_t(blockIdx.x) * Co + c] = sum;
+    }
+  } else {
+    for (int c = threadIdx.x; c < Co; c += 256) {
+      float acc = 0.f;
+      for (int64_t r = r0; r < r1; ++r) acc += static_cast<float>(g[r * Co + c]);
+      partial[size_t(blockIdx.x) * Co + c] = acc;
+    }
   }
 }
+// out[c] = sum_b partial[b, c]: 32 columns per CTA, 8 row groups added up in a fixed order
 template <typename T>
 __global__ void __launch_bounds__(256) bias_final_kernel(const float* __restrict__ partial, int nblk, int Co, T* __restrict__ out,
                                                          float* __restrict__ out_f32) {
-  const int c = blockIdx.x * 256 + threadIdx.x;
-  if (c >= Co) return;
+  __shared__ float s_acc[8][32];
+  const int lane = threadIdx.x & 31, rg = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float acc = 0.f;
-  for (int b = 0; b < nblk; ++b) acc += partial[size_t(b) * Co + c];
-  if (out_f32) out_f32[c] = acc;
-  if (out) out[c] = static_cast<T>(acc);
+  if (c < Co)
+    for (int b = rg; b < nblk; b += 8) acc += partial[size_t(b) * Co + c];
+  s_acc[rg][lane] = acc;
+  __syncthreads();
+  if (rg == 0 && c < Co) {
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sum += s_acc[k][lane];
+    if (out_f32) out_f32[c] = sum;
+    if (out) out[c] = static_cast<T>(sum);
+  }
 }
 
 static int pick_bn(int c) {
@@ -401,6 +438,10 @@ extern "C" int fgb_subm_conv_wgrad(const void* grad_out, const void* feats, cons
   const uint32_t fmt = dtype == FGB_F16 ? kFmtF16 : dtype == FGB_BF16 ? kFmtBF16 : kFmtTF32;
   p.idesc = make_idesc(fmt, 128, w.bn, 1, 1);
   p.tmem_cols = w.tmem_cols;
+  {
+    const char* e = getenv("FGB_WGRAD_ORDER");
+    p.order = e ? atoi(e) : 0;
+  }
   p.status = status;
   const int64_t grid = int64_t(V) * splitk * w.co_groups * w.ci_tiles;
   cudaError_t e;
@@ -442,7 +483,7 @@ extern "C" int fgb_subm_conv_bias_grad(const void* grad_out, void* grad_bias, fl
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* partial = static_cast<float*>(workspace);
   const int nblk = static_cast<int>(n < kBiasBlocks ? (n > 0 ? n : 1) : kBiasBlocks);
-  const unsigned fblocks = static_cast<unsigned>(ceil_div(Co, 256));
+  const unsigned fblocks = static_cast<unsigned>(ceil_div(Co, 32));
   switch (dtype) {
     case FGB_F16:
       bias_partial_kernel<__half><<<nblk, 256, 0, s>>>(static_cast<const __half*>(grad_out), n, Co, partial);
@@ -511,7 +552,7 @@ extern "C" int fgb_subm_conv_bias_grad_noalloc(const void* grad_out, void* grad_
   // Nothing has to be cleared between calls: the first kernel overwrites every
   // partial sum that the second one reads (nblk rows of Co floats).
   const int nblk = static_cast<int>(n < kBiasBlocks ? (n > 0 ? n : 1) : kBiasBlocks);
-  const unsigned fblocks = static_cast<unsigned>(ceil_div(Co, 256));
+  const unsigned fblocks = static_cast<unsigned>(ceil_div(Co, 32));
   switch (dtype) {
     case FGB_F16:
       bias_partial_kernel<__half><<<nblk, 256, 0, s>>>(static_cast<const __half*>(grad_out), n, Co, partial);
