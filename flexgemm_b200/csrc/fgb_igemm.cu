@@ -2,27 +2,37 @@
 //
 //   out[r, :] = bias + sum_{v in mask(tile(r))} x[nbr[r, v], :] . Wn[:, v, :]^T
 //
-// One CTA computes a tile of 128 sorted rows by BN output channels.  The
-// accumulator lives in tensor memory; the reduction runs over the offsets set
-// in the tile's mask times the 128-byte slices of the channel dimension.
+// Persistent kernel: one CTA per SM walks over work items (a block of 256
+// sorted rows x BN output channels).  The block is two 128-row halves with one
+// TMEM accumulator each; both halves multiply the same dense weight tile, so a
+// weight tile fetched once feeds two MMAs, and each half skips the offsets that
+// are absent from its own 27-bit mask (no gather, no MMA for it).
 //
-// Warp roles (192 threads):
-//   warps 0-3  gather the activation rows of the tile into a 128B-swizzled
-//              K-major shared-memory stage with 16-byte cp.async (zero fill for
-//              missing neighbours and past the channel count); each thread's
-//              copies arrive on the stage's mbarrier when they land, so up to
-//              all stages are in flight; afterwards the same warps
-//              run the epilogue (tcgen05.ld -> +bias -> convert -> row store);
-//   warp 4     one lane streams the dense weight tile [BN x 128 B] of the
-//              current (offset, slice) with a tiled TMA load;
-//   warp 5     owns the TMEM allocation; one lane issues tcgen05.mma and
-//              commits stage releases to the mbarriers.
+// Warp roles (448 threads):
+//   warps 0-3   epilogue: tcgen05.ld -> +bias -> convert -> staged through a
+//               small swizzled shared-memory buffer so that every global store
+//               instruction writes whole 128-byte lines of out[sorted_idx[row]];
+//               runs while the next block is gathered;
+//   warp 4      one lane streams the dense weight tile [BN x 128 B] of the
+//               current (offset, channel slice) with a tiled TMA load;
+//   warp 5      owns the TMEM allocation; one lane issues tcgen05.mma and
+//               releases stages / publishes accumulators with tcgen05.commit;
+//   warps 6-13  gather the activation rows of both halves into a 128B-swizzled
+//               K-major stage with 16-byte cp.async (zero fill for missing
+//               neighbours and past the channel count).  Neighbour indices are
+//               read straight from the map into registers one offset ahead;
+//               each thread's copies arrive on the stage's mbarrier when they
+//               land, so every stage can be in flight at once.
+//   (A TMA row gather -- tile::gather4 -- was measured for the activation rows:
+//    correct, zero-fills missing rows, but ~2.4x slower than cp.async for
+//    128-byte rows, so the copies stay on the LSU path.)
 //
 // dgrad is the same kernel: x = grad_out, the weight is first re-laid-out to
 // [Ci, V, Co] and offset v reads weight slot V-1-v.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <type_traits>
 
 #include "fgb_common.cuh"
@@ -30,82 +40,91 @@
 
 namespace fgb {
 
-constexpr int kTileM = 128;
-constexpr int kStages = 4;
-constexpr int kIgemmThreads = 192;
-constexpr int kCtrlBytes = 1024;        // barriers, TMEM holder, abort flag, sorted rows
-constexpr int kNbrTileBytes = kTileM * 32 * 4;
+constexpr int kTileM = 128;             // rows per accumulator (and per tile mask)
+constexpr int kBlockM = 2 * kTileM;     // rows per work item
+constexpr int kMaxStages = 6;
+constexpr int kIgemmThreads = 448;
+constexpr int kGatherWarp0 = 6;
+constexpr int kGatherThreads = 256;
+constexpr int kStoreStageBytes = 4 * 4096;  // per epilogue warp: 32 rows x 128 bytes
+constexpr int kCtrlBytes = 1024;        // barriers, TMEM holder, abort flag
 constexpr int kATileBytes = kTileM * 128;
+constexpr int kSmemBudget = 226 * 1024;
 
 struct IgemmParams {
   const char* x;             // [n, kc] gathered operand
   const void* bias;          // [nout] or null
   const uint32_t* nbr;       // [n, V]
   const int64_t* sorted_idx; // [n]
-  const uint32_t* tile_masks;
+  const uint32_t* tile_masks; // one mask per 128 sorted rows
   char* out;                 // [n, nout]
   uint32_t n;
+  uint32_t num_tiles;        // ceil(n / 128)
+  uint32_t num_work;         // row blocks x column tiles
   int kc;                    // reduction channels per offset
   int nout;                  // output channels
   int V;
-  int bn;                    // output channels per CTA (32, 64, 128, 256)
+  int bn;                    // output channels per work item (32, 64, 128, 256)
   int n_tiles_n;
   int row_bytes;             // kc * element size
   int num_kb;                // 128-byte slices per row
   int flip;                  // weight slot = flip ? V-1-v : v
-  int dtype;
+  int stages;
+  int acc_sets;              // accumulator pairs that fit in TMEM (1 or 2)
   uint32_t idesc;
+  unsigned long long* dbg;   // per-CTA timing counters when debug & 128
+  int debug;                 // timing experiments: 1 no gather, 2 no weight loads, 4 no MMA, 8 no stores
   int32_t* status;
 };
 
 struct IgemmSmem {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
-  uint64_t acc_full;
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
-  uint32_t pad[26];
-  uint32_t srow[kTileM];  // original row of each tile row, kInvalid past the end
 };
 static_assert(sizeof(IgemmSmem) <= kCtrlBytes, "control block too large");
 
+// Adds the bias to 32 accumulator columns of one row, converts them and writes
+// them as 16-byte pieces into the warp's staging buffer: row `lane`, pieces
+// chunk*4 .. chunk*4+3 (16-bit types: two chunks fill a 128-byte row) or 0 .. 7
+// (fp32: one chunk is a whole 128-byte row); piece p of row r sits at p ^ (r & 7).
 template <int kDtype>
-__device__ __forceinline__ void store_row_chunk(char* dst, const uint32_t (&acc)[32], const void* bias, int col0, int nout,
-                                                bool zero_acc) {
+__device__ __forceinline__ void stage_row_chunk(uint8_t* stage, int lane, int chunk, const uint32_t (&acc)[32], const void* bias,
+                                                int col0, int nout, bool zero_acc) {
   float v[32];
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = zero_acc ? 0.f : __uint_as_float(acc[i]);
+  uint8_t* row = stage + lane * 128;
   if constexpr (kDtype == FGB_F16 || kDtype == FGB_BF16) {
     using T = typename std::conditional<kDtype == FGB_F16, __half, __nv_bfloat16>::type;
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {  // 8 columns = 16 bytes per store
+    for (int g = 0; g < 4; ++g) {  // 8 columns = 16 bytes
       const int c = col0 + g * 8;
-      if (c < nout) {
-        if (bias != nullptr) {
-          const uint4 bw = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(bias) + c));
-          const T* bt = reinterpret_cast<const T*>(&bw);
+      if (bias != nullptr && c < nout) {
+        const uint4 bw = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(bias) + c));
+        const T* bt = reinterpret_cast<const T*>(&bw);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) v[g * 8 + i] += static_cast<float>(bt[i]);
-        }
-        uint4 o;
-        T* ot = reinterpret_cast<T*>(&o);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ot[i] = static_cast<T>(v[g * 8 + i]);
-        *reinterpret_cast<uint4*>(dst + size_t(c) * 2) = o;
+        for (int i = 0; i < 8; ++i) v[g * 8 + i] += static_cast<float>(bt[i]);
       }
+      uint4 o;
+      T* ot = reinterpret_cast<T*>(&o);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ot[i] = static_cast<T>(v[g * 8 + i]);
+      *reinterpret_cast<uint4*>(row + (((chunk * 4 + g) ^ (lane & 7)) << 4)) = o;
     }
   } else {
 #pragma unroll
-    for (int g = 0; g < 8; ++g) {  // 4 columns = 16 bytes per store
+    for (int g = 0; g < 8; ++g) {  // 4 columns = 16 bytes
       const int c = col0 + g * 4;
-      if (c < nout) {
-        float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-        if (bias != nullptr) {
-          const float4 b = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(bias) + c));
-          o.x += b.x, o.y += b.y, o.z += b.z, o.w += b.w;
-        }
-        *reinterpret_cast<float4*>(dst + size_t(c) * 4) = o;
+      float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+      if (bias != nullptr && c < nout) {
+        const float4 b = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(bias) + c));
+        o.x += b.x, o.y += b.y, o.z += b.z, o.w += b.w;
       }
+      *reinterpret_cast<float4*>(row + ((g ^ (lane & 7)) << 4)) = o;
     }
   }
 }
@@ -119,9 +138,9 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
   // dynamic shared memory is only guaranteed 16-byte aligned: align by hand
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   IgemmSmem* ctl = reinterpret_cast<IgemmSmem*>(smem);
-  uint32_t* s_nbr = reinterpret_cast<uint32_t*>(smem + kCtrlBytes);
-  uint8_t* stages = smem + kCtrlBytes + kNbrTileBytes;
-  const int stage_bytes = kATileBytes + p.bn * 128;
+  uint8_t* stages = smem + kCtrlBytes;
+  const int stage_bytes = 2 * kATileBytes + p.bn * 128;  // A half 0 | A half 1 | B
+  const int S = p.stages;
 
   // A kernel that already reported a soft error makes the rest of the grid a
   // no-op.  One thread reads the word so that the whole CTA takes the same branch.
@@ -130,134 +149,269 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
   __syncthreads();
   if (s_skip) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t n_tile = blockIdx.x % p.n_tiles_n;
-  const uint32_t m_tile = blockIdx.x / p.n_tiles_n;
-  const uint32_t m0 = m_tile * kTileM;
-  const int n0 = n_tile * p.bn;
   const int V = p.V;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&ctl->full[s], 129);  // 128 gather threads (on completion of their copies) + the TMA lane's expect_tx arrive
-      mbar_init(&ctl->empty[s], 1);  // one tcgen05.commit
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&ctl->full[s], kGatherThreads + 1);  // every gather thread (when its copies land) + the TMA lane
+      mbar_init(&ctl->empty[s], 1);                  // one tcgen05.commit
     }
-    mbar_init(&ctl->acc_full, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&ctl->acc_full[a], 1);   // tcgen05.commit after the block's last MMA
+      mbar_init(&ctl->acc_empty[a], 4);  // the four epilogue warps
+    }
     ctl->abort_flag = 0;
     mbar_init_fence();
   }
   if (warp == 4 && lane == 0) tma_prefetch_desc(&tmap_w);
   if (warp == 5) {
-    tmem_alloc_dyn(&ctl->tmem_base, static_cast<uint32_t>(p.bn));
+    tmem_alloc_dyn(&ctl->tmem_base, 512u);
     tmem_relinquish();
-  }
-  if (tid < kTileM) {
-    const uint32_t r = m0 + tid;
-    ctl->srow[tid] = r < p.n ? static_cast<uint32_t>(__ldg(&p.sorted_idx[r])) : kInvalid;
-  }
-  __syncthreads();
-  for (int i = tid; i < kTileM * V; i += kIgemmThreads) {
-    const int r = i / V, v = i - r * V;
-    const uint32_t sr = ctl->srow[r];
-    s_nbr[i] = sr != kInvalid ? __ldg(&p.nbr[size_t(sr) * V + v]) : kInvalid;
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
-  const uint32_t mask = __ldg(&p.tile_masks[m_tile]);
-  const int total = __popc(mask) * p.num_kb;
 
-  if (warp < 4) {
+  // Every role walks the same sequence: work item w -> (row block, column tile);
+  // within it the offsets of the union mask in ascending order, num_kb slices each.
+  auto masks_of = [&](uint32_t mblk, uint32_t& m0, uint32_t& m1) {
+    const uint32_t t0 = mblk * 2;
+    m0 = __ldg(&p.tile_masks[t0]);
+    m1 = t0 + 1 < p.num_tiles ? __ldg(&p.tile_masks[t0 + 1]) : 0u;
+  };
+
+  if (warp >= kGatherWarp0) {
     // ---------------------------------------------------------------- gather
-    const int chunk = lane & 7;
-    const int rsub = lane >> 3;
-    int it = 0;
-    uint32_t m = mask;
-    while (m) {
-      const int v = __ffs(m) - 1;
-      m &= m - 1;
-      // neighbour rows of this lane's 8 tile rows for offset v
-      uint32_t idx[8];
+    if (p.debug & 16) goto done;
+    const int piece = lane & 7;
+    const int g = (warp - kGatherWarp0) * 4 + (lane >> 3);  // 0..31: rows g, g+32, ... of the block
+    // shared-memory offset of this thread's 16 bytes for each of its 8 rows (j < 4: half 0)
+    uint32_t dst_off[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) idx[j] = s_nbr[(warp * 32 + j * 4 + rsub) * V + v];
-      for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-        const int s = it % kStages;
-        mbar_wait(&ctl->empty[s], ((it / kStages) & 1) ^ 1, abort_flag);
-        const uint32_t a_base = smem_u32(stages + size_t(s) * stage_bytes);
-        const int col = kb * 128 + chunk * 16;
-        const bool col_ok = col < p.row_bytes;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int r = warp * 32 + j * 4 + rsub;
-          const bool ok = col_ok && idx[j] != kInvalid;
-          const char* src = ok ? p.x + size_t(idx[j]) * p.row_bytes + col : p.x;
-          cp_async_16(a_base + r * 128 + ((chunk ^ (r & 7)) << 4), src, ok ? 16u : 0u);
-        }
-        cp_async_arrive(&ctl->full[s]);
-      }
+    for (int j = 0; j < 8; ++j) {
+      const int r = g + 32 * (j & 3);
+      dst_off[j] = (j >> 2) * kATileBytes + r * 128 + ((piece ^ (r & 7)) << 4);
     }
-
-    // -------------------------------------------------------------- epilogue
-    if (total > 0) mbar_wait(&ctl->acc_full, 0, abort_flag);
-    tc_fence_after_sync();
-    const uint32_t sr = ctl->srow[warp * 32 + lane];
-    char* orow = p.out + size_t(sr) * p.nout * kElem;
-    for (int c0 = 0; c0 < p.bn; c0 += 32) {
-      uint32_t acc[32];
-      if (total > 0) {
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c0, acc);
-        tmem_ld_wait();
+    auto load_rows = [&](uint32_t mblk, uint32_t (&rows)[8]) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t r = mblk * kBlockM + (j >> 2) * kTileM + g + 32 * (j & 3);
+        rows[j] = r < p.n ? static_cast<uint32_t>(__ldg(&p.sorted_idx[r])) : kInvalid;
       }
-      if (sr != kInvalid && n0 + c0 < p.nout) store_row_chunk<kDtype>(orow, acc, p.bias, n0 + c0, p.nout, total == 0);
+    };
+    auto load_idx = [&](const uint32_t (&rows)[8], int v, uint32_t m0, uint32_t m1, uint32_t (&idx)[8]) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool need = ((j < 4 ? m0 : m1) >> v) & 1u;
+        idx[j] = (need && rows[j] != kInvalid) ? __ldg(&p.nbr[size_t(rows[j]) * V + v]) : kInvalid;
+      }
+    };
+    uint32_t it = 0;
+    uint32_t w = blockIdx.x;
+    uint32_t rows[8], nrows[8], idx[8], nidx[8];
+    uint32_t m0 = 0, m1 = 0, nm0 = 0, nm1 = 0;
+    if (w < p.num_work) {
+      const uint32_t mblk = w / p.n_tiles_n;
+      masks_of(mblk, m0, m1);
+      load_rows(mblk, rows);
+      if (m0 | m1) load_idx(rows, __ffs(m0 | m1) - 1, m0, m1, nidx);
+    }
+    for (; w < p.num_work; w += gridDim.x) {
+      // rows and masks of the next work item, fetched a whole block ahead
+      const uint32_t wn = w + gridDim.x;
+      const bool has_next = wn < p.num_work;
+      if (has_next) {
+        const uint32_t mblk_n = wn / p.n_tiles_n;
+        masks_of(mblk_n, nm0, nm1);
+        load_rows(mblk_n, nrows);
+      }
+      uint32_t un = m0 | m1;
+      while (un) {
+        const int v = __ffs(un) - 1;
+        un &= un - 1;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) idx[j] = nidx[j];
+        // neighbour indices one offset ahead (or the first offset of the next block)
+        if (un) {
+          load_idx(rows, __ffs(un) - 1, m0, m1, nidx);
+        } else if (has_next && (nm0 | nm1)) {
+          load_idx(nrows, __ffs(nm0 | nm1) - 1, nm0, nm1, nidx);
+        }
+        const bool need0 = (m0 >> v) & 1u, need1 = (m1 >> v) & 1u;
+        const char* src[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) src[j] = p.x + size_t(idx[j] != kInvalid ? idx[j] : 0u) * p.row_bytes + piece * 16;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const uint32_t s = it % S;
+          mbar_wait(&ctl->empty[s], ((it / S) & 1) ^ 1, abort_flag);
+          const uint32_t a_base = smem_u32(stages + size_t(s) * stage_bytes);
+          const bool col_ok = kb * 128 + piece * 16 < p.row_bytes;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if ((j < 4 ? need0 : need1) && !(p.debug & 1)) {
+              const bool ok = col_ok && idx[j] != kInvalid;
+              cp_async_16(a_base + dst_off[j], src[j] + kb * 128, ok ? 16u : 0u);
+            }
+          }
+          cp_async_arrive(&ctl->full[s]);
+        }
+      }
+      m0 = nm0, m1 = nm1;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) rows[j] = nrows[j];
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------ weight TMA
-    if (lane == 0) {
-      int it = 0;
-      uint32_t m = mask;
-      while (m) {
-        const int v = __ffs(m) - 1;
-        m &= m - 1;
-        const int wv = p.flip ? V - 1 - v : v;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-          const int s = it % kStages;
-          mbar_wait(&ctl->empty[s], ((it / kStages) & 1) ^ 1, abort_flag);
-          mbar_arrive_expect_tx(&ctl->full[s], static_cast<uint32_t>(p.bn) * 128u);
-          tma_load_3d(smem_u32(stages + size_t(s) * stage_bytes + kATileBytes), &tmap_w, &ctl->full[s], kb * (128 / kElem), wv, n0);
+    if (lane == 0 && !(p.debug & 16)) {
+      uint32_t it = 0;
+      for (uint32_t w = blockIdx.x; w < p.num_work; w += gridDim.x) {
+        const uint32_t mblk = w / p.n_tiles_n;
+        const int n0 = static_cast<int>(w % p.n_tiles_n) * p.bn;
+        uint32_t m0, m1;
+        masks_of(mblk, m0, m1);
+        uint32_t un = m0 | m1;
+        while (un) {
+          const int v = __ffs(un) - 1;
+          un &= un - 1;
+          const int wv = p.flip ? V - 1 - v : v;
+          for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+            const uint32_t s = it % S;
+            mbar_wait(&ctl->empty[s], ((it / S) & 1) ^ 1, abort_flag);
+            if (p.debug & 2) {
+              mbar_arrive(&ctl->full[s]);
+              continue;
+            }
+            mbar_arrive_expect_tx(&ctl->full[s], static_cast<uint32_t>(p.bn) * 128u);
+            tma_load_3d(smem_u32(stages + size_t(s) * stage_bytes + 2 * kATileBytes), &tmap_w, &ctl->full[s], kb * (128 / kElem), wv, n0);
+          }
         }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------- MMA
+    if (lane == 0) {
+      uint32_t it = 0, item = 0;
+      unsigned long long t_acc = 0, t_full = 0, t_all = global_timer_ns(), n_it = 0;
+      for (uint32_t w = blockIdx.x; w < p.num_work; w += gridDim.x, ++item) {
+        const uint32_t mblk = w / p.n_tiles_n;
+        uint32_t m0, m1;
+        masks_of(mblk, m0, m1);
+        const uint32_t set = item % p.acc_sets;
+        const uint32_t acc_tmem = tmem_base + set * 2 * p.bn;
+        // the epilogue must have drained this accumulator pair
+        unsigned long long t0 = (p.debug & 128) ? global_timer_ns() : 0;
+        mbar_wait(&ctl->acc_empty[set], ((item / p.acc_sets) & 1) ^ 1, abort_flag);
+        if (p.debug & 128) t_acc += global_timer_ns() - t0;
+        tc_fence_after_sync();
+        uint32_t acc0 = 0, acc1 = 0;
+        uint32_t un = m0 | m1;
+        while (un) {
+          const int v = __ffs(un) - 1;
+          un &= un - 1;
+          const bool need0 = (m0 >> v) & 1u, need1 = (m1 >> v) & 1u;
+          for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+            const uint32_t s = it % S;
+            if (p.debug & 128) t0 = global_timer_ns();
+            if (!(p.debug & 16)) mbar_wait(&ctl->full[s], (it / S) & 1, abort_flag);
+            if (p.debug & 128) t_full += global_timer_ns() - t0, ++n_it;
+            tc_fence_after_sync();
+            const uint32_t a_addr = smem_u32(stages + size_t(s) * stage_bytes);
+            const uint64_t da0 = make_smem_desc(a_addr, 16, 1024);
+            const uint64_t da1 = make_smem_desc(a_addr + kATileBytes, 16, 1024);
+            const uint64_t db = make_smem_desc(a_addr + 2 * kATileBytes, 16, 1024);
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              if (kb * 128 + k4 * 32 < p.row_bytes && !(p.debug & 4)) {
+                if (need0) {
+                  umma_ss<kTF32>(acc_tmem, da0 + uint64_t(k4 * 2), db + uint64_t(k4 * 2), p.idesc, acc0);
+                  acc0 = 1;
+                }
+                if (need1) {
+                  umma_ss<kTF32>(acc_tmem + p.bn, da1 + uint64_t(k4 * 2), db + uint64_t(k4 * 2), p.idesc, acc1);
+                  acc1 = 1;
+                }
+              }
+            }
+            if (!(p.debug & 16)) umma_commit(&ctl->empty[s]);
+          }
+        }
+        umma_commit(&ctl->acc_full[set]);
+      }
+      if ((p.debug & 128) && p.dbg) {
+        p.dbg[blockIdx.x * 4 + 0] = global_timer_ns() - t_all;
+        p.dbg[blockIdx.x * 4 + 1] = t_acc;
+        p.dbg[blockIdx.x * 4 + 2] = t_full;
+        p.dbg[blockIdx.x * 4 + 3] = n_it;
       }
     }
   } else {
-    // ------------------------------------------------------------------- MMA
-    if (lane == 0) {
-      uint32_t accumulate = 0;
-      for (int it = 0; it < total; ++it) {
-        const int s = it % kStages;
-        const int kb = it % p.num_kb;
-        mbar_wait(&ctl->full[s], (it / kStages) & 1, abort_flag);
-        tc_fence_after_sync();
-        const uint32_t a_addr = smem_u32(stages + size_t(s) * stage_bytes);
-        const uint64_t da = make_smem_desc(a_addr, 16, 1024);
-        const uint64_t db = make_smem_desc(a_addr + kATileBytes, 16, 1024);
+    // -------------------------------------------------------------- epilogue
+    // Thread `lane` of warp w owns accumulator row 32w + lane.  64 columns at a
+    // time go through a per-warp staging buffer [32 rows][128 or 256 bytes] whose
+    // 16-byte pieces are XOR-swizzled, and come back so that eight (fp32: sixteen)
+    // consecutive lanes hold one row's contiguous bytes.
+    uint8_t* stage_out = smem + kCtrlBytes + size_t(S) * stage_bytes + warp * 4096;
+    constexpr int kColsPerPass = 4096 / 32 / kElem;  // 64 columns of 16-bit, 32 columns of fp32: 128 bytes per row
+    constexpr int kChunksPerPass = kColsPerPass / 32 > 0 ? kColsPerPass / 32 : 1;
+    uint32_t item = 0;
+    for (uint32_t w = blockIdx.x; w < p.num_work; w += gridDim.x, ++item) {
+      const uint32_t mblk = w / p.n_tiles_n;
+      const int n0 = static_cast<int>(w % p.n_tiles_n) * p.bn;
+      uint32_t m0, m1;
+      masks_of(mblk, m0, m1);
+      const uint32_t set = item % p.acc_sets;
+      uint32_t sr[2];
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) {
-          if (kb * 128 + k4 * 32 < p.row_bytes) {
-            umma_ss<kTF32>(tmem_base, da + uint64_t(k4 * 2), db + uint64_t(k4 * 2), p.idesc, accumulate);
-            accumulate = 1;
-          }
-        }
-        umma_commit(&ctl->empty[s]);
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t r = mblk * kBlockM + h * kTileM + warp * 32 + lane;
+        sr[h] = r < p.n ? static_cast<uint32_t>(__ldg(&p.sorted_idx[r])) : kInvalid;
       }
-      if (total > 0) umma_commit(&ctl->acc_full);
+      mbar_wait(&ctl->acc_full[set], (item / p.acc_sets) & 1, abort_flag);
+      tc_fence_after_sync();
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const bool has_acc = (h == 0 ? m0 : m1) != 0u;  // a half without offsets holds no rows
+        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + set * 2 * p.bn + h * p.bn;
+        for (int c0 = 0; c0 < p.bn; c0 += kColsPerPass) {
+#pragma unroll
+          for (int cc = 0; cc < kChunksPerPass; ++cc) {
+            uint32_t acc[32];
+            if (has_acc && !(p.debug & 32)) {
+              tmem_ld_32x32(t_addr + c0 + cc * 32, acc);
+              tmem_ld_wait();
+            }
+            if (!(p.debug & 64)) stage_row_chunk<kDtype>(stage_out, lane, cc, acc, p.bias, n0 + c0 + cc * 32, p.nout, !has_acc);
+          }
+          __syncwarp();
+          if (!(p.debug & 8)) {
+            // 128 bytes per row: lane -> (row = 4 i + lane / 8, piece = lane % 8)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int row = i * 4 + (lane >> 3), piece = lane & 7;
+              const uint32_t orow = __shfl_sync(0xffffffffu, sr[h], row);
+              const int col = n0 + c0 + piece * (16 / kElem);
+              const uint4 val = *reinterpret_cast<const uint4*>(stage_out + row * 128 + ((piece ^ (row & 7)) << 4));
+              if (orow != kInvalid && col < p.nout)
+                *reinterpret_cast<uint4*>(p.out + (size_t(orow) * p.nout + col) * kElem) = val;
+            }
+          }
+          __syncwarp();
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->acc_empty[set]);
     }
   }
 
+done:
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 5) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, static_cast<uint32_t>(p.bn));
+    tmem_dealloc(tmem_base, 512u);
   }
   if (tid == 0 && ctl->abort_flag) report(p.status, FGB_S_WAIT_TIMEOUT);
 }
@@ -320,22 +474,30 @@ static int pick_bn(int nout) {
   return bn;
 }
 
+static int sm_count() {
+  static int sms = []() {
+    int dev = 0, n = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+  }();
+  return sms;
+}
+
 template <int kDtype>
 static int launch_igemm(const CUtensorMap& tmap, const IgemmParams& p, cudaStream_t s) {
-  const size_t smem = 1024 + kCtrlBytes + kNbrTileBytes + size_t(kStages) * (kATileBytes + p.bn * 128);
+  const size_t smem = 1024 + kCtrlBytes + size_t(p.stages) * (2 * kATileBytes + p.bn * 128) + kStoreStageBytes;
   static size_t configured = 0;
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(subm_igemm_kernel<kDtype>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return cuda_status(e);
     configured = smem;
   }
-  const int64_t m_tiles = ceil_div(p.n, kTileM);
-  const int64_t grid = m_tiles * p.n_tiles_n;
-  if (grid > 0x7FFFFFFF) return FGB_E_SIZE;
-  subm_igemm_kernel<kDtype><<<static_cast<unsigned>(grid), kIgemmThreads, smem, s>>>(tmap, p);
+  const unsigned grid = static_cast<unsigned>(p.num_work < uint32_t(sm_count()) ? p.num_work : uint32_t(sm_count()));
+  subm_igemm_kernel<kDtype><<<grid, kIgemmThreads, smem, s>>>(tmap, p);
   return launch_status();
 }
 
+static unsigned long long* g_dbg_buffer = nullptr;
 // x [n, kc] gathered through nbr; w [nout, V, kc]; out [n, nout]
 int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nbr, const int64_t* sorted_idx,
               const uint32_t* tile_masks, void* out, int64_t n, int kc, int nout, int V, int dtype, int flip, int32_t* status,
@@ -365,7 +527,19 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   p.row_bytes = kc * eb;
   p.num_kb = static_cast<int>(ceil_div(p.row_bytes, 128));
   p.flip = flip;
-  p.dtype = dtype;
+  p.num_tiles = static_cast<uint32_t>(ceil_div(n, kTileM));
+  const int64_t num_work = ceil_div(n, kBlockM) * p.n_tiles_n;
+  if (num_work > 0x7FFFFFFF) return FGB_E_SIZE;
+  p.num_work = static_cast<uint32_t>(num_work);
+  const int stage_bytes = 2 * kATileBytes + p.bn * 128;
+  p.stages = (kSmemBudget - 1024 - kCtrlBytes - kStoreStageBytes) / stage_bytes;
+  if (p.stages > kMaxStages) p.stages = kMaxStages;
+  p.acc_sets = 2 * p.bn * 2 <= 512 ? 2 : 1;
+  {
+    const char* e = getenv("FGB_IGEMM_DEBUG");
+    p.debug = e ? atoi(e) : 0;
+    p.dbg = g_dbg_buffer;
+  }
   const uint32_t fmt = dtype == FGB_F16 ? kFmtF16 : dtype == FGB_BF16 ? kFmtBF16 : kFmtTF32;
   p.idesc = make_idesc(fmt, kTileM, p.bn, 0, 0);
   p.status = status;
@@ -385,6 +559,7 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
 }  // namespace fgb
 
 extern "C" int fgb_conv_tile_rows(void) { return fgb::kTileM; }
+extern "C" void fgb_debug_set_buffer(void* p) { fgb::g_dbg_buffer = static_cast<unsigned long long*>(p); }
 
 extern "C" int fgb_subm_conv_fprop(const void* feats, const void* weight, const void* bias, const uint32_t* neighbor_map,
                                    const int64_t* sorted_idx, const uint32_t* tile_masks, void* out, int64_t n, int Ci, int Co,
