@@ -32,7 +32,7 @@ _PROTOTYPES = {
     "fgb_subm_conv_dgrad": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
     "fgb_conv_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "fgb_wgrad_default_splitk": (c_int, [c_int64, c_int, c_int, c_int, c_int]),
-    "fgb_subm_conv_wgrad": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
+    "fgb_subm_conv_wgrad": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
     "fgb_bias_grad_workspace_bytes": (c_int64, [c_int]),
     "fgb_subm_conv_bias_grad": (c_int, [_P, _P, _P, c_int64, c_int, c_int, _P, c_int64, _P]),
     "fgb_cast_from_f32": (c_int, [_P, _P, c_int64, c_int, _P]),

@@ -27,7 +27,9 @@
 
 namespace fgb {
 
-constexpr int kWgThreads = 192;
+constexpr int kWgThreads = 416;   // 4 epilogue warps, 1 MMA warp, 8 gather warps
+constexpr int kWgGatherWarp0 = 5;
+constexpr int kWgGatherThreads = 256;
 constexpr int kWgMaxStages = 8;
 
 struct WgradParams {
@@ -36,9 +38,9 @@ struct WgradParams {
   const uint32_t* vs_i;
   const uint32_t* vs_o;
   const uint32_t* seg;  // [V + 1]
-  float* partial;       // [splitk, Co, V, Ci]
+  float* partial;       // [units, Co, Ci] slabs
   int Co, Ci, V;
-  int splitk;
+  int unit_kb;    // k-blocks (stages of pairs) per unit
   int mt;         // 128-row accumulator blocks per CTA (1 or 2)
   int bn;         // input channels per CTA
   int co_groups;  // ceil(Co / (mt * 128))
@@ -49,7 +51,7 @@ struct WgradParams {
   int b_chunks;
   uint32_t idesc;
   uint32_t tmem_cols;
-  int order;  // CTA order: 0 = offset-major, 1 = split-major
+  int order;      // unit enumeration: 0 = offset-major, 1 = chunk-major
   int32_t* status;
 };
 
@@ -59,13 +61,50 @@ struct WgradSmem {
   uint64_t acc_full;
   uint32_t tmem_base;
   uint32_t abort_flag;
-  uint32_t pad[28];
-  uint32_t idx[2][2][64];  // [buffer][0 = output rows (A), 1 = input rows (B)][pair]
+  int unit_v, unit_j;  // the unit this CTA works on (offset, chunk index), -1 if none
 };
-static_assert(sizeof(WgradSmem) <= 2048, "control block too large");
+static_assert(sizeof(WgradSmem) <= 1024, "control block too large");
 
-__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+// Units: offset v is cut into ceil(nk_v / unit_kb) chunks of unit_kb k-blocks
+// (nk_v = k-blocks of the offset's pair list).  Unit ids enumerate (v, chunk)
+// either offset-major or chunk-major.  Returns false when `u` is past the end.
+__device__ __forceinline__ uint32_t wg_chunks_of(const uint32_t* seg, int v, int kb, int unit_kb) {
+  const uint32_t len = __ldg(&seg[v + 1]) - __ldg(&seg[v]);
+  const uint32_t nk = (len + kb - 1) / kb;
+  return (nk + unit_kb - 1) / unit_kb;
+}
+__device__ bool wg_find_unit(const uint32_t* seg, int V, int kb, int unit_kb, int order, uint32_t u, int* v_out, int* j_out) {
+  if (order == 0) {
+    for (int v = 0; v < V; ++v) {
+      const uint32_t c = wg_chunks_of(seg, v, kb, unit_kb);
+      if (u < c) {
+        *v_out = v, *j_out = static_cast<int>(u);
+        return true;
+      }
+      u -= c;
+    }
+    return false;
+  }
+  for (uint32_t j = 0;; ++j) {
+    uint32_t alive = 0;
+    for (int v = 0; v < V; ++v) {
+      if (wg_chunks_of(seg, v, kb, unit_kb) > j) {
+        if (u == alive) {
+          *v_out = v, *j_out = static_cast<int>(j);
+          return true;
+        }
+        ++alive;
+      }
+    }
+    if (alive == 0) return false;
+    u -= alive;
+  }
+}
+// slab index of unit (v, j): units are stored offset-major whatever the launch order
+__device__ __forceinline__ uint32_t wg_slab_of(const uint32_t* seg, int kb, int unit_kb, int v, int j) {
+  uint32_t base = 0;
+  for (int t = 0; t < v; ++t) base += wg_chunks_of(seg, t, kb, unit_kb);
+  return base + j;
 }
 
 template <int kElem>
@@ -80,148 +119,125 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   WgradSmem* ctl = reinterpret_cast<WgradSmem*>(smem);
-  uint8_t* stages = smem + 2048;
+  uint8_t* stages = smem + 1024;
   const int chunk_bytes = p.kb * 128;
   const int a_bytes = p.a_chunks * chunk_bytes;
   const int stage_bytes = (p.a_chunks + p.b_chunks) * chunk_bytes;
+  const int S = p.stages;
 
-  // A kernel that already reported a soft error makes the rest of the grid a
-  // no-op.  One thread reads the word so that the whole CTA takes the same branch.
-  __shared__ int s_skip;
-  if (threadIdx.x == 0) s_skip = p.status != nullptr && *reinterpret_cast<volatile const int32_t*>(p.status) != 0;
-  __syncthreads();
-  if (s_skip) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // work item
-  // Split-major order: CTAs that run at the same time work on the same slice of
-  // the pair lists of all offsets.  The lists are sorted by output row and a
-  // neighbour's row is close to its voxel's row, so the slice touches a narrow
-  // band of rows of both gathered matrices and that band stays in L2.
+  // work item: (unit, output-channel group, input-channel tile)
   uint32_t bid = blockIdx.x;
   const int ci_tile = bid % p.ci_tiles;
   bid /= p.ci_tiles;
   const int co_group = bid % p.co_groups;
   bid /= p.co_groups;
-  int v, split;
-  if (p.order == 1) {
-    v = bid % p.V;
-    split = bid / p.V;
-  } else {
-    split = bid % p.splitk;
-    v = bid / p.splitk;
+  if (tid == 0) {
+    int v = -1, j = -1;
+    const bool skip = p.status != nullptr && *reinterpret_cast<volatile const int32_t*>(p.status) != 0;
+    if (skip || !wg_find_unit(p.seg, p.V, p.kb, p.unit_kb, p.order, bid, &v, &j)) v = j = -1;
+    ctl->unit_v = v, ctl->unit_j = j;
   }
+  __syncthreads();
+  const int v = ctl->unit_v, unit_j = ctl->unit_j;
+  if (v < 0) return;  // grid is sized for the worst case; also the no-op path after a soft error
   const int co0 = co_group * p.mt * 128;
   const int ci0 = ci_tile * p.bn;
 
   const uint32_t seg_begin = __ldg(&p.seg[v]);
-  const uint32_t seg_len = __ldg(&p.seg[v + 1]) - seg_begin;
-  const uint32_t num_k = (seg_len + p.kb - 1) / p.kb;
-  const uint32_t k_begin = static_cast<uint32_t>((uint64_t(num_k) * split + p.splitk - 1) / p.splitk);
-  const uint32_t k_end = static_cast<uint32_t>((uint64_t(num_k) * (split + 1) + p.splitk - 1) / p.splitk);
-  const int total = static_cast<int>(k_end - k_begin);
-  const uint32_t seg_end = seg_begin + seg_len;
+  const uint32_t seg_end = __ldg(&p.seg[v + 1]);
+  const uint32_t num_k = (seg_end - seg_begin + p.kb - 1) / p.kb;
+  const uint32_t k_begin = static_cast<uint32_t>(unit_j) * p.unit_kb;
+  const uint32_t k_end = min(num_k, k_begin + p.unit_kb);
+  const int total = static_cast<int>(k_end - k_begin);  // >= 1 by construction
   volatile uint32_t* abort_flag = &ctl->abort_flag;
 
   if (tid == 0) {
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&ctl->full[s], 128);  // every gather thread, on completion of its copies
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&ctl->full[s], kWgGatherThreads);  // every gather thread, on completion of its copies
       mbar_init(&ctl->empty[s], 1);
     }
     mbar_init(&ctl->acc_full, 1);
     ctl->abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 5) {
+  if (warp == 4) {
     tmem_alloc_dyn(&ctl->tmem_base, p.tmem_cols);
     tmem_relinquish();
-  }
-  // pair indices of the first stage
-  if (tid < 128 && total > 0) {
-    const int which = tid >> 6, j = tid & 63;
-    if (j < p.kb) {
-      const uint32_t pp = seg_begin + k_begin * p.kb + j;
-      ctl->idx[0][which][j] = pp < seg_end ? __ldg(which ? &p.vs_i[pp] : &p.vs_o[pp]) : kInvalid;
-    }
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  if (warp < 4) {
+  if (warp >= kWgGatherWarp0) {
     // ---------------------------------------------------------------- gather
-    const int piece = lane & 7, sub = lane >> 3;
-    const int nchunks = p.a_chunks + p.b_chunks;
-    const int units = p.kb * nchunks;  // (pair row, 128-byte chunk) units per stage, 4 per warp instruction
+    // Eight lanes move one 128-byte chunk of one pair row; a thread owns rows
+    // g, g+32, ... of every stage and walks over the chunks of both operands.
+    const int piece = lane & 7;
+    const int g = (warp - kWgGatherWarp0) * 4 + (lane >> 3);  // 0..31
+    const int rows_per_thread = p.kb / 32;                     // 2 (16-bit) or 1 (tf32)
     const int a_row_bytes = p.Co * kElem, b_row_bytes = p.Ci * kElem;
-    for (int it = 0; it < total; ++it) {
-      const int s = it % p.stages;
-      const int buf = it & 1;
-      // prefetch the next stage's pair indices into a register
-      uint32_t next_idx = kInvalid;
-      const int which = tid >> 6, j = tid & 63;
-      if (it + 1 < total && j < p.kb) {
-        const uint32_t pp = seg_begin + (k_begin + it + 1) * p.kb + j;
-        if (pp < seg_end) next_idx = __ldg(which ? &p.vs_i[pp] : &p.vs_o[pp]);
+    uint32_t row_off[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int row = g + 32 * j;
+      // 16-bit types: 16-byte pieces swizzled by (row & 7); tf32: 32-byte pieces swizzled by (row & 3)
+      const int swz = kElem == 2 ? ((piece ^ (row & 7)) << 4) : (((((piece >> 1) ^ (row & 3)) << 1) | (piece & 1)) << 4);
+      row_off[j] = row * 128 + swz;
+    }
+    auto load_pairs = [&](uint32_t kblk, uint32_t (&io)[2], uint32_t (&ii)[2]) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint32_t pp = seg_begin + kblk * p.kb + g + 32 * j;
+        const bool ok = j < rows_per_thread && pp < seg_end;
+        io[j] = ok ? __ldg(&p.vs_o[pp]) : kInvalid;
+        ii[j] = ok ? __ldg(&p.vs_i[pp]) : kInvalid;
       }
-      mbar_wait(&ctl->empty[s], ((it / p.stages) & 1) ^ 1, abort_flag);
+    };
+    uint32_t io[2], ii[2], nio[2], nii[2];
+    load_pairs(k_begin, nio, nii);
+    for (int it = 0; it < total; ++it) {
+      const int s = it % S;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) io[j] = nio[j], ii[j] = nii[j];
+      if (it + 1 < total) load_pairs(k_begin + it + 1, nio, nii);  // one stage ahead
+      const char* srca[2];
+      const char* srcb[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        srca[j] = p.gout + size_t(io[j] != kInvalid ? io[j] : 0u) * a_row_bytes + co0 * kElem + piece * 16;
+        srcb[j] = p.x + size_t(ii[j] != kInvalid ? ii[j] : 0u) * b_row_bytes + ci0 * kElem + piece * 16;
+      }
+      mbar_wait(&ctl->empty[s], ((it / S) & 1) ^ 1, abort_flag);
       const uint32_t st_base = smem_u32(stages + size_t(s) * stage_bytes);
-      for (int u = warp * 4 + sub; u < units; u += 16) {
-        const int row = u / nchunks, chunk = u - row * nchunks;
-        const bool is_b = chunk >= p.a_chunks;
-        const int c = is_b ? chunk - p.a_chunks : chunk;
-        const uint32_t gidx = ctl->idx[buf][is_b ? 1 : 0][row];
-        const int col_bytes = (is_b ? ci0 * kElem : co0 * kElem) + c * 128 + piece * 16;
-        const bool ok = gidx != kInvalid && col_bytes < (is_b ? b_row_bytes : a_row_bytes);
-        const char* base = is_b ? p.x : p.gout;
-        const char* src = ok ? base + size_t(gidx) * (is_b ? b_row_bytes : a_row_bytes) + col_bytes : base;
-        // 16-bit types: 16-byte pieces swizzled by (row & 7); tf32: 32-byte pieces swizzled by (row & 3)
-        const int swz = kElem == 2 ? ((piece ^ (row & 7)) << 4) : (((((piece >> 1) ^ (row & 3)) << 1) | (piece & 1)) << 4);
-        const uint32_t dst = st_base + (is_b ? a_bytes : 0) + c * chunk_bytes + row * 128 + swz;
-        cp_async_16(dst, src, ok ? 16u : 0u);
+      for (int c = 0; c < p.a_chunks; ++c) {
+        const bool col_ok = co0 * kElem + c * 128 + piece * 16 < a_row_bytes;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          if (j < rows_per_thread)
+            cp_async_16(st_base + c * chunk_bytes + row_off[j], srca[j] + c * 128, (col_ok && io[j] != kInvalid) ? 16u : 0u);
+      }
+      for (int c = 0; c < p.b_chunks; ++c) {
+        const bool col_ok = ci0 * kElem + c * 128 + piece * 16 < b_row_bytes;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          if (j < rows_per_thread)
+            cp_async_16(st_base + a_bytes + c * chunk_bytes + row_off[j], srcb[j] + c * 128, (col_ok && ii[j] != kInvalid) ? 16u : 0u);
       }
       cp_async_arrive(&ctl->full[s]);
-      if (j < p.kb) ctl->idx[buf ^ 1][which][j] = next_idx;
-      named_barrier_sync(1, 128);
     }
-
-    // -------------------------------------------------------------- epilogue
-    if (total > 0) mbar_wait(&ctl->acc_full, 0, abort_flag);
-    tc_fence_after_sync();
-    for (int mt = 0; mt < p.mt; ++mt) {
-      const int co = co0 + mt * 128 + warp * 32 + lane;
-      float* orow = p.partial + ((size_t(split) * p.Co + co) * p.V + v) * p.Ci;
-      for (int c0 = 0; c0 < p.bn; c0 += 32) {
-        uint32_t acc[32];
-        if (total > 0) {
-          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + mt * p.bn + c0, acc);
-          tmem_ld_wait();
-        }
-        if (co < p.Co) {
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const int ci = ci0 + c0 + g * 4;
-            if (ci < p.Ci) {
-              float4 o = total > 0 ? make_float4(__uint_as_float(acc[g * 4]), __uint_as_float(acc[g * 4 + 1]),
-                                                 __uint_as_float(acc[g * 4 + 2]), __uint_as_float(acc[g * 4 + 3]))
-                                   : make_float4(0.f, 0.f, 0.f, 0.f);
-              *reinterpret_cast<float4*>(orow + ci) = o;
-            }
-          }
-        }
-      }
-    }
-  } else if (warp == 5) {
+  } else if (warp == 4) {
     // ------------------------------------------------------------------- MMA
     if (lane == 0) {
       uint32_t accumulate = 0;
+      const int chunks_per_m = 128 / kChunkElems;  // 128-byte chunks per 128 accumulator rows
       for (int it = 0; it < total; ++it) {
-        const int s = it % p.stages;
-        mbar_wait(&ctl->full[s], (it / p.stages) & 1, abort_flag);
+        const int s = it % S;
+        mbar_wait(&ctl->full[s], (it / S) & 1, abort_flag);
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(stages + size_t(s) * stage_bytes);
         const uint32_t b_addr = a_addr + a_bytes;
-        const int chunks_per_m = 128 / kChunkElems;  // 128-byte chunks per 128 accumulator rows
         for (int ks = 0; ks < p.kb / kUmmaK; ++ks) {
           const uint32_t koff = ks * kUmmaK * 128;  // kUmmaK pair rows of 128 bytes
           const uint64_t db = make_smem_desc(b_addr + koff, chunk_bytes, kSbo, kLayout);
@@ -233,37 +249,66 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
         }
         umma_commit(&ctl->empty[s]);
       }
-      if (total > 0) umma_commit(&ctl->acc_full);
+      umma_commit(&ctl->acc_full);
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue
+    const uint32_t slab = wg_slab_of(p.seg, p.kb, p.unit_kb, v, unit_j);
+    mbar_wait(&ctl->acc_full, 0, abort_flag);
+    tc_fence_after_sync();
+    for (int mt = 0; mt < p.mt; ++mt) {
+      const int co = co0 + mt * 128 + warp * 32 + lane;
+      float* orow = p.partial + (size_t(slab) * p.Co + co) * p.Ci;
+      for (int c0 = 0; c0 < p.bn; c0 += 32) {
+        uint32_t acc[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + mt * p.bn + c0, acc);
+        tmem_ld_wait();
+        if (co < p.Co) {
+#pragma unroll
+          for (int g4 = 0; g4 < 8; ++g4) {
+            const int ci = ci0 + c0 + g4 * 4;
+            if (ci < p.Ci)
+              *reinterpret_cast<float4*>(orow + ci) = make_float4(__uint_as_float(acc[g4 * 4]), __uint_as_float(acc[g4 * 4 + 1]),
+                                                                  __uint_as_float(acc[g4 * 4 + 2]), __uint_as_float(acc[g4 * 4 + 3]));
+          }
+        }
+      }
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 4) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
   if (tid == 0 && ctl->abort_flag) report(p.status, FGB_S_WAIT_TIMEOUT);
 }
 
-// out[e] = sum_s partial[s][e], written as dtype and/or fp32
+// out[co, v, ci] = sum over the slabs of offset v, in slab order; written as dtype and/or fp32
 template <typename T>
-__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, int splitk, int64_t count,
-                                                            T* __restrict__ out, float* __restrict__ out_f32) {
-  const int64_t i = (blockIdx.x * int64_t(256) + threadIdx.x) * 4;
-  if (i >= count) return;
-  float4 acc = __ldg(reinterpret_cast<const float4*>(partial + i));
-  for (int s = 1; s < splitk; ++s) {
-    const float4 t = __ldg(reinterpret_cast<const float4*>(partial + int64_t(s) * count + i));
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, const uint32_t* __restrict__ seg, int kb,
+                                                            int unit_kb, int Co, int V, int Ci, T* __restrict__ out,
+                                                            float* __restrict__ out_f32) {
+  const int v = blockIdx.y;
+  const int64_t e = (blockIdx.x * int64_t(256) + threadIdx.x) * 4;  // element of the [Co, Ci] slab
+  if (e >= int64_t(Co) * Ci) return;
+  const uint32_t first = wg_slab_of(seg, kb, unit_kb, v, 0);
+  const uint32_t count = wg_chunks_of(seg, v, kb, unit_kb);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (uint32_t s = 0; s < count; ++s) {
+    const float4 t = __ldg(reinterpret_cast<const float4*>(partial + (size_t(first) + s) * Co * Ci + e));
     acc.x += t.x, acc.y += t.y, acc.z += t.z, acc.w += t.w;
   }
-  if (out_f32) *reinterpret_cast<float4*>(out_f32 + i) = acc;
+  const int co = static_cast<int>(e / Ci), ci = static_cast<int>(e % Ci);
+  const int64_t o = (int64_t(co) * V + v) * Ci + ci;
+  if (out_f32) *reinterpret_cast<float4*>(out_f32 + o) = acc;
   if (out) {
     if constexpr (std::is_same<T, float>::value) {
-      *reinterpret_cast<float4*>(out + i) = acc;
+      *reinterpret_cast<float4*>(out + o) = acc;
     } else {
-      T o[4] = {static_cast<T>(acc.x), static_cast<T>(acc.y), static_cast<T>(acc.z), static_cast<T>(acc.w)};
-      *reinterpret_cast<uint2*>(out + i) = *reinterpret_cast<uint2*>(o);
+      T t4[4] = {static_cast<T>(acc.x), static_cast<T>(acc.y), static_cast<T>(acc.z), static_cast<T>(acc.w)};
+      *reinterpret_cast<uint2*>(out + o) = *reinterpret_cast<uint2*>(t4);
     }
   }
 }
@@ -357,15 +402,24 @@ static WgradPlan plan_wgrad(int Ci, int Co, int eb) {
   w.a_chunks = w.mt * 128 * eb / 128;
   w.b_chunks = static_cast<int>(ceil_div(w.bn * eb, 128));
   const size_t stage = size_t(w.a_chunks + w.b_chunks) * w.kb * 128;
-  const size_t budget = 200 * 1024;
+  const size_t budget = 224 * 1024;
   w.stages = static_cast<int>(budget / stage);
   if (w.stages > kWgMaxStages) w.stages = kWgMaxStages;
   if (w.stages < 2) w.stages = 2;
   uint32_t cols = 32;
   while (cols < uint32_t(w.mt * w.bn)) cols <<= 1;
   w.tmem_cols = cols;
-  w.smem = 1024 + 2048 + stage * w.stages;
+  w.smem = 1024 + 1024 + stage * w.stages;
   return w;
+}
+
+// k-blocks per unit and the worst-case unit count for `splitk` parts per offset on average
+static void unit_plan(int64_t n_pairs, int V, int kb, int splitk, int* unit_kb, int64_t* max_units) {
+  const int64_t nk_total = ceil_div(n_pairs, kb) + V;  // every offset rounds up
+  int64_t ukb = ceil_div(nk_total, int64_t(splitk) * V);
+  if (ukb < 1) ukb = 1;
+  *unit_kb = static_cast<int>(ukb);
+  *max_units = nk_total / ukb + V;
 }
 
 }  // namespace fgb
@@ -379,7 +433,9 @@ extern "C" int fgb_wgrad_default_splitk(int64_t n_pairs, int Ci, int Co, int V, 
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t base = int64_t(V) * w.co_groups * w.ci_tiles;
-  int64_t s = ceil_div(int64_t(3) * sms, base);
+  // about two CTAs per SM in total: measured best on B200 (fewer leaves SMs idle in the
+  // second wave, more adds partial slabs without shortening the critical path)
+  int64_t s = (int64_t(2) * sms) / base;
   // no more splits than stages of pairs per offset on average
   const int64_t max_s = n_pairs > 0 ? ceil_div(ceil_div(n_pairs, V), w.kb) : 1;
   if (s > max_s) s = max_s;
@@ -401,7 +457,7 @@ extern "C" int64_t fgb_conv_workspace_bytes(int pass, int Ci, int Co, int V, int
       return w_elems * eb;
     case 2:
       if (splitk < 1 || splitk > 1024) return FGB_E_SIZE;
-      return w_elems * 4 * splitk;
+      return w_elems * 4 * (int64_t(splitk) + 1);  // slabs [Co, Ci] for up to (splitk + 1) * V units
     default:
       return FGB_E_SIZE;
   }
@@ -409,20 +465,20 @@ extern "C" int64_t fgb_conv_workspace_bytes(int pass, int Ci, int Co, int V, int
 
 extern "C" int fgb_subm_conv_wgrad(const void* grad_out, const void* feats, const uint32_t* valid_signal_i,
                                    const uint32_t* valid_signal_o, const uint32_t* valid_signal_seg, void* grad_weight,
-                                   float* grad_weight_f32, int64_t n, int Ci, int Co, int V, int dtype, int splitk,
+                                   float* grad_weight_f32, int64_t n, int64_t n_pairs, int Ci, int Co, int V, int dtype, int splitk,
                                    void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
   using namespace fgb;
   const int eb = elem_bytes(dtype);
   if (eb == 0 || dtype == FGB_F32_IEEE) return FGB_E_DTYPE;
-  if (n < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32 || splitk < 1 || splitk > 1024) return FGB_E_SIZE;
+  if (n < 0 || n_pairs < 0 || n_pairs > n * V || Ci <= 0 || Co <= 0 || V < 1 || V > 32 || splitk < 1 || splitk > 1024) return FGB_E_SIZE;
   if ((Ci * eb) % 16 || (Co * eb) % 16) return FGB_E_ALIGN;
   if (!valid_signal_seg || !workspace) return FGB_E_NULL;
-  if (n > 0 && (!grad_out || !feats || !valid_signal_i || !valid_signal_o)) return FGB_E_NULL;
+  if (n_pairs > 0 && (!grad_out || !feats || !valid_signal_i || !valid_signal_o)) return FGB_E_NULL;
   if ((reinterpret_cast<uintptr_t>(grad_out) | reinterpret_cast<uintptr_t>(feats) | reinterpret_cast<uintptr_t>(workspace) |
        reinterpret_cast<uintptr_t>(grad_weight) | reinterpret_cast<uintptr_t>(grad_weight_f32)) & 15)
     return FGB_E_ALIGN;
-  const int64_t count = int64_t(Co) * V * Ci;
-  if (workspace_bytes < count * 4 * splitk) return FGB_E_WORKSPACE;
+  const int64_t need = fgb_conv_workspace_bytes(2, Ci, Co, V, dtype, splitk);
+  if (workspace_bytes < need) return FGB_E_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const WgradPlan w = plan_wgrad(Ci, Co, eb);
   WgradParams p;
@@ -432,7 +488,9 @@ extern "C" int fgb_subm_conv_wgrad(const void* grad_out, const void* feats, cons
   p.vs_o = valid_signal_o;
   p.seg = valid_signal_seg;
   p.partial = static_cast<float*>(workspace);
-  p.Co = Co, p.Ci = Ci, p.V = V, p.splitk = splitk;
+  p.Co = Co, p.Ci = Ci, p.V = V;
+  int64_t max_units = 0;
+  unit_plan(n_pairs, V, w.kb, splitk, &p.unit_kb, &max_units);
   p.mt = w.mt, p.bn = w.bn, p.co_groups = w.co_groups, p.ci_tiles = w.ci_tiles;
   p.kb = w.kb, p.stages = w.stages, p.a_chunks = w.a_chunks, p.b_chunks = w.b_chunks;
   const uint32_t fmt = dtype == FGB_F16 ? kFmtF16 : dtype == FGB_BF16 ? kFmtBF16 : kFmtTF32;
@@ -443,7 +501,8 @@ extern "C" int fgb_subm_conv_wgrad(const void* grad_out, const void* feats, cons
     p.order = e ? atoi(e) : 0;
   }
   p.status = status;
-  const int64_t grid = int64_t(V) * splitk * w.co_groups * w.ci_tiles;
+  const int64_t grid = max_units * w.co_groups * w.ci_tiles;
+  if (grid > 0x7FFFFFFF) return FGB_E_SIZE;
   cudaError_t e;
   if (eb == 2) {
     e = cudaFuncSetAttribute(subm_wgrad_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(w.smem));
@@ -456,16 +515,16 @@ extern "C" int fgb_subm_conv_wgrad(const void* grad_out, const void* feats, cons
   }
   int rc = launch_status();
   if (rc != FGB_OK) return rc;
-  const unsigned rblocks = static_cast<unsigned>(ceil_div(count, 1024));
+  const dim3 rgrid(static_cast<unsigned>(ceil_div(int64_t(Co) * Ci, 1024)), static_cast<unsigned>(V));
   switch (dtype) {
     case FGB_F16:
-      splitk_reduce_kernel<__half><<<rblocks, 256, 0, s>>>(p.partial, splitk, count, static_cast<__half*>(grad_weight), grad_weight_f32);
+      splitk_reduce_kernel<__half><<<rgrid, 256, 0, s>>>(p.partial, p.seg, p.kb, p.unit_kb, Co, V, Ci, static_cast<__half*>(grad_weight), grad_weight_f32);
       break;
     case FGB_BF16:
-      splitk_reduce_kernel<__nv_bfloat16><<<rblocks, 256, 0, s>>>(p.partial, splitk, count, static_cast<__nv_bfloat16*>(grad_weight), grad_weight_f32);
+      splitk_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, s>>>(p.partial, p.seg, p.kb, p.unit_kb, Co, V, Ci, static_cast<__nv_bfloat16*>(grad_weight), grad_weight_f32);
       break;
     default:
-      splitk_reduce_kernel<float><<<rblocks, 256, 0, s>>>(p.partial, splitk, count, static_cast<float*>(grad_weight), grad_weight_f32);
+      splitk_reduce_kernel<float><<<rgrid, 256, 0, s>>>(p.partial, p.seg, p.kb, p.unit_kb, Co, V, Ci, static_cast<float*>(grad_weight), grad_weight_f32);
   }
   return launch_status();
 }

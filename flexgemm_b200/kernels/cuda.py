@@ -241,7 +241,7 @@ def conv_wgrad(grad_out, feats, vs_i, vs_o, vs_seg, splitk: Optional[int] = None
     nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(2, Ci, Co, V, code, splitk), "fgb_conv_workspace_bytes")
     ws = workspace(dev, "wgrad", nbytes)
     rc = lib.fgb_subm_conv_wgrad(_ptr(grad_out), _ptr(feats), _ptr(vs_i), _ptr(vs_o), vs_seg.data_ptr(), _ptr(gw), _ptr(gw32),
-                                 n, Ci, Co, V, code, int(splitk), ws.data_ptr(), ws.numel() * 8,
+                                 n, int(vs_i.shape[0]), Ci, Co, V, code, int(splitk), ws.data_ptr(), ws.numel() * 8,
                                  status_word(dev).data_ptr(), _stream(dev))
     _cabi.check(rc, "fgb_subm_conv_wgrad")
     _count(2)

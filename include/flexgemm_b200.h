@@ -176,17 +176,20 @@ int fgb_wgrad_default_splitk(int64_t n_pairs, int Ci, int Co, int V, int dtype);
 
 /* grad_weight[co, v, ci] = sum_{p in segment v} grad_out[valid_signal_o[p], co]
  *                                              * feats[valid_signal_i[p], ci]
- * Each offset's pair range is cut into `splitk` parts whose fp32 partial sums
- * go to the workspace and are then added up in a fixed order (deterministic).
- * grad_weight (element type `dtype`) and/or grad_weight_f32 may be null; the
- * fp32 copy is what a multi-GPU caller hands to its all-reduce.
+ * The pair lists are cut into units of equal length (about `splitk` per offset
+ * on average; an offset with more pairs gets more units); each unit's fp32
+ * partial [Co, Ci] goes to the workspace and the partials of an offset are then
+ * added in a fixed order (deterministic).  n_pairs is the length of the pair
+ * lists (valid_signal_seg[V]).  grad_weight (element type `dtype`) and/or
+ * grad_weight_f32 may be null; the fp32 copy is what a multi-GPU caller hands
+ * to its all-reduce.
  * Stands in for sparse_submanifold_conv_bwd_weight_masked_implicit_gemm_splitk
  * (…/sparse_submanifold_conv_bwd_masked_implicit_gemm_splitk.py:107-182, 274-317). */
 int fgb_subm_conv_wgrad(const void* grad_out, const void* feats,
                         const uint32_t* valid_signal_i, const uint32_t* valid_signal_o,
                         const uint32_t* valid_signal_seg,
                         void* grad_weight, float* grad_weight_f32,
-                        int64_t n, int Ci, int Co, int V, int dtype, int splitk,
+                        int64_t n, int64_t n_pairs, int Ci, int Co, int V, int dtype, int splitk,
                         void* workspace, int64_t workspace_bytes,
                         int32_t* status, void* stream);
 

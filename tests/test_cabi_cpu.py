@@ -47,7 +47,7 @@ def test_size_queries(lib):
     assert lib.fgb_conv_tile_rows() == 128
     assert lib.fgb_conv_workspace_bytes(0, 64, 64, 27, _cabi.F16, 1) == 0
     assert lib.fgb_conv_workspace_bytes(1, 64, 32, 27, _cabi.F16, 1) == 64 * 32 * 27 * 2
-    assert lib.fgb_conv_workspace_bytes(2, 64, 32, 27, _cabi.F16, 4) == 64 * 32 * 27 * 4 * 4
+    assert lib.fgb_conv_workspace_bytes(2, 64, 32, 27, _cabi.F16, 4) == 64 * 32 * 27 * 4 * 5
     assert lib.fgb_conv_workspace_bytes(2, 64, 32, 27, 9, 4) < 0
     assert lib.fgb_bias_grad_workspace_bytes(256) > 0
 
@@ -63,7 +63,7 @@ def test_argument_validation_without_launch(lib):
     assert lib.fgb_subm_conv_fprop(0, 0, 0, 0, 0, 0, 0, 10, 64, 64, 27, _cabi.F16, 0, 0, 0, 0) == -1
     assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 16, 10, 60, 64, 27, _cabi.F16, 0, 0, 0, 0) == -4  # Ci % 8
     assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 16, 10, 64, 64, 27, 7, 0, 0, 0, 0) == -3
-    assert lib.fgb_subm_conv_wgrad(16, 16, 16, 16, 16, 16, 0, 10, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -5  # workspace
+    assert lib.fgb_subm_conv_wgrad(16, 16, 16, 16, 16, 16, 0, 10, 100, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -5  # workspace
 
 
 def test_python_surface_matches_reference_names():
