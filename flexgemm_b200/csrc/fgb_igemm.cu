@@ -57,6 +57,7 @@ struct IgemmParams {
   const uint32_t* nbr;       // [n, V]
   const int64_t* sorted_idx; // [n]
   const uint32_t* tile_masks; // one mask per 128 sorted rows
+  const uint32_t* block_order; // row blocks in descending cost order, or null for natural order
   char* out;                 // [n, nout]
   uint32_t n;
   uint32_t num_tiles;        // ceil(n / 128)
@@ -176,6 +177,18 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
 
   // Every role walks the same sequence: work item w -> (row block, column tile);
   // within it the offsets of the union mask in ascending order, num_kb slices each.
+  // Work item of this CTA in pass i.  Items are dealt to the CTAs in a
+  // boustrophedon over the cost-sorted list (pass 0: CTA c takes item c, pass 1:
+  // item 2G-1-c, ...), which evens out the total cost per CTA.
+  auto work_of = [&](uint32_t pass, uint32_t& mblk, uint32_t& ntile) -> bool {
+    const uint32_t G = gridDim.x;
+    const uint32_t w = pass * G + ((pass & 1u) ? G - 1u - blockIdx.x : blockIdx.x);
+    if (w >= p.num_work) return false;
+    const uint32_t b = w / p.n_tiles_n;
+    ntile = w - b * p.n_tiles_n;
+    mblk = p.block_order != nullptr ? __ldg(&p.block_order[b]) : b;
+    return true;
+  };
   auto masks_of = [&](uint32_t mblk, uint32_t& m0, uint32_t& m1) {
     const uint32_t t0 = mblk * 2;
     m0 = __ldg(&p.tile_masks[t0]);
@@ -209,21 +222,20 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
       }
     };
     uint32_t it = 0;
-    uint32_t w = blockIdx.x;
     uint32_t rows[8], nrows[8], idx[8], nidx[8];
     uint32_t m0 = 0, m1 = 0, nm0 = 0, nm1 = 0;
-    if (w < p.num_work) {
-      const uint32_t mblk = w / p.n_tiles_n;
+    uint32_t mblk = 0, ntile = 0;
+    bool has_work = work_of(0, mblk, ntile);
+    if (has_work) {
       masks_of(mblk, m0, m1);
       load_rows(mblk, rows);
       if (m0 | m1) load_idx(rows, __ffs(m0 | m1) - 1, m0, m1, nidx);
     }
-    for (; w < p.num_work; w += gridDim.x) {
+    for (uint32_t pass = 0; has_work; ++pass) {
       // rows and masks of the next work item, fetched a whole block ahead
-      const uint32_t wn = w + gridDim.x;
-      const bool has_next = wn < p.num_work;
+      uint32_t mblk_n = 0, ntile_n = 0;
+      const bool has_next = work_of(pass + 1, mblk_n, ntile_n);
       if (has_next) {
-        const uint32_t mblk_n = wn / p.n_tiles_n;
         masks_of(mblk_n, nm0, nm1);
         load_rows(mblk_n, nrows);
       }
@@ -261,14 +273,15 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
       m0 = nm0, m1 = nm1;
 #pragma unroll
       for (int j = 0; j < 8; ++j) rows[j] = nrows[j];
+      has_work = has_next;
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------ weight TMA
     if (lane == 0 && !(p.debug & 16)) {
       uint32_t it = 0;
-      for (uint32_t w = blockIdx.x; w < p.num_work; w += gridDim.x) {
-        const uint32_t mblk = w / p.n_tiles_n;
-        const int n0 = static_cast<int>(w % p.n_tiles_n) * p.bn;
+      uint32_t mblk = 0, ntile = 0;
+      for (uint32_t pass = 0; work_of(pass, mblk, ntile); ++pass) {
+        const int n0 = static_cast<int>(ntile) * p.bn;
         uint32_t m0, m1;
         masks_of(mblk, m0, m1);
         uint32_t un = m0 | m1;
@@ -294,8 +307,9 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     if (lane == 0) {
       uint32_t it = 0, item = 0;
       unsigned long long t_acc = 0, t_full = 0, t_all = global_timer_ns(), n_it = 0;
-      for (uint32_t w = blockIdx.x; w < p.num_work; w += gridDim.x, ++item) {
-        const uint32_t mblk = w / p.n_tiles_n;
+      const long long c_all = clock64();
+      uint32_t mblk = 0, ntile = 0;
+      for (; work_of(item, mblk, ntile); ++item) {
         uint32_t m0, m1;
         masks_of(mblk, m0, m1);
         const uint32_t set = item % p.acc_sets;
@@ -343,7 +357,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
         p.dbg[blockIdx.x * 4 + 0] = global_timer_ns() - t_all;
         p.dbg[blockIdx.x * 4 + 1] = t_acc;
         p.dbg[blockIdx.x * 4 + 2] = t_full;
-        p.dbg[blockIdx.x * 4 + 3] = n_it;
+        p.dbg[blockIdx.x * 4 + 3] = static_cast<unsigned long long>(clock64() - c_all);
       }
     }
   } else {
@@ -356,9 +370,9 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     constexpr int kColsPerPass = 4096 / 32 / kElem;  // 64 columns of 16-bit, 32 columns of fp32: 128 bytes per row
     constexpr int kChunksPerPass = kColsPerPass / 32 > 0 ? kColsPerPass / 32 : 1;
     uint32_t item = 0;
-    for (uint32_t w = blockIdx.x; w < p.num_work; w += gridDim.x, ++item) {
-      const uint32_t mblk = w / p.n_tiles_n;
-      const int n0 = static_cast<int>(w % p.n_tiles_n) * p.bn;
+    uint32_t mblk = 0, ntile = 0;
+    for (; work_of(item, mblk, ntile); ++item) {
+      const int n0 = static_cast<int>(ntile) * p.bn;
       uint32_t m0, m1;
       masks_of(mblk, m0, m1);
       const uint32_t set = item % p.acc_sets;
@@ -375,15 +389,15 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
         const bool has_acc = (h == 0 ? m0 : m1) != 0u;  // a half without offsets holds no rows
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + set * 2 * p.bn + h * p.bn;
         for (int c0 = 0; c0 < p.bn; c0 += kColsPerPass) {
+          uint32_t acc[kChunksPerPass][32];
+          if (has_acc && !(p.debug & 32)) {
 #pragma unroll
-          for (int cc = 0; cc < kChunksPerPass; ++cc) {
-            uint32_t acc[32];
-            if (has_acc && !(p.debug & 32)) {
-              tmem_ld_32x32(t_addr + c0 + cc * 32, acc);
-              tmem_ld_wait();
-            }
-            if (!(p.debug & 64)) stage_row_chunk<kDtype>(stage_out, lane, cc, acc, p.bias, n0 + c0 + cc * 32, p.nout, !has_acc);
+            for (int cc = 0; cc < kChunksPerPass; ++cc) tmem_ld_32x32(t_addr + c0 + cc * 32, acc[cc]);
+            tmem_ld_wait();
           }
+#pragma unroll
+          for (int cc = 0; cc < kChunksPerPass; ++cc)
+            if (!(p.debug & 64)) stage_row_chunk<kDtype>(stage_out, lane, cc, acc[cc], p.bias, n0 + c0 + cc * 32, p.nout, !has_acc);
           __syncwarp();
           if (!(p.debug & 8)) {
             // 128 bytes per row: lane -> (row = 4 i + lane / 8, piece = lane % 8)
@@ -414,6 +428,35 @@ done:
     tmem_dealloc(tmem_base, 512u);
   }
   if (tid == 0 && ctl->abort_flag) report(p.status, FGB_S_WAIT_TIMEOUT);
+}
+
+// ------------------------------------------------------------------ block schedule
+// order[] = row blocks (pairs of 128-row tiles) sorted by descending cost, the
+// cost of a block being the number of (tile, offset) products it runs.  One CTA;
+// a counting sort over the 65 possible costs.  Blocks of equal cost may come out
+// in any order: the order only decides which SM computes a block, never a result.
+__global__ void __launch_bounds__(1024) block_schedule_kernel(const uint32_t* __restrict__ masks, uint32_t num_tiles, uint32_t nb,
+                                                              uint32_t* __restrict__ order) {
+  __shared__ uint32_t s_count[65];
+  __shared__ uint32_t s_start[65];
+  const int t = threadIdx.x;
+  if (t < 65) s_count[t] = 0;
+  __syncthreads();
+  auto cost_of = [&](uint32_t b) {
+    const uint32_t t0 = 2 * b;
+    return __popc(__ldg(&masks[t0])) + (t0 + 1 < num_tiles ? __popc(__ldg(&masks[t0 + 1])) : 0);
+  };
+  for (uint32_t b = t; b < nb; b += 1024) atomicAdd(&s_count[cost_of(b)], 1u);
+  __syncthreads();
+  if (t == 0) {
+    uint32_t acc = 0;
+    for (int c = 64; c >= 0; --c) {
+      s_start[c] = acc;
+      acc += s_count[c];
+    }
+  }
+  __syncthreads();
+  for (uint32_t b = t; b < nb; b += 1024) order[atomicAdd(&s_start[cost_of(b)], 1u)] = b;
 }
 
 // ------------------------------------------------------------------ weight re-layout for dgrad
@@ -500,7 +543,7 @@ static int launch_igemm(const CUtensorMap& tmap, const IgemmParams& p, cudaStrea
 static unsigned long long* g_dbg_buffer = nullptr;
 // x [n, kc] gathered through nbr; w [nout, V, kc]; out [n, nout]
 int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nbr, const int64_t* sorted_idx,
-              const uint32_t* tile_masks, void* out, int64_t n, int kc, int nout, int V, int dtype, int flip, int32_t* status,
+              const uint32_t* tile_masks, const uint32_t* block_order, void* out, int64_t n, int kc, int nout, int V, int dtype, int flip, int32_t* status,
               cudaStream_t s) {
   const int eb = elem_bytes(dtype);
   if (eb == 0 || dtype == FGB_F32_IEEE) return FGB_E_DTYPE;
@@ -517,6 +560,7 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   p.nbr = nbr;
   p.sorted_idx = sorted_idx;
   p.tile_masks = tile_masks;
+  p.block_order = block_order;
   p.out = static_cast<char*>(out);
   p.n = static_cast<uint32_t>(n);
   p.kc = kc;
@@ -561,19 +605,30 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
 extern "C" int fgb_conv_tile_rows(void) { return fgb::kTileM; }
 extern "C" void fgb_debug_set_buffer(void* p) { fgb::g_dbg_buffer = static_cast<unsigned long long*>(p); }
 
+extern "C" int fgb_conv_block_schedule(const uint32_t* tile_masks, int64_t num_tiles, uint32_t* block_order, void* stream) {
+  using namespace fgb;
+  if (num_tiles < 0 || num_tiles > 0x7FFFFFFF) return FGB_E_SIZE;
+  if (num_tiles == 0) return FGB_OK;
+  if (!tile_masks || !block_order) return FGB_E_NULL;
+  const uint32_t nb = static_cast<uint32_t>(ceil_div(num_tiles, 2));
+  block_schedule_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(tile_masks, static_cast<uint32_t>(num_tiles), nb, block_order);
+  return launch_status();
+}
+
 extern "C" int fgb_subm_conv_fprop(const void* feats, const void* weight, const void* bias, const uint32_t* neighbor_map,
-                                   const int64_t* sorted_idx, const uint32_t* tile_masks, void* out, int64_t n, int Ci, int Co,
-                                   int V, int dtype, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+                                   const int64_t* sorted_idx, const uint32_t* tile_masks, const uint32_t* block_order, void* out,
+                                   int64_t n, int Ci, int Co, int V, int dtype, void* workspace, int64_t workspace_bytes,
+                                   int32_t* status, void* stream) {
   (void)workspace;
   (void)workspace_bytes;
-  return fgb::run_igemm(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, out, n, Ci, Co, V, dtype, 0, status,
+  return fgb::run_igemm(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, out, n, Ci, Co, V, dtype, 0, status,
                         static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int fgb_subm_conv_dgrad(const void* grad_out, const void* weight, const uint32_t* neighbor_map,
-                                   const int64_t* sorted_idx, const uint32_t* tile_masks, void* grad_feats, int64_t n, int Ci,
-                                   int Co, int V, int dtype, void* workspace, int64_t workspace_bytes, int32_t* status,
-                                   void* stream) {
+                                   const int64_t* sorted_idx, const uint32_t* tile_masks, const uint32_t* block_order,
+                                   void* grad_feats, int64_t n, int Ci, int Co, int V, int dtype, void* workspace,
+                                   int64_t workspace_bytes, int32_t* status, void* stream) {
   using namespace fgb;
   const int eb = elem_bytes(dtype);
   if (eb == 0) return FGB_E_DTYPE;
@@ -590,5 +645,6 @@ extern "C" int fgb_subm_conv_dgrad(const void* grad_out, const void* weight, con
     weight_transpose_kernel<uint32_t><<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(weight), static_cast<uint32_t*>(workspace), Co, V, Ci);
   int rc = launch_status();
   if (rc != FGB_OK) return rc;
-  return run_igemm(grad_out, workspace, nullptr, neighbor_map, sorted_idx, tile_masks, grad_feats, n, Co, Ci, V, dtype, 1, status, s);
+  return run_igemm(grad_out, workspace, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, grad_feats, n, Co, Ci, V, dtype, 1,
+                   status, s);
 }

@@ -164,6 +164,17 @@ def tile_masks(gray_code: torch.Tensor, sorted_idx: torch.Tensor, block: int) ->
     return out
 
 
+def block_schedule(masks: torch.Tensor) -> torch.Tensor:
+    """256-row blocks in descending order of work, for the persistent conv kernels."""
+    dev = masks.device
+    nt = masks.shape[0]
+    out = torch.empty(max((nt + 1) // 2, 1), dtype=torch.uint32, device=dev)
+    rc = _cabi.lib().fgb_conv_block_schedule(_ptr(masks), nt, out.data_ptr(), _stream(dev))
+    _cabi.check(rc, "fgb_conv_block_schedule")
+    _count(1)
+    return out
+
+
 def valid_kernel(masks: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """List form of the tile masks: (valid_kernel int32 [sum popcount],
     valid_kernel_seg int32 [nblk+1]).  Synchronises once to size the list, as
@@ -187,7 +198,7 @@ def conv_tile_rows() -> int:
     return int(_cabi.lib().fgb_conv_tile_rows())
 
 
-def conv_fprop(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks) -> torch.Tensor:
+def conv_fprop(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks, order=None) -> torch.Tensor:
     """feats [N,Ci], weight_cvc [Co,V,Ci] -> out [N,Co]."""
     lib = _cabi.lib()
     dev = feats.device
@@ -198,14 +209,14 @@ def conv_fprop(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks) -> torc
     nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(0, Ci, Co, V, code, 1), "fgb_conv_workspace_bytes")
     ws = workspace(dev, "fprop", nbytes) if nbytes else None
     rc = lib.fgb_subm_conv_fprop(_ptr(feats), weight_cvc.data_ptr(), _ptr(bias), _ptr(neighbor_map), _ptr(sorted_idx),
-                                 _ptr(masks), _ptr(out), n, Ci, Co, V, code, _ptr(ws), ws.numel() * 8 if ws is not None else 0,
+                                 _ptr(masks), _ptr(order), _ptr(out), n, Ci, Co, V, code, _ptr(ws), ws.numel() * 8 if ws is not None else 0,
                                  status_word(dev).data_ptr(), _stream(dev))
     _cabi.check(rc, "fgb_subm_conv_fprop")
     _count(1)
     return out
 
 
-def conv_dgrad(grad_out, weight_cvc, neighbor_map, sorted_idx, masks) -> torch.Tensor:
+def conv_dgrad(grad_out, weight_cvc, neighbor_map, sorted_idx, masks, order=None) -> torch.Tensor:
     """grad_out [N,Co], weight_cvc [Co,V,Ci] -> grad_feats [N,Ci]."""
     lib = _cabi.lib()
     dev = grad_out.device
@@ -216,7 +227,7 @@ def conv_dgrad(grad_out, weight_cvc, neighbor_map, sorted_idx, masks) -> torch.T
     nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(1, Ci, Co, V, code, 1), "fgb_conv_workspace_bytes")
     ws = workspace(dev, "dgrad", nbytes)
     rc = lib.fgb_subm_conv_dgrad(_ptr(grad_out), weight_cvc.data_ptr(), _ptr(neighbor_map), _ptr(sorted_idx), _ptr(masks),
-                                 _ptr(out), n, Ci, Co, V, code, ws.data_ptr(), ws.numel() * 8,
+                                 _ptr(order), _ptr(out), n, Ci, Co, V, code, ws.data_ptr(), ws.numel() * 8,
                                  status_word(dev).data_ptr(), _stream(dev))
     _cabi.check(rc, "fgb_subm_conv_dgrad")
     _count(2)

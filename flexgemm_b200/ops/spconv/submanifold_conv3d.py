@@ -44,6 +44,14 @@ class SubMConv3dNeighborCache:
             setattr(self, name, kernels.cuda.tile_masks(self["gray_code"], self["sorted_idx"], block_size))
         return getattr(self, name)
 
+    def block_order(self, block_size: int) -> torch.Tensor:
+        """Pairs of consecutive tiles in descending order of work (the schedule of
+        the persistent kernels); computed with the tile masks, once per cache."""
+        name = f"block_order_{block_size}"
+        if not hasattr(self, name):
+            setattr(self, name, kernels.cuda.block_schedule(self.tile_masks(block_size)))
+        return getattr(self, name)
+
     def compute_kernel_idx(self, block_size: int):
         vk, seg = kernels.cuda.valid_kernel(self.tile_masks(block_size))
         self[f"valid_kernel_{block_size}"] = vk
@@ -152,7 +160,8 @@ class SubMConv3dFunction(Function):
             tile = kernels.cuda.conv_tile_rows()
             return kernels.cuda.conv_fprop(
                 feats, weight.reshape(Co, V, Ci), bias.contiguous() if bias is not None else None,
-                neighbor_cache["neighbor_map"], neighbor_cache["sorted_idx"], neighbor_cache.tile_masks(tile))
+                neighbor_cache["neighbor_map"], neighbor_cache["sorted_idx"], neighbor_cache.tile_masks(tile),
+                neighbor_cache.block_order(tile))
         raise ValueError(f"Unsupported algorithm {spconv.ALGORITHM}")
 
     @staticmethod
@@ -183,7 +192,7 @@ class SubMConv3dFunction(Function):
             if feats.requires_grad:
                 tile = kernels.cuda.conv_tile_rows()
                 grad_input = kernels.cuda.conv_dgrad(grad_output, w, neighbor_cache["neighbor_map"], neighbor_cache["sorted_idx"],
-                                                     neighbor_cache.tile_masks(tile))
+                                                     neighbor_cache.tile_masks(tile), neighbor_cache.block_order(tile))
             if weight.requires_grad:
                 gw, _ = kernels.cuda.conv_wgrad(grad_output, feats, neighbor_cache["valid_signal_i"], neighbor_cache["valid_signal_o"],
                                                 neighbor_cache["valid_signal_seg"])

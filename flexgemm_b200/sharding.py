@@ -106,7 +106,8 @@ def sharded_backward(grad_out: torch.Tensor, feats: torch.Tensor, cache, weight:
     if local_grads is None:
         from .kernels import cuda as K
         if want_input_grad:
-            grad_in = K.conv_dgrad(grad_out, w, cache["neighbor_map"], cache["sorted_idx"], cache.tile_masks(K.conv_tile_rows()))
+            tile = K.conv_tile_rows()
+            grad_in = K.conv_dgrad(grad_out, w, cache["neighbor_map"], cache["sorted_idx"], cache.tile_masks(tile), cache.block_order(tile))
         gw32, gb32 = _cuda_local_grads(grad_out, feats, cache, w, bias is not None)
     else:
         grad_in, gw32, gb32 = local_grads(grad_out, feats, cache, w, bias is not None)

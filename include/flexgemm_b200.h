@@ -139,18 +139,27 @@ int fgb_pp_valid_kernel(const uint32_t* tile_masks, int64_t nblk,
  * been built with block == fgb_conv_tile_rows(). */
 int fgb_conv_tile_rows(void);
 
+/* block_order (uint32 [ceil(num_tiles / 2)]) = the 256-row blocks (pairs of
+ * consecutive 128-row tiles) in descending order of work, computed from the tile
+ * masks.  The persistent conv kernels deal blocks to the SMs from this list so
+ * that every SM gets about the same amount of work; passing a null block_order
+ * to them means natural order.  (The reference balances by launching one CTA
+ * per tile; it has no counterpart of this list.) */
+int fgb_conv_block_schedule(const uint32_t* tile_masks, int64_t num_tiles,
+                            uint32_t* block_order, void* stream);
+
 /* out[r, :] = bias + sum_v feats[neighbor_map[r, v], :] * weight[:, v, :]^T
  * for every row r, visiting only the offsets set in the row's tile mask.
  * feats [n, Ci], weight [Co, V, Ci], bias [Co] or null, out [n, Co]; all of
  * element type `dtype`, rows 16-byte aligned (Ci, Co multiples of 8 for 16-bit
- * types, of 4 for fp32).
+ * types, of 4 for fp32).  tile_masks: fgb_pp_tile_masks with block = 128.
  * Stands in for sparse_submanifold_conv_fwd_masked_implicit_gemm_splitk
  * (flex_gemm/kernels/triton/spconv/
  *  sparse_submanifold_conv_fwd_masked_implicit_gemm_splitk.py:21-172).
  * `workspace` is needed only for FGB_F32_IEEE (fgb_conv_workspace_bytes). */
 int fgb_subm_conv_fprop(const void* feats, const void* weight, const void* bias,
                         const uint32_t* neighbor_map, const int64_t* sorted_idx,
-                        const uint32_t* tile_masks,
+                        const uint32_t* tile_masks, const uint32_t* block_order,
                         void* out, int64_t n, int Ci, int Co, int V, int dtype,
                         void* workspace, int64_t workspace_bytes,
                         int32_t* status, void* stream);
@@ -162,7 +171,7 @@ int fgb_subm_conv_fprop(const void* feats, const void* weight, const void* bias,
  * (…/sparse_submanifold_conv_bwd_masked_implicit_gemm_splitk.py:23-100, 205-251). */
 int fgb_subm_conv_dgrad(const void* grad_out, const void* weight,
                         const uint32_t* neighbor_map, const int64_t* sorted_idx,
-                        const uint32_t* tile_masks,
+                        const uint32_t* tile_masks, const uint32_t* block_order,
                         void* grad_feats, int64_t n, int Ci, int Co, int V, int dtype,
                         void* workspace, int64_t workspace_bytes,
                         int32_t* status, void* stream);

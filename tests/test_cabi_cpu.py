@@ -60,9 +60,9 @@ def test_argument_validation_without_launch(lib):
     assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 20, 48, 0, 0, 0, 0, 0, 0, 0) == -3  # key width
     assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 20, 32, 0, 0, 0, 0, 0, 0, 0) == -1  # null seg
     assert lib.fgb_pp_tile_masks(0, 0, 10, 100, 0, 0) == -2   # not a power of two
-    assert lib.fgb_subm_conv_fprop(0, 0, 0, 0, 0, 0, 0, 10, 64, 64, 27, _cabi.F16, 0, 0, 0, 0) == -1
-    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 16, 10, 60, 64, 27, _cabi.F16, 0, 0, 0, 0) == -4  # Ci % 8
-    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 16, 10, 64, 64, 27, 7, 0, 0, 0, 0) == -3
+    assert lib.fgb_subm_conv_fprop(0, 0, 0, 0, 0, 0, 0, 0, 10, 64, 64, 27, _cabi.F16, 0, 0, 0, 0) == -1
+    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 60, 64, 27, _cabi.F16, 0, 0, 0, 0) == -4  # Ci % 8
+    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 64, 64, 27, 7, 0, 0, 0, 0) == -3
     assert lib.fgb_subm_conv_wgrad(16, 16, 16, 16, 16, 16, 0, 10, 100, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -5  # workspace
 
 
