@@ -36,6 +36,7 @@
 #include <type_traits>
 
 #include "fgb_common.cuh"
+#include "fgb_precision.cuh"
 #include "fgb_umma.cuh"
 
 namespace fgb {
@@ -546,7 +547,7 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
               const uint32_t* tile_masks, const uint32_t* block_order, void* out, int64_t n, int kc, int nout, int V, int dtype, int flip, int32_t* status,
               cudaStream_t s) {
   const int eb = elem_bytes(dtype);
-  if (eb == 0 || dtype == FGB_F32_IEEE) return FGB_E_DTYPE;
+  if (eb == 0 || dtype == FGB_F32_IEEE) return FGB_E_DTYPE;  // callers expand fp32-accurate mode to TF32 operands
   if (n < 0 || n >= (int64_t(1) << 32) - 1 || kc <= 0 || nout <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
   if (n == 0) return FGB_OK;
   if (!x || !w || !nbr || !sorted_idx || !tile_masks || !out) return FGB_E_NULL;
@@ -619,10 +620,24 @@ extern "C" int fgb_subm_conv_fprop(const void* feats, const void* weight, const 
                                    const int64_t* sorted_idx, const uint32_t* tile_masks, const uint32_t* block_order, void* out,
                                    int64_t n, int Ci, int Co, int V, int dtype, void* workspace, int64_t workspace_bytes,
                                    int32_t* status, void* stream) {
-  (void)workspace;
-  (void)workspace_bytes;
-  return fgb::run_igemm(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, out, n, Ci, Co, V, dtype, 0, status,
-                        static_cast<cudaStream_t>(stream));
+  using namespace fgb;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype != FGB_F32_IEEE)
+    return run_igemm(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, out, n, Ci, Co, V, dtype, 0, status, s);
+  // fp32-accurate: one TF32 run over the tripled channel dimension
+  if (n < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
+  if (n == 0) return FGB_OK;
+  if (!feats || !weight || !workspace) return FGB_E_NULL;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return FGB_E_ALIGN;
+  const int64_t x_bytes = align256(n * 3 * Ci * 4), w_bytes = align256(int64_t(Co) * V * 3 * Ci * 4);
+  if (workspace_bytes < x_bytes + w_bytes) return FGB_E_WORKSPACE;
+  float* x3 = static_cast<float*>(workspace);
+  float* w3 = reinterpret_cast<float*>(static_cast<char*>(workspace) + x_bytes);
+  int rc = launch_split3(static_cast<const float*>(feats), x3, n, Ci, kSplitActivations, s);
+  if (rc != FGB_OK) return rc;
+  rc = launch_split3(static_cast<const float*>(weight), w3, int64_t(Co) * V, Ci, kSplitWeights, s);
+  if (rc != FGB_OK) return rc;
+  return run_igemm(x3, w3, bias, neighbor_map, sorted_idx, tile_masks, block_order, out, n, 3 * Ci, Co, V, FGB_F32_TF32, 0, status, s);
 }
 
 extern "C" int fgb_subm_conv_dgrad(const void* grad_out, const void* weight, const uint32_t* neighbor_map,
@@ -632,11 +647,15 @@ extern "C" int fgb_subm_conv_dgrad(const void* grad_out, const void* weight, con
   using namespace fgb;
   const int eb = elem_bytes(dtype);
   if (eb == 0) return FGB_E_DTYPE;
-  if (Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
+  if (n < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
   if (n == 0) return FGB_OK;
   if (!weight || !workspace) return FGB_E_NULL;
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return FGB_E_ALIGN;
-  if (workspace_bytes < int64_t(Ci) * V * Co * eb) return FGB_E_WORKSPACE;
+  const int64_t wt_bytes = align256(int64_t(Ci) * V * Co * eb);
+  const bool ieee = dtype == FGB_F32_IEEE;
+  const int64_t w3_bytes = ieee ? align256(int64_t(Ci) * V * 3 * Co * 4) : 0;
+  const int64_t g3_bytes = ieee ? align256(n * 3 * Co * 4) : 0;
+  if (workspace_bytes < wt_bytes + w3_bytes + g3_bytes) return FGB_E_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid(static_cast<unsigned>(ceil_div(Ci, 32)), static_cast<unsigned>(ceil_div(Co, 32)), V);
   if (eb == 2)
@@ -645,6 +664,16 @@ extern "C" int fgb_subm_conv_dgrad(const void* grad_out, const void* weight, con
     weight_transpose_kernel<uint32_t><<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(weight), static_cast<uint32_t*>(workspace), Co, V, Ci);
   int rc = launch_status();
   if (rc != FGB_OK) return rc;
-  return run_igemm(grad_out, workspace, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, grad_feats, n, Co, Ci, V, dtype, 1,
+  if (!ieee)
+    return run_igemm(grad_out, workspace, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, grad_feats, n, Co, Ci, V, dtype, 1,
+                     status, s);
+  if (!grad_out) return FGB_E_NULL;
+  float* w3 = reinterpret_cast<float*>(static_cast<char*>(workspace) + wt_bytes);
+  float* g3 = reinterpret_cast<float*>(static_cast<char*>(workspace) + wt_bytes + w3_bytes);
+  rc = launch_split3(static_cast<const float*>(workspace), w3, int64_t(Ci) * V, Co, kSplitWeights, s);
+  if (rc != FGB_OK) return rc;
+  rc = launch_split3(static_cast<const float*>(grad_out), g3, n, Co, kSplitActivations, s);
+  if (rc != FGB_OK) return rc;
+  return run_igemm(g3, w3, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, grad_feats, n, 3 * Co, Ci, V, FGB_F32_TF32, 1,
                    status, s);
 }

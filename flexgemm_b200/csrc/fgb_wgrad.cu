@@ -23,6 +23,7 @@
 #include <type_traits>
 
 #include "fgb_common.cuh"
+#include "fgb_precision.cuh"
 #include "fgb_umma.cuh"
 
 namespace fgb {
@@ -289,7 +290,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
 template <typename T>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, const uint32_t* __restrict__ seg, int kb,
                                                             int unit_kb, int Co, int V, int Ci, T* __restrict__ out,
-                                                            float* __restrict__ out_f32) {
+                                                            float* __restrict__ out_f32, int accumulate) {
   const int v = blockIdx.y;
   const int64_t e = (blockIdx.x * int64_t(256) + threadIdx.x) * 4;  // element of the [Co, Ci] slab
   if (e >= int64_t(Co) * Ci) return;
@@ -302,6 +303,11 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
   }
   const int co = static_cast<int>(e / Ci), ci = static_cast<int>(e % Ci);
   const int64_t o = (int64_t(co) * V + v) * Ci + ci;
+  if (accumulate) {  // later passes of the fp32-accurate mode add to what an earlier pass wrote (fp32 outputs only)
+    const float* prev = out_f32 ? out_f32 : reinterpret_cast<const float*>(out);
+    const float4 t = *reinterpret_cast<const float4*>(prev + o);
+    acc.x += t.x, acc.y += t.y, acc.z += t.z, acc.w += t.w;
+  }
   if (out_f32) *reinterpret_cast<float4*>(out_f32 + o) = acc;
   if (out) {
     if constexpr (std::is_same<T, float>::value) {
@@ -444,50 +450,40 @@ extern "C" int fgb_wgrad_default_splitk(int64_t n_pairs, int Ci, int Co, int V, 
   return static_cast<int>(s);
 }
 
-extern "C" int64_t fgb_conv_workspace_bytes(int pass, int Ci, int Co, int V, int dtype, int splitk) {
+extern "C" int64_t fgb_conv_workspace_bytes(int pass, int64_t n, int Ci, int Co, int V, int dtype, int splitk) {
   using namespace fgb;
   const int eb = elem_bytes(dtype);
   if (eb == 0) return FGB_E_DTYPE;
-  if (Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
+  if (n < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
   const int64_t w_elems = int64_t(Ci) * V * Co;
+  const bool ieee = dtype == FGB_F32_IEEE;
   switch (pass) {
-    case 0:
-      return 0;
-    case 1:
-      return w_elems * eb;
-    case 2:
+    case 0:  // fp32-accurate mode: tripled activations and weights
+      return ieee ? align256(n * 3 * Ci * 4) + align256(w_elems * 3 * 4) : 0;
+    case 1:  // re-laid-out weight (+ its tripled copy and the tripled grad_out)
+      return align256(w_elems * eb) + (ieee ? align256(w_elems * 3 * 4) + align256(n * 3 * Co * 4) : 0);
+    case 2:  // slabs [Co, Ci] for up to (splitk + 1) * V units (+ hi/lo copies of both operands)
       if (splitk < 1 || splitk > 1024) return FGB_E_SIZE;
-      return w_elems * 4 * (int64_t(splitk) + 1);  // slabs [Co, Ci] for up to (splitk + 1) * V units
+      return align256(w_elems * 4 * (int64_t(splitk) + 1)) + (ieee ? 2 * align256(n * Ci * 4) + 2 * align256(n * Co * 4) : 0);
     default:
       return FGB_E_SIZE;
   }
 }
 
-extern "C" int fgb_subm_conv_wgrad(const void* grad_out, const void* feats, const uint32_t* valid_signal_i,
-                                   const uint32_t* valid_signal_o, const uint32_t* valid_signal_seg, void* grad_weight,
-                                   float* grad_weight_f32, int64_t n, int64_t n_pairs, int Ci, int Co, int V, int dtype, int splitk,
-                                   void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
-  using namespace fgb;
+namespace fgb {
+// one wgrad pass over operands of element type `dtype` (never FGB_F32_IEEE): partial slabs, then the ordered sum
+static int wgrad_pass(const void* grad_out, const void* feats, const uint32_t* vs_i, const uint32_t* vs_o, const uint32_t* seg,
+                      void* grad_weight, float* grad_weight_f32, int64_t n_pairs, int Ci, int Co, int V, int dtype, int splitk,
+                      float* slabs, int accumulate, int32_t* status, cudaStream_t s) {
   const int eb = elem_bytes(dtype);
-  if (eb == 0 || dtype == FGB_F32_IEEE) return FGB_E_DTYPE;
-  if (n < 0 || n_pairs < 0 || n_pairs > n * V || Ci <= 0 || Co <= 0 || V < 1 || V > 32 || splitk < 1 || splitk > 1024) return FGB_E_SIZE;
-  if ((Ci * eb) % 16 || (Co * eb) % 16) return FGB_E_ALIGN;
-  if (!valid_signal_seg || !workspace) return FGB_E_NULL;
-  if (n_pairs > 0 && (!grad_out || !feats || !valid_signal_i || !valid_signal_o)) return FGB_E_NULL;
-  if ((reinterpret_cast<uintptr_t>(grad_out) | reinterpret_cast<uintptr_t>(feats) | reinterpret_cast<uintptr_t>(workspace) |
-       reinterpret_cast<uintptr_t>(grad_weight) | reinterpret_cast<uintptr_t>(grad_weight_f32)) & 15)
-    return FGB_E_ALIGN;
-  const int64_t need = fgb_conv_workspace_bytes(2, Ci, Co, V, dtype, splitk);
-  if (workspace_bytes < need) return FGB_E_WORKSPACE;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
   const WgradPlan w = plan_wgrad(Ci, Co, eb);
   WgradParams p;
   p.gout = static_cast<const char*>(grad_out);
   p.x = static_cast<const char*>(feats);
-  p.vs_i = valid_signal_i;
-  p.vs_o = valid_signal_o;
-  p.seg = valid_signal_seg;
-  p.partial = static_cast<float*>(workspace);
+  p.vs_i = vs_i;
+  p.vs_o = vs_o;
+  p.seg = seg;
+  p.partial = slabs;
   p.Co = Co, p.Ci = Ci, p.V = V;
   int64_t max_units = 0;
   unit_plan(n_pairs, V, w.kb, splitk, &p.unit_kb, &max_units);
@@ -518,15 +514,58 @@ extern "C" int fgb_subm_conv_wgrad(const void* grad_out, const void* feats, cons
   const dim3 rgrid(static_cast<unsigned>(ceil_div(int64_t(Co) * Ci, 1024)), static_cast<unsigned>(V));
   switch (dtype) {
     case FGB_F16:
-      splitk_reduce_kernel<__half><<<rgrid, 256, 0, s>>>(p.partial, p.seg, p.kb, p.unit_kb, Co, V, Ci, static_cast<__half*>(grad_weight), grad_weight_f32);
+      splitk_reduce_kernel<__half><<<rgrid, 256, 0, s>>>(slabs, seg, p.kb, p.unit_kb, Co, V, Ci, static_cast<__half*>(grad_weight), grad_weight_f32, 0);
       break;
     case FGB_BF16:
-      splitk_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, s>>>(p.partial, p.seg, p.kb, p.unit_kb, Co, V, Ci, static_cast<__nv_bfloat16*>(grad_weight), grad_weight_f32);
+      splitk_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, s>>>(slabs, seg, p.kb, p.unit_kb, Co, V, Ci, static_cast<__nv_bfloat16*>(grad_weight), grad_weight_f32, 0);
       break;
     default:
-      splitk_reduce_kernel<float><<<rgrid, 256, 0, s>>>(p.partial, p.seg, p.kb, p.unit_kb, Co, V, Ci, static_cast<float*>(grad_weight), grad_weight_f32);
+      splitk_reduce_kernel<float><<<rgrid, 256, 0, s>>>(slabs, seg, p.kb, p.unit_kb, Co, V, Ci, static_cast<float*>(grad_weight), grad_weight_f32, accumulate);
   }
   return launch_status();
+}
+}  // namespace fgb
+
+extern "C" int fgb_subm_conv_wgrad(const void* grad_out, const void* feats, const uint32_t* valid_signal_i,
+                                   const uint32_t* valid_signal_o, const uint32_t* valid_signal_seg, void* grad_weight,
+                                   float* grad_weight_f32, int64_t n, int64_t n_pairs, int Ci, int Co, int V, int dtype, int splitk,
+                                   void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+  using namespace fgb;
+  const int eb = elem_bytes(dtype);
+  if (eb == 0) return FGB_E_DTYPE;
+  if (n < 0 || n_pairs < 0 || n_pairs > n * V || Ci <= 0 || Co <= 0 || V < 1 || V > 32 || splitk < 1 || splitk > 1024) return FGB_E_SIZE;
+  if ((Ci * eb) % 16 || (Co * eb) % 16) return FGB_E_ALIGN;
+  if (!valid_signal_seg || !workspace) return FGB_E_NULL;
+  if (n_pairs > 0 && (!grad_out || !feats || !valid_signal_i || !valid_signal_o)) return FGB_E_NULL;
+  if (!grad_weight && !grad_weight_f32) return FGB_E_NULL;
+  if ((reinterpret_cast<uintptr_t>(grad_out) | reinterpret_cast<uintptr_t>(feats) | reinterpret_cast<uintptr_t>(grad_weight) |
+       reinterpret_cast<uintptr_t>(grad_weight_f32)) & 15)
+    return FGB_E_ALIGN;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return FGB_E_ALIGN;
+  if (workspace_bytes < fgb_conv_workspace_bytes(2, n, Ci, Co, V, dtype, splitk)) return FGB_E_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* slabs = static_cast<float*>(workspace);
+  if (dtype != FGB_F32_IEEE)
+    return wgrad_pass(grad_out, feats, valid_signal_i, valid_signal_o, valid_signal_seg, grad_weight, grad_weight_f32, n_pairs, Ci, Co, V,
+                      dtype, splitk, slabs, 0, status, s);
+  // fp32-accurate: g_hi*x_hi + g_hi*x_lo + g_lo*x_hi, three passes adding into the fp32 output
+  char* base = static_cast<char*>(workspace) + align256(int64_t(Ci) * V * Co * 4 * (int64_t(splitk) + 1));
+  float* x_hi = reinterpret_cast<float*>(base);
+  float* x_lo = reinterpret_cast<float*>(base + align256(n * Ci * 4));
+  float* g_hi = reinterpret_cast<float*>(base + 2 * align256(n * Ci * 4));
+  float* g_lo = reinterpret_cast<float*>(base + 2 * align256(n * Ci * 4) + align256(n * Co * 4));
+  int rc = launch_split2(static_cast<const float*>(feats), x_hi, x_lo, n * Ci, s);
+  if (rc != FGB_OK) return rc;
+  rc = launch_split2(static_cast<const float*>(grad_out), g_hi, g_lo, n * Co, s);
+  if (rc != FGB_OK) return rc;
+  const float* ga[3] = {g_hi, g_hi, g_lo};
+  const float* xa[3] = {x_hi, x_lo, x_hi};
+  for (int pass = 0; pass < 3; ++pass) {
+    rc = wgrad_pass(ga[pass], xa[pass], valid_signal_i, valid_signal_o, valid_signal_seg, grad_weight, grad_weight_f32, n_pairs, Ci, Co,
+                    V, FGB_F32_TF32, splitk, slabs, pass > 0, status, s);
+    if (rc != FGB_OK) return rc;
+  }
+  return FGB_OK;
 }
 
 extern "C" int64_t fgb_bias_grad_workspace_bytes(int Co) { return Co <= 0 ? FGB_E_SIZE : int64_t(fgb::kBiasBlocks) * Co * 4; }

@@ -206,7 +206,7 @@ def conv_fprop(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks, order=N
     Co, V, _ = weight_cvc.shape
     code = dtype_code(feats.dtype)
     out = torch.empty((n, Co), dtype=feats.dtype, device=dev)
-    nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(0, Ci, Co, V, code, 1), "fgb_conv_workspace_bytes")
+    nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(0, n, Ci, Co, V, code, 1), "fgb_conv_workspace_bytes")
     ws = workspace(dev, "fprop", nbytes) if nbytes else None
     rc = lib.fgb_subm_conv_fprop(_ptr(feats), weight_cvc.data_ptr(), _ptr(bias), _ptr(neighbor_map), _ptr(sorted_idx),
                                  _ptr(masks), _ptr(order), _ptr(out), n, Ci, Co, V, code, _ptr(ws), ws.numel() * 8 if ws is not None else 0,
@@ -224,7 +224,7 @@ def conv_dgrad(grad_out, weight_cvc, neighbor_map, sorted_idx, masks, order=None
     _, V, Ci = weight_cvc.shape
     code = dtype_code(grad_out.dtype)
     out = torch.empty((n, Ci), dtype=grad_out.dtype, device=dev)
-    nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(1, Ci, Co, V, code, 1), "fgb_conv_workspace_bytes")
+    nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(1, n, Ci, Co, V, code, 1), "fgb_conv_workspace_bytes")
     ws = workspace(dev, "dgrad", nbytes)
     rc = lib.fgb_subm_conv_dgrad(_ptr(grad_out), weight_cvc.data_ptr(), _ptr(neighbor_map), _ptr(sorted_idx), _ptr(masks),
                                  _ptr(order), _ptr(out), n, Ci, Co, V, code, ws.data_ptr(), ws.numel() * 8,
@@ -249,7 +249,7 @@ def conv_wgrad(grad_out, feats, vs_i, vs_o, vs_seg, splitk: Optional[int] = None
             _cabi.check(splitk, "fgb_wgrad_default_splitk")
     gw = torch.empty((Co, V, Ci), dtype=feats.dtype, device=dev) if want_dtype else None
     gw32 = torch.empty((Co, V, Ci), dtype=torch.float32, device=dev) if want_f32 else None
-    nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(2, Ci, Co, V, code, splitk), "fgb_conv_workspace_bytes")
+    nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(2, n, Ci, Co, V, code, splitk), "fgb_conv_workspace_bytes")
     ws = workspace(dev, "wgrad", nbytes)
     rc = lib.fgb_subm_conv_wgrad(_ptr(grad_out), _ptr(feats), _ptr(vs_i), _ptr(vs_o), vs_seg.data_ptr(), _ptr(gw), _ptr(gw32),
                                  n, int(vs_i.shape[0]), Ci, Co, V, code, int(splitk), ws.data_ptr(), ws.numel() * 8,

@@ -177,8 +177,9 @@ int fgb_subm_conv_dgrad(const void* grad_out, const void* weight,
                         int32_t* status, void* stream);
 
 /* Workspace bytes for fprop (pass = 0), dgrad (pass = 1) and wgrad (pass = 2,
- * with the given split count). */
-int64_t fgb_conv_workspace_bytes(int pass, int Ci, int Co, int V, int dtype, int splitk);
+ * with the given split count) on n rows.  FGB_F32_IEEE needs room for the
+ * hi/lo-split copies of its operands, hence the dependence on n. */
+int64_t fgb_conv_workspace_bytes(int pass, int64_t n, int Ci, int Co, int V, int dtype, int splitk);
 
 /* Split count the library would pick for wgrad on the current device. */
 int fgb_wgrad_default_splitk(int64_t n_pairs, int Ci, int Co, int V, int dtype);

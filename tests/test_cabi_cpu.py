@@ -45,10 +45,11 @@ def test_size_queries(lib):
     assert lib.fgb_map_num_blocks(0) == 0
     assert lib.fgb_map_num_blocks(257) == 2
     assert lib.fgb_conv_tile_rows() == 128
-    assert lib.fgb_conv_workspace_bytes(0, 64, 64, 27, _cabi.F16, 1) == 0
-    assert lib.fgb_conv_workspace_bytes(1, 64, 32, 27, _cabi.F16, 1) == 64 * 32 * 27 * 2
-    assert lib.fgb_conv_workspace_bytes(2, 64, 32, 27, _cabi.F16, 4) == 64 * 32 * 27 * 4 * 5
-    assert lib.fgb_conv_workspace_bytes(2, 64, 32, 27, 9, 4) < 0
+    assert lib.fgb_conv_workspace_bytes(0, 1000, 64, 64, 27, _cabi.F16, 1) == 0
+    assert lib.fgb_conv_workspace_bytes(0, 1000, 64, 64, 27, _cabi.F32_IEEE, 1) == 1000 * 3 * 64 * 4 + 64 * 64 * 27 * 3 * 4
+    assert lib.fgb_conv_workspace_bytes(1, 1000, 64, 32, 27, _cabi.F16, 1) == 64 * 32 * 27 * 2
+    assert lib.fgb_conv_workspace_bytes(2, 1000, 64, 32, 27, _cabi.F16, 4) == 64 * 32 * 27 * 4 * 5
+    assert lib.fgb_conv_workspace_bytes(2, 1000, 64, 32, 27, 9, 4) < 0
     assert lib.fgb_bias_grad_workspace_bytes(256) > 0
 
 

@@ -198,6 +198,26 @@ def test_conv_fwd_bwd_vs_oracle(res, ci, co, dtype, batch, tol, K):
         assert rel_err(a, b) <= tol, (name, rel_err(a, b))
 
 
+@pytest.mark.parametrize("res,ci,co,batch", [(32, 32, 32, 1), (16, 64, 48, 2), (24, 128, 256, 1)])
+def test_conv_fp32_without_tf32(res, ci, co, batch, K):
+    """allow_tf32 = False: fp32-accurate products (split-TF32), <= 1e-4 relative."""
+    from flexgemm_b200.kernels import config
+    config.allow_tf32 = False
+    scales = tuple(1.0 - 0.2 * i for i in range(batch))
+    coords, feats, weight, bias, shape = orc.make_problem(res, ci, co, "float32", seed=res + ci, batch=batch, scales=scales)
+    g = torch.Generator().manual_seed(2)
+    grad_out = torch.randn(coords.shape[0], co, generator=g)
+    got = run_conv(coords, feats, weight, bias, shape, grad_out)
+    want = oracle_conv(coords, feats, weight, bias, shape, grad_out)
+    for name, a, b in zip(("out", "grad_feats", "grad_weight", "grad_bias"), got[:4], want):
+        assert a.dtype == torch.float32
+        assert rel_err(a, b) <= 1e-4, (name, rel_err(a, b))
+    # and it is really tighter than the TF32 mode on the same inputs
+    config.allow_tf32 = True
+    tf32 = run_conv(coords, feats, weight, bias, shape, grad_out)
+    assert rel_err(tf32[0], want[0]) > rel_err(got[0], want[0])
+
+
 CONV = np.load(os.path.join(GOLD, "conv_explicit.npz"))
 
 
