@@ -22,9 +22,7 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
 import time
 
 import torch
@@ -36,6 +34,9 @@ if ROOT not in sys.path:
 METRIC = "submconv fwd+bwd useful TFLOP/s (C=256 fp16, RES=256); neighbor-map build ms"
 RES, CI, CO = 256, 256, 256
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch at this workload, from the ncu capture summarised in
+# profiles/subm_igemm_and_wgrad_res256_c256_fp16.md
+NCU_DRAM_TRAFFIC_BYTES = {"fprop": 285.2e6, "dgrad": 285.3e6, "wgrad": 857.3e6}
 
 
 def load_peaks():
@@ -52,59 +53,66 @@ def load_peaks():
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock, power and throttle reasons of one GPU through NVML from
+    a background thread (read-only queries; about one sample per millisecond, so
+    that even a 20 ms timed region is covered)."""
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
-        self.proc = None
-        self.path = None
+        self.samples = []
+        self.thread = None
+        self.stop_flag = False
+        self.nvml = None
 
     def start(self):
         try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            import threading
+
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = int(visible.split(",")[self.gpu]) if visible and visible.split(",")[self.gpu].isdigit() else self.gpu
+            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.nvml = pynvml
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+
+            def loop():
+                while not self.stop_flag:
+                    try:
+                        mhz = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                        reasons = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                        watts = pynvml.nvmlDeviceGetPowerUsage(handle) / 1000.0
+                        self.samples.append((mhz, reasons, watts))
+                    except Exception:
+                        pass
+                    time.sleep(0.001)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
         except Exception:
-            self.proc = None
+            self.thread = None
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
+        if self.thread is None:
             return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        rows = []
-        try:
-            with open(self.path) as f:
-                for line in f:
-                    parts = [x.strip() for x in line.split(",")]
-                    if len(parts) >= 9 and parts[1].isdigit():
-                        rows.append(parts)
-            os.unlink(self.path)
-        except Exception:
-            pass
-        if not rows:
+        self.stop_flag = True
+        self.thread.join(timeout=2)
+        if not self.samples:
             return out
-        # under load = the upper half of the power samples
-        powers = sorted(float(r[3]) for r in rows if r[3].replace(".", "").isdigit())
-        cut = powers[len(powers) // 2] if powers else 0.0
-        busy = [r for r in rows if r[3].replace(".", "").isdigit() and float(r[3]) >= cut] or rows
-        out["sm_mhz"] = statistics.median(int(r[1]) for r in busy)
-        out["sm_max_mhz"] = max(int(r[2]) for r in rows)
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = set()
-        for r in rows:
-            for name, val in zip(names, r[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        out["reasons"] = sorted(reasons)
-        out["samples"] = len(rows)
+        nv = self.nvml
+        names = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+        seen = set()
+        for _, reasons, _ in self.samples:
+            for name, bit in names.items():
+                if reasons & bit:
+                    seen.add(name)
+        out["sm_mhz"] = statistics.median(m for m, _, _ in self.samples)
+        out["sm_max_mhz"] = self.max_mhz
+        out["power_w_max"] = max(w for _, _, w in self.samples)
+        out["reasons"] = sorted(seen)
+        out["samples"] = len(self.samples)
         return out
 
 
@@ -223,7 +231,7 @@ def run_gpu_arm(args):
     pairs = int(cache["valid_signal_i"].shape[0])
     flops_step = 6.0 * pairs * CI * CO
     tile = K.conv_tile_rows()
-    cache.tile_masks(tile)
+    cache.block_order(tile)
     f_req = feats.detach().requires_grad_(True)
     w_req = weight.detach().requires_grad_(True)
     b_req = bias.detach().requires_grad_(True)
@@ -301,10 +309,10 @@ def run_gpu_arm(args):
 
     # ---- per-kernel times for the roofline (rank 0) --------------------------
     w_cvc = weight.reshape(CO, 27, CI)
-    masks = cache.tile_masks(tile)
+    masks, order = cache.tile_masks(tile), cache.block_order(tile)
     it = max(args.steps, 10)
-    t_fprop = time_loop(lambda: K.conv_fprop(feats, w_cvc, bias, cache["neighbor_map"], cache["sorted_idx"], masks), it)
-    t_dgrad = time_loop(lambda: K.conv_dgrad(gout, w_cvc, cache["neighbor_map"], cache["sorted_idx"], masks), it)
+    t_fprop = time_loop(lambda: K.conv_fprop(feats, w_cvc, bias, cache["neighbor_map"], cache["sorted_idx"], masks, order), it)
+    t_dgrad = time_loop(lambda: K.conv_dgrad(gout, w_cvc, cache["neighbor_map"], cache["sorted_idx"], masks, order), it)
     t_wgrad = time_loop(lambda: K.conv_wgrad(gout, feats, cache["valid_signal_i"], cache["valid_signal_o"], cache["valid_signal_seg"]), it)
     kernels = {"fprop": t_fprop, "dgrad": t_dgrad, "wgrad": t_wgrad}
     dom = max(kernels, key=kernels.get)
@@ -312,7 +320,8 @@ def run_gpu_arm(args):
     achieved = pass_flops / (kernels[dom] * 1e-3) / 1e12
     peak_tf = float(peaks["bf16_tflops"])
     roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
-                "frac": achieved / peak_tf, "traffic": None, "peak_source": peaks["source"],
+                "frac": achieved / peak_tf, "traffic": NCU_DRAM_TRAFFIC_BYTES.get(dom), "traffic_unit": "bytes per launch (ncu)",
+                "algorithmic_flops_per_launch": pass_flops, "peak_source": peaks["source"],
                 "ms": {k: round(v, 4) for k, v in kernels.items()},
                 "tflops": {k: round(pass_flops / (v * 1e-3) / 1e12, 1) for k, v in kernels.items()}}
     V, k = 27, 4

@@ -32,7 +32,6 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include <cstdlib>
 #include <type_traits>
 
 #include "fgb_common.cuh"
@@ -74,8 +73,6 @@ struct IgemmParams {
   int stages;
   int acc_sets;              // accumulator pairs that fit in TMEM (1 or 2)
   uint32_t idesc;
-  unsigned long long* dbg;   // per-CTA timing counters when debug & 128
-  int debug;                 // timing experiments: 1 no gather, 2 no weight loads, 4 no MMA, 8 no stores
   int32_t* status;
 };
 
@@ -198,7 +195,6 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
 
   if (warp >= kGatherWarp0) {
     // ---------------------------------------------------------------- gather
-    if (p.debug & 16) goto done;
     const int piece = lane & 7;
     const int g = (warp - kGatherWarp0) * 4 + (lane >> 3);  // 0..31: rows g, g+32, ... of the block
     // shared-memory offset of this thread's 16 bytes for each of its 8 rows (j < 4: half 0)
@@ -263,7 +259,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
           const bool col_ok = kb * 128 + piece * 16 < p.row_bytes;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            if ((j < 4 ? need0 : need1) && !(p.debug & 1)) {
+            if (j < 4 ? need0 : need1) {
               const bool ok = col_ok && idx[j] != kInvalid;
               cp_async_16(a_base + dst_off[j], src[j] + kb * 128, ok ? 16u : 0u);
             }
@@ -278,7 +274,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------ weight TMA
-    if (lane == 0 && !(p.debug & 16)) {
+    if (lane == 0) {
       uint32_t it = 0;
       uint32_t mblk = 0, ntile = 0;
       for (uint32_t pass = 0; work_of(pass, mblk, ntile); ++pass) {
@@ -293,10 +289,6 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
           for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
             const uint32_t s = it % S;
             mbar_wait(&ctl->empty[s], ((it / S) & 1) ^ 1, abort_flag);
-            if (p.debug & 2) {
-              mbar_arrive(&ctl->full[s]);
-              continue;
-            }
             mbar_arrive_expect_tx(&ctl->full[s], static_cast<uint32_t>(p.bn) * 128u);
             tma_load_3d(smem_u32(stages + size_t(s) * stage_bytes + 2 * kATileBytes), &tmap_w, &ctl->full[s], kb * (128 / kElem), wv, n0);
           }
@@ -307,8 +299,6 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     // ------------------------------------------------------------------- MMA
     if (lane == 0) {
       uint32_t it = 0, item = 0;
-      unsigned long long t_acc = 0, t_full = 0, t_all = global_timer_ns(), n_it = 0;
-      const long long c_all = clock64();
       uint32_t mblk = 0, ntile = 0;
       for (; work_of(item, mblk, ntile); ++item) {
         uint32_t m0, m1;
@@ -316,9 +306,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
         const uint32_t set = item % p.acc_sets;
         const uint32_t acc_tmem = tmem_base + set * 2 * p.bn;
         // the epilogue must have drained this accumulator pair
-        unsigned long long t0 = (p.debug & 128) ? global_timer_ns() : 0;
         mbar_wait(&ctl->acc_empty[set], ((item / p.acc_sets) & 1) ^ 1, abort_flag);
-        if (p.debug & 128) t_acc += global_timer_ns() - t0;
         tc_fence_after_sync();
         uint32_t acc0 = 0, acc1 = 0;
         uint32_t un = m0 | m1;
@@ -328,9 +316,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
           const bool need0 = (m0 >> v) & 1u, need1 = (m1 >> v) & 1u;
           for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
             const uint32_t s = it % S;
-            if (p.debug & 128) t0 = global_timer_ns();
-            if (!(p.debug & 16)) mbar_wait(&ctl->full[s], (it / S) & 1, abort_flag);
-            if (p.debug & 128) t_full += global_timer_ns() - t0, ++n_it;
+            mbar_wait(&ctl->full[s], (it / S) & 1, abort_flag);
             tc_fence_after_sync();
             const uint32_t a_addr = smem_u32(stages + size_t(s) * stage_bytes);
             const uint64_t da0 = make_smem_desc(a_addr, 16, 1024);
@@ -338,7 +324,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
             const uint64_t db = make_smem_desc(a_addr + 2 * kATileBytes, 16, 1024);
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4) {
-              if (kb * 128 + k4 * 32 < p.row_bytes && !(p.debug & 4)) {
+              if (kb * 128 + k4 * 32 < p.row_bytes) {
                 if (need0) {
                   umma_ss<kTF32>(acc_tmem, da0 + uint64_t(k4 * 2), db + uint64_t(k4 * 2), p.idesc, acc0);
                   acc0 = 1;
@@ -349,16 +335,10 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
                 }
               }
             }
-            if (!(p.debug & 16)) umma_commit(&ctl->empty[s]);
+            umma_commit(&ctl->empty[s]);
           }
         }
         umma_commit(&ctl->acc_full[set]);
-      }
-      if ((p.debug & 128) && p.dbg) {
-        p.dbg[blockIdx.x * 4 + 0] = global_timer_ns() - t_all;
-        p.dbg[blockIdx.x * 4 + 1] = t_acc;
-        p.dbg[blockIdx.x * 4 + 2] = t_full;
-        p.dbg[blockIdx.x * 4 + 3] = static_cast<unsigned long long>(clock64() - c_all);
       }
     }
   } else {
@@ -391,16 +371,16 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + set * 2 * p.bn + h * p.bn;
         for (int c0 = 0; c0 < p.bn; c0 += kColsPerPass) {
           uint32_t acc[kChunksPerPass][32];
-          if (has_acc && !(p.debug & 32)) {
+          if (has_acc) {
 #pragma unroll
             for (int cc = 0; cc < kChunksPerPass; ++cc) tmem_ld_32x32(t_addr + c0 + cc * 32, acc[cc]);
             tmem_ld_wait();
           }
 #pragma unroll
           for (int cc = 0; cc < kChunksPerPass; ++cc)
-            if (!(p.debug & 64)) stage_row_chunk<kDtype>(stage_out, lane, cc, acc[cc], p.bias, n0 + c0 + cc * 32, p.nout, !has_acc);
+            stage_row_chunk<kDtype>(stage_out, lane, cc, acc[cc], p.bias, n0 + c0 + cc * 32, p.nout, !has_acc);
           __syncwarp();
-          if (!(p.debug & 8)) {
+          {
             // 128 bytes per row: lane -> (row = 4 i + lane / 8, piece = lane % 8)
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -421,7 +401,6 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     }
   }
 
-done:
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 5) {
@@ -541,7 +520,6 @@ static int launch_igemm(const CUtensorMap& tmap, const IgemmParams& p, cudaStrea
   return launch_status();
 }
 
-static unsigned long long* g_dbg_buffer = nullptr;
 // x [n, kc] gathered through nbr; w [nout, V, kc]; out [n, nout]
 int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nbr, const int64_t* sorted_idx,
               const uint32_t* tile_masks, const uint32_t* block_order, void* out, int64_t n, int kc, int nout, int V, int dtype, int flip, int32_t* status,
@@ -580,11 +558,6 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   p.stages = (kSmemBudget - 1024 - kCtrlBytes - kStoreStageBytes) / stage_bytes;
   if (p.stages > kMaxStages) p.stages = kMaxStages;
   p.acc_sets = 2 * p.bn * 2 <= 512 ? 2 : 1;
-  {
-    const char* e = getenv("FGB_IGEMM_DEBUG");
-    p.debug = e ? atoi(e) : 0;
-    p.dbg = g_dbg_buffer;
-  }
   const uint32_t fmt = dtype == FGB_F16 ? kFmtF16 : dtype == FGB_BF16 ? kFmtBF16 : kFmtTF32;
   p.idesc = make_idesc(fmt, kTileM, p.bn, 0, 0);
   p.status = status;
@@ -604,7 +577,6 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
 }  // namespace fgb
 
 extern "C" int fgb_conv_tile_rows(void) { return fgb::kTileM; }
-extern "C" void fgb_debug_set_buffer(void* p) { fgb::g_dbg_buffer = static_cast<unsigned long long*>(p); }
 
 extern "C" int fgb_conv_block_schedule(const uint32_t* tile_masks, int64_t num_tiles, uint32_t* block_order, void* stream) {
   using namespace fgb;
