@@ -112,8 +112,14 @@ __device__ __forceinline__ Table<64> make_table<64>(void* mem, uint32_t slots) {
 
 struct Grid3 {
   int W, H, D;
+  // flat index b*W*H*D + x*H*D + y*D + z; 32-bit arithmetic is exact whenever the 32-bit table is in use
+  template <int kKeyBits>
   __device__ __forceinline__ uint64_t key(int b, int x, int y, int z) const {
-    return ((static_cast<uint64_t>(b) * W + x) * H + y) * static_cast<uint64_t>(D) + z;
+    if constexpr (kKeyBits == 32) {
+      return ((static_cast<uint32_t>(b) * W + x) * H + y) * static_cast<uint32_t>(D) + z;
+    } else {
+      return ((static_cast<uint64_t>(b) * W + x) * H + y) * static_cast<uint64_t>(D) + z;
+    }
   }
 };
 
@@ -125,7 +131,7 @@ __global__ void __launch_bounds__(kMapBlock) hash_insert_kernel(const int4* __re
   if (i >= n) return;
   const int4 c = __ldg(&coords[i]);
   const auto table = make_table<kKeyBits>(table_mem, slots);
-  if (!table.insert(g.key(c.x, c.y, c.z, c.w), i)) report(status, FGB_S_TABLE_FULL);
+  if (!table.insert(g.template key<kKeyBits>(c.x, c.y, c.z, c.w), i)) report(status, FGB_S_TABLE_FULL);
 }
 
 struct Stencil {
@@ -143,39 +149,51 @@ __global__ void __launch_bounds__(kMapBlock)
   __shared__ int4 s_coord[kMapBlock];
   __shared__ uint32_t s_gray[kMapBlock];
   __shared__ uint32_t s_count[32];
+  __shared__ int4 s_delta[32];  // (dx, dy, dz) of each offset: no divisions in the item loop
   const uint32_t n0 = blockIdx.x * kMapBlock;
   const uint32_t nv = min(static_cast<uint32_t>(kMapBlock), n - n0);
   const int t = threadIdx.x;
+  const int V = st.V;
   if (t < nv) s_coord[t] = __ldg(&coords[n0 + t]);
   s_gray[t] = 0;
-  if (t < 32) s_count[t] = 0;
+  if (t < 32) {
+    s_count[t] = 0;
+    const int KhKd = st.Kh * st.Kd;
+    const int kx = t / KhKd, ky = (t / st.Kd) % st.Kh, kz = t % st.Kd;
+    s_delta[t] = make_int4((kx - st.Kw / 2) * st.Dw, (ky - st.Kh / 2) * st.Dh, (kz - st.Kd / 2) * st.Dd, 0);
+  }
   __syncthreads();
 
   const auto table = make_table<kKeyBits>(table_mem, slots);
-  const int V = st.V;
-  const int KhKd = st.Kh * st.Kd;
   const int centre = V >> 1;  // all kernel extents are odd
   const uint32_t items = nv * V;
   uint32_t* out = nbr + static_cast<size_t>(n0) * V;
+  // item = lv * V + v walks t, t + 256, ...: (lv, v) advance by (256 / V, 256 % V) with a carry
+  const uint32_t step_lv = kMapBlock / V;
+  const int step_v = kMapBlock % V;
+  uint32_t lv = t / V;
+  int v = t - lv * V;
   for (uint32_t item = t; item < items; item += kMapBlock) {
-    const uint32_t lv = item / V;
-    const int v = item - lv * V;
     uint32_t val;
     if (v == centre) {
       val = n0 + lv;
     } else {
       const int4 c = s_coord[lv];
-      const int kx = v / KhKd, ky = (v / st.Kd) % st.Kh, kz = v % st.Kd;
-      const int x = c.y + (kx - st.Kw / 2) * st.Dw;
-      const int y = c.z + (ky - st.Kh / 2) * st.Dh;
-      const int z = c.w + (kz - st.Kd / 2) * st.Dd;
+      const int4 d = s_delta[v];
+      const int x = c.y + d.x, y = c.z + d.y, z = c.w + d.z;
       val = kInvalid;
-      if (x >= 0 && x < g.W && y >= 0 && y < g.H && z >= 0 && z < g.D) val = table.find(g.key(c.x, x, y, z));
+      if (x >= 0 && x < g.W && y >= 0 && y < g.H && z >= 0 && z < g.D) val = table.find(g.template key<kKeyBits>(c.x, x, y, z));
     }
     out[item] = val;
     if (val != kInvalid) {
       atomicOr(&s_gray[lv], 1u << v);
       atomicAdd(&s_count[v], 1u);
+    }
+    lv += step_lv;
+    v += step_v;
+    if (v >= V) {
+      v -= V;
+      ++lv;
     }
   }
   __syncthreads();

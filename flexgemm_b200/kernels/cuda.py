@@ -83,9 +83,7 @@ def check_status(device: torch.device) -> None:
     code = int(word.item())
     if code != 0:
         word.zero_()
-        what = {_cabi.S_TABLE_FULL: "hash table full (raise the hashmap ratio)",
-                _cabi.S_WAIT_TIMEOUT: "a bounded barrier wait ran out inside a kernel"}.get(code, f"code {code}")
-        raise RuntimeError(f"flexgemm_b200 device-side error: {what}")
+        raise_for_status(code)
 
 
 # --------------------------------------------------------------------------
@@ -94,7 +92,9 @@ def check_status(device: torch.device) -> None:
 def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table: torch.Tensor, key_bits: int,
                             slots: int) -> Dict[str, torch.Tensor]:
     """Hash build + lookup.  Returns neighbor_map [N,V] uint32, gray_code and
-    binary_code [N] int32, block_offsets [V*nblk] uint32, valid_signal_seg [V+1] uint32."""
+    binary_code [N] int32, block_offsets [V*nblk] uint32, valid_signal_seg [V+1]
+    uint32 and ``meta`` (uint32 [V+2]: the segment array followed by this call's
+    own status word, so that one device-to-host copy fetches both)."""
     _require_cuda(coords, "coords")
     lib = _cabi.lib()
     dev = coords.device
@@ -102,23 +102,32 @@ def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table:
     _, _, W, H, D = [int(s) for s in shape]
     V = int(ksize[0]) * int(ksize[1]) * int(ksize[2])
     nblk = _cabi.check_size(lib.fgb_map_num_blocks(n), "fgb_map_num_blocks")
+    meta = torch.zeros(V + 2, dtype=torch.uint32, device=dev)
     out = {
         "neighbor_map": torch.empty((n, V), dtype=torch.uint32, device=dev),
         "gray_code": torch.empty(n, dtype=torch.int32, device=dev),
         "binary_code": torch.empty(n, dtype=torch.int32, device=dev),
         "block_offsets": torch.empty(max(V * nblk, 1), dtype=torch.uint32, device=dev),
-        "valid_signal_seg": torch.empty(V + 1, dtype=torch.uint32, device=dev),
+        "valid_signal_seg": meta[:V + 1],
+        "meta": meta,
     }
     rc = lib.fgb_subm_build_neighbor_map(
         _ptr(coords), n, W, H, D, int(ksize[0]), int(ksize[1]), int(ksize[2]),
         int(dilation[0]), int(dilation[1]), int(dilation[2]),
         table.data_ptr(), int(slots), int(key_bits),
         _ptr(out["neighbor_map"]), _ptr(out["gray_code"]), _ptr(out["binary_code"]),
-        out["block_offsets"].data_ptr(), out["valid_signal_seg"].data_ptr(),
-        status_word(dev).data_ptr(), _stream(dev))
+        out["block_offsets"].data_ptr(), meta.data_ptr(),
+        meta.data_ptr() + 4 * (V + 1), _stream(dev))
     _cabi.check(rc, "fgb_subm_build_neighbor_map")
     _count(4)
     return out
+
+
+def raise_for_status(code: int) -> None:
+    if code != 0:
+        what = {_cabi.S_TABLE_FULL: "hash table full (raise the hashmap ratio)",
+                _cabi.S_WAIT_TIMEOUT: "a bounded barrier wait ran out inside a kernel"}.get(code, f"code {code}")
+        raise RuntimeError(f"flexgemm_b200 device-side error: {what}")
 
 
 def sorted_idx_from_binary(binary_code: torch.Tensor, key_bits: int) -> torch.Tensor:

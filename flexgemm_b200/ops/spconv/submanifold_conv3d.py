@@ -97,20 +97,32 @@ class SubMConv3dFunction(Function):
         table, key_bits = utils.init_hashmap(shape, slots, coords.device)
         built = kernels.cuda.subm_build_neighbor_map(coords, shape, kernel_size, dilation, table, key_bits, slots)
         if spconv.ALGORITHM == Algorithm.EXPLICIT_GEMM:
-            kernels.cuda.check_status(coords.device)
+            kernels.cuda.raise_for_status(int(built["meta"][-1].item()))
             return SubMConv3dNeighborCache(neighbor_map=built["neighbor_map"])
 
+        if needs_grad:
+            # The one host round trip of the build: the pair count sizes the lists, and
+            # the same copy brings the build's status word (hash table overflow).  The
+            # copy is queued before the sort so that the host wait overlaps the sort.
+            meta_host = torch.empty(built["meta"].shape, dtype=built["meta"].dtype, pin_memory=True)
+            meta_host.copy_(built["meta"], non_blocking=True)
+            copied = torch.cuda.Event()
+            copied.record(torch.cuda.current_stream(coords.device))
         sorted_idx = kernels.cuda.sorted_idx_from_binary(built["binary_code"], V)
         cache = SubMConv3dNeighborCache(neighbor_map=built["neighbor_map"], gray_code=built["gray_code"], sorted_idx=sorted_idx)
         if needs_grad:
-            # The one host round trip of the build: the pair count sizes the lists.
+            copied.synchronize()
+            kernels.cuda.raise_for_status(int(meta_host[-1]))
             seg = built["valid_signal_seg"]
-            num_pairs = int(seg[-1].item())
+            num_pairs = int(meta_host[V])
             vs_i, vs_o = kernels.cuda.valid_signal(built["neighbor_map"], built["gray_code"], built["block_offsets"], seg, num_pairs)
             cache["valid_signal_seg"] = seg
             cache["valid_signal_i"] = vs_i
             cache["valid_signal_o"] = vs_o
-        kernels.cuda.check_status(coords.device)
+        else:
+            # inference cache: nothing needs the host, so nothing synchronises; an
+            # overflowing table would show in this word, readable at any later time
+            cache["build_status"] = built["meta"][-1:]
         return cache
 
     @staticmethod
