@@ -43,6 +43,8 @@ namespace fgb {
 constexpr int kTileM = 128;             // rows per accumulator (and per tile mask)
 constexpr int kBlockM = 2 * kTileM;     // rows per work item
 constexpr int kMaxStages = 6;
+constexpr int kSchedRing = 16;  // deeper than the gather front can ever run ahead of the epilogue (stages + accumulator sets + 1 blocks)
+constexpr int kSchedReaders = 14;  // 8 gather warps, the TMA lane, the MMA lane, 4 epilogue warps
 constexpr int kIgemmThreads = 448;
 constexpr int kGatherWarp0 = 6;
 constexpr int kGatherThreads = 256;
@@ -58,10 +60,11 @@ struct IgemmParams {
   const int64_t* sorted_idx; // [n]
   const uint32_t* tile_masks; // one mask per 128 sorted rows
   const uint32_t* block_order; // row blocks in descending cost order, or null for natural order
+  uint32_t* ticket;          // zeroed counter: the next position of the block list to hand out
   char* out;                 // [n, nout]
   uint32_t n;
   uint32_t num_tiles;        // ceil(n / 128)
-  uint32_t num_work;         // row blocks x column tiles
+  uint32_t num_blocks;       // ceil(n / 256)
   int kc;                    // reduction channels per offset
   int nout;                  // output channels
   int V;
@@ -81,6 +84,9 @@ struct IgemmSmem {
   uint64_t empty[kMaxStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t sched_full[kSchedRing];   // work entry published
+  uint64_t sched_empty[kSchedRing];  // work entry read by every role
+  uint32_t sched_entry[kSchedRing];  // block * n_tiles_n + column tile, or kInvalid = no more work
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -160,6 +166,10 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
       mbar_init(&ctl->acc_full[a], 1);   // tcgen05.commit after the block's last MMA
       mbar_init(&ctl->acc_empty[a], 4);  // the four epilogue warps
     }
+    for (int k = 0; k < kSchedRing; ++k) {
+      mbar_init(&ctl->sched_full[k], 1);
+      mbar_init(&ctl->sched_empty[k], kSchedReaders);
+    }
     ctl->abort_flag = 0;
     mbar_init_fence();
   }
@@ -173,18 +183,39 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  // Every role walks the same sequence: work item w -> (row block, column tile);
-  // within it the offsets of the union mask in ascending order, num_kb slices each.
-  // Work item of this CTA in pass i.  Items are dealt to the CTAs in a
-  // boustrophedon over the cost-sorted list (pass 0: CTA c takes item c, pass 1:
-  // item 2G-1-c, ...), which evens out the total cost per CTA.
-  auto work_of = [&](uint32_t pass, uint32_t& mblk, uint32_t& ntile) -> bool {
-    const uint32_t G = gridDim.x;
-    const uint32_t w = pass * G + ((pass & 1u) ? G - 1u - blockIdx.x : blockIdx.x);
-    if (w >= p.num_work) return false;
-    const uint32_t b = w / p.n_tiles_n;
-    ntile = w - b * p.n_tiles_n;
-    mblk = p.block_order != nullptr ? __ldg(&p.block_order[b]) : b;
+  // Work distribution.  Row blocks are handed out dynamically, in descending
+  // cost order, from a global ticket counter: lane 0 of the first gather warp
+  // claims the ticket of the CTA's next block when the gather front starts the
+  // current one, and publishes it (block x column tile, or "no more work") in a
+  // small shared-memory ring that every role reads in order.  So each role walks
+  // the same sequence of work items, an SM that got cheap blocks simply takes
+  // more of them, and within an item all roles enumerate the offsets of the
+  // union mask in ascending order, num_kb slices each.
+  const uint32_t none = 0xFFFFFFFFu;  // "no more work" (kInvalid as a plain value, usable in conditional expressions)
+  auto publish_work = [&](uint32_t k, uint32_t& pub_block, uint32_t& pub_ntile) {  // one thread
+    const uint32_t slot = k % kSchedRing;
+    mbar_wait(&ctl->sched_empty[slot], ((k / kSchedRing) & 1) ^ 1, abort_flag);
+    if (pub_block != kInvalid && ++pub_ntile >= static_cast<uint32_t>(p.n_tiles_n)) pub_ntile = 0;
+    if (pub_block == kInvalid || pub_ntile == 0) {
+      const uint32_t t = atomicAdd(p.ticket, 1u);
+      pub_block = t < p.num_blocks ? (p.block_order != nullptr ? __ldg(&p.block_order[t]) : t) : none;
+      pub_ntile = 0;
+      if (pub_block == kInvalid) pub_ntile = 0xFFFFFFFFu;  // stays "no more work"
+    }
+    ctl->sched_entry[slot] = (pub_block == none || *abort_flag) ? none : pub_block * p.n_tiles_n + pub_ntile;
+    mbar_arrive(&ctl->sched_full[slot]);
+  };
+  // k-th work item of this CTA; every reader (a whole warp, or a single lane when
+  // `one_lane`) calls it exactly once per k, in order, until it returns false
+  auto work_of = [&](uint32_t k, uint32_t& mblk, uint32_t& ntile, bool one_lane) -> bool {
+    const uint32_t slot = k % kSchedRing;
+    const bool ok = mbar_wait(&ctl->sched_full[slot], (k / kSchedRing) & 1, abort_flag);
+    const uint32_t e = ok ? *reinterpret_cast<volatile uint32_t*>(&ctl->sched_entry[slot]) : none;
+    if (!one_lane) __syncwarp();
+    if (one_lane || lane == 0) mbar_arrive(&ctl->sched_empty[slot]);
+    if (e == kInvalid) return false;
+    mblk = e / p.n_tiles_n;
+    ntile = e - mblk * p.n_tiles_n;
     return true;
   };
   auto masks_of = [&](uint32_t mblk, uint32_t& m0, uint32_t& m1) {
@@ -222,7 +253,10 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     uint32_t rows[8], nrows[8], idx[8], nidx[8];
     uint32_t m0 = 0, m1 = 0, nm0 = 0, nm1 = 0;
     uint32_t mblk = 0, ntile = 0;
-    bool has_work = work_of(0, mblk, ntile);
+    const bool publisher = warp == kGatherWarp0 && lane == 0;
+    uint32_t pub_block = kInvalid, pub_ntile = 0;
+    if (publisher) publish_work(0, pub_block, pub_ntile);
+    bool has_work = work_of(0, mblk, ntile, false);
     if (has_work) {
       masks_of(mblk, m0, m1);
       load_rows(mblk, rows);
@@ -231,7 +265,8 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     for (uint32_t pass = 0; has_work; ++pass) {
       // rows and masks of the next work item, fetched a whole block ahead
       uint32_t mblk_n = 0, ntile_n = 0;
-      const bool has_next = work_of(pass + 1, mblk_n, ntile_n);
+      if (publisher) publish_work(pass + 1, pub_block, pub_ntile);
+      const bool has_next = work_of(pass + 1, mblk_n, ntile_n, false);
       if (has_next) {
         masks_of(mblk_n, nm0, nm1);
         load_rows(mblk_n, nrows);
@@ -277,7 +312,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     if (lane == 0) {
       uint32_t it = 0;
       uint32_t mblk = 0, ntile = 0;
-      for (uint32_t pass = 0; work_of(pass, mblk, ntile); ++pass) {
+      for (uint32_t pass = 0; work_of(pass, mblk, ntile, true); ++pass) {
         const int n0 = static_cast<int>(ntile) * p.bn;
         uint32_t m0, m1;
         masks_of(mblk, m0, m1);
@@ -300,7 +335,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     if (lane == 0) {
       uint32_t it = 0, item = 0;
       uint32_t mblk = 0, ntile = 0;
-      for (; work_of(item, mblk, ntile); ++item) {
+      for (; work_of(item, mblk, ntile, true); ++item) {
         uint32_t m0, m1;
         masks_of(mblk, m0, m1);
         const uint32_t set = item % p.acc_sets;
@@ -352,7 +387,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     constexpr int kChunksPerPass = kColsPerPass / 32 > 0 ? kColsPerPass / 32 : 1;
     uint32_t item = 0;
     uint32_t mblk = 0, ntile = 0;
-    for (; work_of(item, mblk, ntile); ++item) {
+    for (; work_of(item, mblk, ntile, false); ++item) {
       const int n0 = static_cast<int>(ntile) * p.bn;
       uint32_t m0, m1;
       masks_of(mblk, m0, m1);
@@ -515,14 +550,15 @@ static int launch_igemm(const CUtensorMap& tmap, const IgemmParams& p, cudaStrea
     if (e != cudaSuccess) return cuda_status(e);
     configured = smem;
   }
-  const unsigned grid = static_cast<unsigned>(p.num_work < uint32_t(sm_count()) ? p.num_work : uint32_t(sm_count()));
+  const int64_t work = int64_t(p.num_blocks) * p.n_tiles_n;
+  const unsigned grid = static_cast<unsigned>(work < sm_count() ? work : sm_count());
   subm_igemm_kernel<kDtype><<<grid, kIgemmThreads, smem, s>>>(tmap, p);
   return launch_status();
 }
 
 // x [n, kc] gathered through nbr; w [nout, V, kc]; out [n, nout]
 int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nbr, const int64_t* sorted_idx,
-              const uint32_t* tile_masks, const uint32_t* block_order, void* out, int64_t n, int kc, int nout, int V, int dtype, int flip, int32_t* status,
+              const uint32_t* tile_masks, const uint32_t* block_order, uint32_t* ticket, void* out, int64_t n, int kc, int nout, int V, int dtype, int flip, int32_t* status,
               cudaStream_t s) {
   const int eb = elem_bytes(dtype);
   if (eb == 0 || dtype == FGB_F32_IEEE) return FGB_E_DTYPE;  // callers expand fp32-accurate mode to TF32 operands
@@ -540,6 +576,7 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   p.sorted_idx = sorted_idx;
   p.tile_masks = tile_masks;
   p.block_order = block_order;
+  p.ticket = ticket;
   p.out = static_cast<char*>(out);
   p.n = static_cast<uint32_t>(n);
   p.kc = kc;
@@ -551,9 +588,7 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   p.num_kb = static_cast<int>(ceil_div(p.row_bytes, 128));
   p.flip = flip;
   p.num_tiles = static_cast<uint32_t>(ceil_div(n, kTileM));
-  const int64_t num_work = ceil_div(n, kBlockM) * p.n_tiles_n;
-  if (num_work > 0x7FFFFFFF) return FGB_E_SIZE;
-  p.num_work = static_cast<uint32_t>(num_work);
+  p.num_blocks = static_cast<uint32_t>(ceil_div(n, kBlockM));
   const int stage_bytes = 2 * kATileBytes + p.bn * 128;
   p.stages = (kSmemBudget - 1024 - kCtrlBytes - kStoreStageBytes) / stage_bytes;
   if (p.stages > kMaxStages) p.stages = kMaxStages;
@@ -561,8 +596,11 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   const uint32_t fmt = dtype == FGB_F16 ? kFmtF16 : dtype == FGB_BF16 ? kFmtBF16 : kFmtTF32;
   p.idesc = make_idesc(fmt, kTileM, p.bn, 0, 0);
   p.status = status;
+  if (!ticket) return FGB_E_NULL;
+  int rc = cuda_status(cudaMemsetAsync(ticket, 0, sizeof(uint32_t), s));
+  if (rc != FGB_OK) return rc;
   CUtensorMap tmap;
-  int rc = make_weight_tmap(&tmap, w, nout, V, kc, p.bn, dtype);
+  rc = make_weight_tmap(&tmap, w, nout, V, kc, p.bn, dtype);
   if (rc != FGB_OK) return rc;
   switch (dtype) {
     case FGB_F16:
@@ -588,28 +626,36 @@ extern "C" int fgb_conv_block_schedule(const uint32_t* tile_masks, int64_t num_t
   return launch_status();
 }
 
+// Every conv workspace starts with a 256-byte header whose first word is the
+// ticket counter of the persistent kernel; the pass-specific scratch follows.
+constexpr int64_t kWsHeader = 256;
+
 extern "C" int fgb_subm_conv_fprop(const void* feats, const void* weight, const void* bias, const uint32_t* neighbor_map,
                                    const int64_t* sorted_idx, const uint32_t* tile_masks, const uint32_t* block_order, void* out,
                                    int64_t n, int Ci, int Co, int V, int dtype, void* workspace, int64_t workspace_bytes,
                                    int32_t* status, void* stream) {
   using namespace fgb;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype != FGB_F32_IEEE)
-    return run_igemm(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, out, n, Ci, Co, V, dtype, 0, status, s);
-  // fp32-accurate: one TF32 run over the tripled channel dimension
   if (n < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
   if (n == 0) return FGB_OK;
-  if (!feats || !weight || !workspace) return FGB_E_NULL;
+  if (!workspace) return FGB_E_NULL;
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return FGB_E_ALIGN;
+  if (workspace_bytes < kWsHeader) return FGB_E_WORKSPACE;
+  uint32_t* ticket = static_cast<uint32_t*>(workspace);
+  char* scratch = static_cast<char*>(workspace) + kWsHeader;
+  if (dtype != FGB_F32_IEEE)
+    return run_igemm(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, ticket, out, n, Ci, Co, V, dtype, 0, status, s);
+  // fp32-accurate: one TF32 run over the tripled channel dimension
+  if (!feats || !weight) return FGB_E_NULL;
   const int64_t x_bytes = align256(n * 3 * Ci * 4), w_bytes = align256(int64_t(Co) * V * 3 * Ci * 4);
-  if (workspace_bytes < x_bytes + w_bytes) return FGB_E_WORKSPACE;
-  float* x3 = static_cast<float*>(workspace);
-  float* w3 = reinterpret_cast<float*>(static_cast<char*>(workspace) + x_bytes);
+  if (workspace_bytes < kWsHeader + x_bytes + w_bytes) return FGB_E_WORKSPACE;
+  float* x3 = reinterpret_cast<float*>(scratch);
+  float* w3 = reinterpret_cast<float*>(scratch + x_bytes);
   int rc = launch_split3(static_cast<const float*>(feats), x3, n, Ci, kSplitActivations, s);
   if (rc != FGB_OK) return rc;
   rc = launch_split3(static_cast<const float*>(weight), w3, int64_t(Co) * V, Ci, kSplitWeights, s);
   if (rc != FGB_OK) return rc;
-  return run_igemm(x3, w3, bias, neighbor_map, sorted_idx, tile_masks, block_order, out, n, 3 * Ci, Co, V, FGB_F32_TF32, 0, status, s);
+  return run_igemm(x3, w3, bias, neighbor_map, sorted_idx, tile_masks, block_order, ticket, out, n, 3 * Ci, Co, V, FGB_F32_TF32, 0, status, s);
 }
 
 extern "C" int fgb_subm_conv_dgrad(const void* grad_out, const void* weight, const uint32_t* neighbor_map,
@@ -627,25 +673,27 @@ extern "C" int fgb_subm_conv_dgrad(const void* grad_out, const void* weight, con
   const bool ieee = dtype == FGB_F32_IEEE;
   const int64_t w3_bytes = ieee ? align256(int64_t(Ci) * V * 3 * Co * 4) : 0;
   const int64_t g3_bytes = ieee ? align256(n * 3 * Co * 4) : 0;
-  if (workspace_bytes < wt_bytes + w3_bytes + g3_bytes) return FGB_E_WORKSPACE;
+  if (workspace_bytes < kWsHeader + wt_bytes + w3_bytes + g3_bytes) return FGB_E_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint32_t* ticket = static_cast<uint32_t*>(workspace);
+  char* wt = static_cast<char*>(workspace) + kWsHeader;
   dim3 grid(static_cast<unsigned>(ceil_div(Ci, 32)), static_cast<unsigned>(ceil_div(Co, 32)), V);
   if (eb == 2)
-    weight_transpose_kernel<uint16_t><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(workspace), Co, V, Ci);
+    weight_transpose_kernel<uint16_t><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(weight), reinterpret_cast<uint16_t*>(wt), Co, V, Ci);
   else
-    weight_transpose_kernel<uint32_t><<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(weight), static_cast<uint32_t*>(workspace), Co, V, Ci);
+    weight_transpose_kernel<uint32_t><<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(weight), reinterpret_cast<uint32_t*>(wt), Co, V, Ci);
   int rc = launch_status();
   if (rc != FGB_OK) return rc;
   if (!ieee)
-    return run_igemm(grad_out, workspace, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, grad_feats, n, Co, Ci, V, dtype, 1,
+    return run_igemm(grad_out, wt, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, ticket, grad_feats, n, Co, Ci, V, dtype, 1,
                      status, s);
   if (!grad_out) return FGB_E_NULL;
-  float* w3 = reinterpret_cast<float*>(static_cast<char*>(workspace) + wt_bytes);
-  float* g3 = reinterpret_cast<float*>(static_cast<char*>(workspace) + wt_bytes + w3_bytes);
-  rc = launch_split3(static_cast<const float*>(workspace), w3, int64_t(Ci) * V, Co, kSplitWeights, s);
+  float* w3 = reinterpret_cast<float*>(wt + wt_bytes);
+  float* g3 = reinterpret_cast<float*>(wt + wt_bytes + w3_bytes);
+  rc = launch_split3(reinterpret_cast<const float*>(wt), w3, int64_t(Ci) * V, Co, kSplitWeights, s);
   if (rc != FGB_OK) return rc;
   rc = launch_split3(static_cast<const float*>(grad_out), g3, n, Co, kSplitActivations, s);
   if (rc != FGB_OK) return rc;
-  return run_igemm(g3, w3, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, grad_feats, n, 3 * Co, Ci, V, FGB_F32_TF32, 1,
+  return run_igemm(g3, w3, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, ticket, grad_feats, n, 3 * Co, Ci, V, FGB_F32_TF32, 1,
                    status, s);
 }

@@ -457,10 +457,10 @@ extern "C" int64_t fgb_conv_workspace_bytes(int pass, int64_t n, int Ci, int Co,
   const int64_t w_elems = int64_t(Ci) * V * Co;
   const bool ieee = dtype == FGB_F32_IEEE;
   switch (pass) {
-    case 0:  // fp32-accurate mode: tripled activations and weights
-      return ieee ? align256(n * 3 * Ci * 4) + align256(w_elems * 3 * 4) : 0;
-    case 1:  // re-laid-out weight (+ its tripled copy and the tripled grad_out)
-      return align256(w_elems * eb) + (ieee ? align256(w_elems * 3 * 4) + align256(n * 3 * Co * 4) : 0);
+    case 0:  // header with the ticket counter (+ fp32-accurate mode: tripled activations and weights)
+      return 256 + (ieee ? align256(n * 3 * Ci * 4) + align256(w_elems * 3 * 4) : 0);
+    case 1:  // header, re-laid-out weight (+ its tripled copy and the tripled grad_out)
+      return 256 + align256(w_elems * eb) + (ieee ? align256(w_elems * 3 * 4) + align256(n * 3 * Co * 4) : 0);
     case 2:  // slabs [Co, Ci] for up to (splitk + 1) * V units (+ hi/lo copies of both operands)
       if (splitk < 1 || splitk > 1024) return FGB_E_SIZE;
       return align256(w_elems * 4 * (int64_t(splitk) + 1)) + (ieee ? 2 * align256(n * Ci * 4) + 2 * align256(n * Co * 4) : 0);

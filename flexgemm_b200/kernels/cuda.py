@@ -216,9 +216,9 @@ def conv_fprop(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks, order=N
     code = dtype_code(feats.dtype)
     out = torch.empty((n, Co), dtype=feats.dtype, device=dev)
     nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(0, n, Ci, Co, V, code, 1), "fgb_conv_workspace_bytes")
-    ws = workspace(dev, "fprop", nbytes) if nbytes else None
+    ws = workspace(dev, "fprop", nbytes)
     rc = lib.fgb_subm_conv_fprop(_ptr(feats), weight_cvc.data_ptr(), _ptr(bias), _ptr(neighbor_map), _ptr(sorted_idx),
-                                 _ptr(masks), _ptr(order), _ptr(out), n, Ci, Co, V, code, _ptr(ws), ws.numel() * 8 if ws is not None else 0,
+                                 _ptr(masks), _ptr(order), _ptr(out), n, Ci, Co, V, code, ws.data_ptr(), ws.numel() * 8,
                                  status_word(dev).data_ptr(), _stream(dev))
     _cabi.check(rc, "fgb_subm_conv_fprop")
     _count(1)

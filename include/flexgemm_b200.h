@@ -156,7 +156,9 @@ int fgb_conv_block_schedule(const uint32_t* tile_masks, int64_t num_tiles,
  * Stands in for sparse_submanifold_conv_fwd_masked_implicit_gemm_splitk
  * (flex_gemm/kernels/triton/spconv/
  *  sparse_submanifold_conv_fwd_masked_implicit_gemm_splitk.py:21-172).
- * `workspace` is needed only for FGB_F32_IEEE (fgb_conv_workspace_bytes). */
+ * `workspace`: fgb_conv_workspace_bytes(0, ...) bytes, 256-byte aligned (it holds
+ * the work counter of the persistent kernel, and the split operands for
+ * FGB_F32_IEEE). */
 int fgb_subm_conv_fprop(const void* feats, const void* weight, const void* bias,
                         const uint32_t* neighbor_map, const int64_t* sorted_idx,
                         const uint32_t* tile_masks, const uint32_t* block_order,

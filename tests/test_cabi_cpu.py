@@ -45,9 +45,9 @@ def test_size_queries(lib):
     assert lib.fgb_map_num_blocks(0) == 0
     assert lib.fgb_map_num_blocks(257) == 2
     assert lib.fgb_conv_tile_rows() == 128
-    assert lib.fgb_conv_workspace_bytes(0, 1000, 64, 64, 27, _cabi.F16, 1) == 0
-    assert lib.fgb_conv_workspace_bytes(0, 1000, 64, 64, 27, _cabi.F32_IEEE, 1) == 1000 * 3 * 64 * 4 + 64 * 64 * 27 * 3 * 4
-    assert lib.fgb_conv_workspace_bytes(1, 1000, 64, 32, 27, _cabi.F16, 1) == 64 * 32 * 27 * 2
+    assert lib.fgb_conv_workspace_bytes(0, 1000, 64, 64, 27, _cabi.F16, 1) == 256
+    assert lib.fgb_conv_workspace_bytes(0, 1000, 64, 64, 27, _cabi.F32_IEEE, 1) == 256 + 1000 * 3 * 64 * 4 + 64 * 64 * 27 * 3 * 4
+    assert lib.fgb_conv_workspace_bytes(1, 1000, 64, 32, 27, _cabi.F16, 1) == 256 + 64 * 32 * 27 * 2
     assert lib.fgb_conv_workspace_bytes(2, 1000, 64, 32, 27, _cabi.F16, 4) == 64 * 32 * 27 * 4 * 5
     assert lib.fgb_conv_workspace_bytes(2, 1000, 64, 32, 27, 9, 4) < 0
     assert lib.fgb_bias_grad_workspace_bytes(256) > 0
@@ -62,8 +62,8 @@ def test_argument_validation_without_launch(lib):
     assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 20, 32, 0, 0, 0, 0, 0, 0, 0) == -1  # null seg
     assert lib.fgb_pp_tile_masks(0, 0, 10, 100, 0, 0) == -2   # not a power of two
     assert lib.fgb_subm_conv_fprop(0, 0, 0, 0, 0, 0, 0, 0, 10, 64, 64, 27, _cabi.F16, 0, 0, 0, 0) == -1
-    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 60, 64, 27, _cabi.F16, 0, 0, 0, 0) == -4  # Ci % 8
-    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 64, 64, 27, 7, 0, 0, 0, 0) == -3
+    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 60, 64, 27, _cabi.F16, 256, 256, 0, 0) == -4  # Ci % 8
+    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 64, 64, 27, 7, 256, 256, 0, 0) == -3
     assert lib.fgb_subm_conv_wgrad(16, 16, 16, 16, 16, 16, 0, 10, 100, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -5  # workspace
 
 
