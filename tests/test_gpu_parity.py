@@ -336,3 +336,55 @@ def test_large_sample_res1024_c64(K):
     ref_gw_centre = gout.double().t() @ feats.double()
     assert rel_err(w.grad[:, 1, 1, 1, :], ref_gw_centre) <= 1e-2
     assert rel_err(b.grad, gout.double().sum(0)) <= 1e-2
+
+
+def test_residual_stack_with_shared_cache(K):
+    """Two residual blocks [conv, SiLU, conv] + skip over a batch of shells, bf16,
+    the neighbour cache built once and passed to every layer (the way a network
+    uses the op); loss = mean of the output.  Checked against the same network
+    written with plain torch ops in fp64 on the CPU (gather through the oracle's
+    neighbour map, autograd for the gradients)."""
+    from flexgemm_b200.ops import spconv
+    C, res, batch = 64, 16, 2
+    coords_np = orc.shell_coords(res, batch=batch, scales=(1.0, 0.8))
+    n = coords_np.shape[0]
+    shape = torch.Size((batch, C, res, res, res))
+    g = torch.Generator().manual_seed(8)
+    x0 = torch.randn(n, C, generator=g).bfloat16()
+    ws = [(torch.randn(C, 3, 3, 3, C, generator=g) / (27 * C) ** 0.5).bfloat16() for _ in range(4)]
+    bs = [torch.randn(C, generator=g).bfloat16() * 0.1 for _ in range(4)]
+
+    # device
+    coords = torch.from_numpy(coords_np).to(DEV)
+    wd = [w.to(DEV).requires_grad_(True) for w in ws]
+    bd = [b.to(DEV).requires_grad_(True) for b in bs]
+    xd = x0.to(DEV).requires_grad_(True)
+    cache, h = None, xd
+    for blk in range(2):
+        y, cache = spconv.sparse_submanifold_conv3d(h, coords, shape, wd[2 * blk], bd[2 * blk], cache)
+        y = torch.nn.functional.silu(y)
+        y, cache = spconv.sparse_submanifold_conv3d(y, coords, shape, wd[2 * blk + 1], bd[2 * blk + 1], cache)
+        h = h + y
+    h.float().mean().backward()
+    torch.cuda.synchronize()
+    K.check_status(DEV)
+
+    # reference
+    nbr = torch.from_numpy(orc.neighbor_map(coords_np, shape).astype(np.int64))
+    ok = (nbr != 0xFFFFFFFF).unsqueeze(-1)
+    idx = nbr.clamp(max=n - 1)
+    def conv(x, w, b):
+        col = torch.where(ok, x[idx], torch.zeros((), dtype=x.dtype)).reshape(n, -1)
+        return col @ w.reshape(C, -1).t() + b
+    wr = [w.double().requires_grad_(True) for w in ws]
+    br = [b.double().requires_grad_(True) for b in bs]
+    xr = x0.double().requires_grad_(True)
+    hr = xr
+    for blk in range(2):
+        y = torch.nn.functional.silu(conv(hr, wr[2 * blk], br[2 * blk]))
+        hr = hr + conv(y, wr[2 * blk + 1], br[2 * blk + 1])
+    hr.mean().backward()
+    assert rel_err(h, hr) <= 2e-2          # four bf16 layers deep
+    assert rel_err(xd.grad, xr.grad) <= 2e-2
+    for a, b in zip(wd + bd, wr + br):
+        assert rel_err(a.grad, b.grad) <= 2e-2
