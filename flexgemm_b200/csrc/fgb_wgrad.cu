@@ -31,6 +31,7 @@ constexpr int kWgThreads = 416;   // 4 epilogue warps, 1 MMA warp, 8 gather warp
 constexpr int kWgGatherWarp0 = 5;
 constexpr int kWgGatherThreads = 256;
 constexpr int kWgMaxStages = 8;
+constexpr int kWgRowsMax = 4;  // pair rows of a stage per gather thread: stages hold up to 128 pairs
 
 struct WgradParams {
   const char* gout;  // [n, Co]
@@ -107,7 +108,7 @@ __device__ __forceinline__ uint32_t wg_slab_of(const uint32_t* seg, int kb, int 
   return base + j;
 }
 
-template <int kElem>
+template <int kElem, int kRows>  // kRows = pairs of a stage / 32 = pair rows per gather thread
 __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradParams p) {
   constexpr bool kTF32 = (kElem == 4);
   constexpr int kUmmaK = 32 / kElem;      // 16 for 16-bit types, 8 for tf32
@@ -176,36 +177,35 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
     // g, g+32, ... of every stage and walks over the chunks of both operands.
     const int piece = lane & 7;
     const int g = (warp - kWgGatherWarp0) * 4 + (lane >> 3);  // 0..31
-    const int rows_per_thread = p.kb / 32;                     // 2 (16-bit) or 1 (tf32)
     const int a_row_bytes = p.Co * kElem, b_row_bytes = p.Ci * kElem;
-    uint32_t row_off[2];
+    uint32_t row_off[kRows];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < kRows; ++j) {
       const int row = g + 32 * j;
       // 16-bit types: 16-byte pieces swizzled by (row & 7); tf32: 32-byte pieces swizzled by (row & 3)
       const int swz = kElem == 2 ? ((piece ^ (row & 7)) << 4) : (((((piece >> 1) ^ (row & 3)) << 1) | (piece & 1)) << 4);
       row_off[j] = row * 128 + swz;
     }
-    auto load_pairs = [&](uint32_t kblk, uint32_t (&io)[2], uint32_t (&ii)[2]) {
+    auto load_pairs = [&](uint32_t kblk, uint32_t (&io)[kRows], uint32_t (&ii)[kRows]) {
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
+      for (int j = 0; j < kRows; ++j) {
         const uint32_t pp = seg_begin + kblk * p.kb + g + 32 * j;
-        const bool ok = j < rows_per_thread && pp < seg_end;
+        const bool ok = pp < seg_end;
         io[j] = ok ? __ldg(&p.vs_o[pp]) : kInvalid;
         ii[j] = ok ? __ldg(&p.vs_i[pp]) : kInvalid;
       }
     };
-    uint32_t io[2], ii[2], nio[2], nii[2];
+    uint32_t io[kRows], ii[kRows], nio[kRows], nii[kRows];
     load_pairs(k_begin, nio, nii);
     for (int it = 0; it < total; ++it) {
       const int s = it % S;
 #pragma unroll
-      for (int j = 0; j < 2; ++j) io[j] = nio[j], ii[j] = nii[j];
+      for (int j = 0; j < kRows; ++j) io[j] = nio[j], ii[j] = nii[j];
       if (it + 1 < total) load_pairs(k_begin + it + 1, nio, nii);  // one stage ahead
-      const char* srca[2];
-      const char* srcb[2];
+      const char* srca[kRows];
+      const char* srcb[kRows];
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
+      for (int j = 0; j < kRows; ++j) {
         srca[j] = p.gout + size_t(io[j] != kInvalid ? io[j] : 0u) * a_row_bytes + co0 * kElem + piece * 16;
         srcb[j] = p.x + size_t(ii[j] != kInvalid ? ii[j] : 0u) * b_row_bytes + ci0 * kElem + piece * 16;
       }
@@ -214,16 +214,14 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
       for (int c = 0; c < p.a_chunks; ++c) {
         const bool col_ok = co0 * kElem + c * 128 + piece * 16 < a_row_bytes;
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-          if (j < rows_per_thread)
-            cp_async_16(st_base + c * chunk_bytes + row_off[j], srca[j] + c * 128, (col_ok && io[j] != kInvalid) ? 16u : 0u);
+        for (int j = 0; j < kRows; ++j)
+          cp_async_16(st_base + c * chunk_bytes + row_off[j], srca[j] + c * 128, (col_ok && io[j] != kInvalid) ? 16u : 0u);
       }
       for (int c = 0; c < p.b_chunks; ++c) {
         const bool col_ok = ci0 * kElem + c * 128 + piece * 16 < b_row_bytes;
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-          if (j < rows_per_thread)
-            cp_async_16(st_base + a_bytes + c * chunk_bytes + row_off[j], srcb[j] + c * 128, (col_ok && ii[j] != kInvalid) ? 16u : 0u);
+        for (int j = 0; j < kRows; ++j)
+          cp_async_16(st_base + a_bytes + c * chunk_bytes + row_off[j], srcb[j] + c * 128, (col_ok && ii[j] != kInvalid) ? 16u : 0u);
       }
       cp_async_arrive(&ctl->full[s]);
     }
@@ -403,9 +401,12 @@ static WgradPlan plan_wgrad(int Ci, int Co, int eb) {
   w.mt = (Co > 128 && w.bn * 2 <= 512) ? 2 : 1;
   w.co_groups = static_cast<int>(ceil_div(Co, w.mt * 128));
   w.ci_tiles = static_cast<int>(ceil_div(Ci, w.bn));
-  w.kb = eb == 2 ? 64 : 32;
   w.a_chunks = w.mt * 128 * eb / 128;
   w.b_chunks = static_cast<int>(ceil_div(w.bn * eb, 128));
+  // pairs per stage: as many as keep a stage near 64 KB (more pairs per stage for narrow channel counts, so that the
+  // fixed cost of a stage hand-over is spread over enough bytes); a multiple of 32 (one row per gather lane group)
+  w.kb = 32;
+  while (w.kb < 32 * kWgRowsMax && size_t(w.a_chunks + w.b_chunks) * (w.kb * 2) * 128 <= 64 * 1024) w.kb *= 2;
   const size_t stage = size_t(w.a_chunks + w.b_chunks) * w.kb * 128;
   const size_t budget = 224 * 1024;
   w.stages = static_cast<int>(budget / stage);
@@ -438,13 +439,18 @@ extern "C" int fgb_wgrad_default_splitk(int64_t n_pairs, int Ci, int Co, int V, 
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t base = int64_t(V) * w.co_groups * w.ci_tiles;
-  // about two CTAs per SM in total: measured best on B200 (fewer leaves SMs idle in the
-  // second wave, more adds partial slabs without shortening the critical path)
+  // About two CTAs per SM in total: measured best on B200 at a few hundred k-blocks per unit (fewer leaves SMs idle
+  // in the second wave, more adds partial slabs without shortening the critical path).  Large inputs get more,
+  // shorter units (about 256 k-blocks each, at most 16 per SM) so that the last wave is a small part of the run.
   int64_t s = (int64_t(2) * sms) / base;
+  const int64_t total_kb = ceil_div(n_pairs, w.kb);
+  const int64_t by_work = total_kb / 256 / base;
+  if (by_work > s) s = by_work;
+  if (s > (int64_t(16) * sms) / base) s = (int64_t(16) * sms) / base;
   // no more splits than stages of pairs per offset on average
   const int64_t max_s = n_pairs > 0 ? ceil_div(ceil_div(n_pairs, V), w.kb) : 1;
   if (s > max_s) s = max_s;
-  if (s > 64) s = 64;
+  if (s > 1024) s = 1024;
   if (s < 1) s = 1;
   return static_cast<int>(s);
 }
@@ -495,16 +501,17 @@ static int wgrad_pass(const void* grad_out, const void* feats, const uint32_t* v
   p.status = status;
   const int64_t grid = max_units * w.co_groups * w.ci_tiles;
   if (grid > 0x7FFFFFFF) return FGB_E_SIZE;
+  const auto launch = [&](auto kernel) -> cudaError_t {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(w.smem));
+    if (e != cudaSuccess) return e;
+    kernel<<<static_cast<unsigned>(grid), kWgThreads, w.smem, s>>>(p);
+    return cudaSuccess;
+  };
   cudaError_t e;
-  if (eb == 2) {
-    e = cudaFuncSetAttribute(subm_wgrad_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(w.smem));
-    if (e != cudaSuccess) return cuda_status(e);
-    subm_wgrad_kernel<2><<<static_cast<unsigned>(grid), kWgThreads, w.smem, s>>>(p);
-  } else {
-    e = cudaFuncSetAttribute(subm_wgrad_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(w.smem));
-    if (e != cudaSuccess) return cuda_status(e);
-    subm_wgrad_kernel<4><<<static_cast<unsigned>(grid), kWgThreads, w.smem, s>>>(p);
-  }
+  const int rows = w.kb / 32;
+  if (eb == 2) e = rows == 4 ? launch(subm_wgrad_kernel<2, 4>) : rows == 2 ? launch(subm_wgrad_kernel<2, 2>) : launch(subm_wgrad_kernel<2, 1>);
+  else e = rows == 4 ? launch(subm_wgrad_kernel<4, 4>) : rows == 2 ? launch(subm_wgrad_kernel<4, 2>) : launch(subm_wgrad_kernel<4, 1>);
+  if (e != cudaSuccess) return cuda_status(e);
   int rc = launch_status();
   if (rc != FGB_OK) return rc;
   const dim3 rgrid(static_cast<unsigned>(ceil_div(int64_t(Co) * Ci, 1024)), static_cast<unsigned>(V));
