@@ -37,6 +37,16 @@ _PROTOTYPES = {
     "fgb_bias_grad_workspace_bytes": (c_int64, [c_int]),
     "fgb_subm_conv_bias_grad": (c_int, [_P, _P, _P, c_int64, c_int, c_int, _P, c_int64, _P]),
     "fgb_cast_from_f32": (c_int, [_P, _P, c_int64, c_int, _P]),
+    "fgb_sparse_out_grid": (c_int, [c_int] * 15 + [_P, _P, _P]),
+    "fgb_sparse_out_coords_collect": (c_int, [_P, c_int64] + [c_int] * 15 + [_P, c_int64, c_int, _P, _P, _P, _P]),
+    "fgb_sparse_out_coords_workspace_bytes": (c_int64, [c_int64, c_int, c_int]),
+    "fgb_sparse_out_coords_finalize": (c_int, [_P, c_int64, c_int, c_int, c_int, c_int] + [c_int] * 15 + [_P, c_int64, _P, _P]),
+    "fgb_sparse_build_neighbor_map": (c_int, [_P, c_int64, _P, c_int64] + [c_int] * 15 + [_P, c_int64, c_int, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "fgb_pp_gray_code": (c_int, [_P, c_int64, c_int, _P, _P, _P]),
+    "fgb_sparse_conv_fprop": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
+    "fgb_sparse_conv_dgrad": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
+    "fgb_sparse_conv_wgrad": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
+    "fgb_sparse_conv_workspace_bytes": (c_int64, [c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int]),
     "fgb_noalloc_max_channels": (c_int, []),
     "fgb_subm_conv_bias_grad_noalloc": (c_int, [_P, _P, _P, c_int64, c_int, c_int, _P]),
 }

@@ -35,4 +35,24 @@ inline int elem_bytes(int dtype) {
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+#ifdef __CUDACC__
+// Murmur3 finalisers: the hash of every table in the library
+__device__ __forceinline__ uint32_t fmix32(uint32_t k) {
+  k ^= k >> 16;
+  k *= 0x85ebca6bu;
+  k ^= k >> 13;
+  k *= 0xc2b2ae35u;
+  k ^= k >> 16;
+  return k;
+}
+__device__ __forceinline__ uint32_t fmix64_hi(uint64_t k) {
+  k ^= k >> 33;
+  k *= 0xff51afd7ed558ccdULL;
+  k ^= k >> 33;
+  k *= 0xc4ceb9fe1a85ec53ULL;
+  k ^= k >> 33;
+  return static_cast<uint32_t>(k >> 32) ^ static_cast<uint32_t>(k);
+}
+#endif
+
 }  // namespace fgb

@@ -630,13 +630,14 @@ extern "C" int fgb_conv_block_schedule(const uint32_t* tile_masks, int64_t num_t
 // ticket counter of the persistent kernel; the pass-specific scratch follows.
 constexpr int64_t kWsHeader = 256;
 
-extern "C" int fgb_subm_conv_fprop(const void* feats, const void* weight, const void* bias, const uint32_t* neighbor_map,
-                                   const int64_t* sorted_idx, const uint32_t* tile_masks, const uint32_t* block_order, void* out,
-                                   int64_t n, int Ci, int Co, int V, int dtype, void* workspace, int64_t workspace_bytes,
-                                   int32_t* status, void* stream) {
-  using namespace fgb;
+namespace fgb {
+
+// n rows of the map / of `out`; n_src rows of `feats` (equal for a submanifold conv)
+static int fprop_impl(const void* feats, const void* weight, const void* bias, const uint32_t* neighbor_map, const int64_t* sorted_idx,
+                      const uint32_t* tile_masks, const uint32_t* block_order, void* out, int64_t n, int64_t n_src, int Ci, int Co, int V,
+                      int dtype, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (n < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
+  if (n < 0 || n_src < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
   if (n == 0) return FGB_OK;
   if (!workspace) return FGB_E_NULL;
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return FGB_E_ALIGN;
@@ -647,32 +648,53 @@ extern "C" int fgb_subm_conv_fprop(const void* feats, const void* weight, const 
     return run_igemm(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, ticket, out, n, Ci, Co, V, dtype, 0, status, s);
   // fp32-accurate: one TF32 run over the tripled channel dimension
   if (!feats || !weight) return FGB_E_NULL;
-  const int64_t x_bytes = align256(n * 3 * Ci * 4), w_bytes = align256(int64_t(Co) * V * 3 * Ci * 4);
+  const int64_t x_bytes = align256(n_src * 3 * Ci * 4), w_bytes = align256(int64_t(Co) * V * 3 * Ci * 4);
   if (workspace_bytes < kWsHeader + x_bytes + w_bytes) return FGB_E_WORKSPACE;
   float* x3 = reinterpret_cast<float*>(scratch);
   float* w3 = reinterpret_cast<float*>(scratch + x_bytes);
-  int rc = launch_split3(static_cast<const float*>(feats), x3, n, Ci, kSplitActivations, s);
+  int rc = FGB_OK;
+  if (n_src > 0) rc = launch_split3(static_cast<const float*>(feats), x3, n_src, Ci, kSplitActivations, s);
   if (rc != FGB_OK) return rc;
   rc = launch_split3(static_cast<const float*>(weight), w3, int64_t(Co) * V, Ci, kSplitWeights, s);
   if (rc != FGB_OK) return rc;
   return run_igemm(x3, w3, bias, neighbor_map, sorted_idx, tile_masks, block_order, ticket, out, n, 3 * Ci, Co, V, FGB_F32_TF32, 0, status, s);
 }
 
-extern "C" int fgb_subm_conv_dgrad(const void* grad_out, const void* weight, const uint32_t* neighbor_map,
-                                   const int64_t* sorted_idx, const uint32_t* tile_masks, const uint32_t* block_order,
-                                   void* grad_feats, int64_t n, int Ci, int Co, int V, int dtype, void* workspace,
-                                   int64_t workspace_bytes, int32_t* status, void* stream) {
-  using namespace fgb;
+}  // namespace fgb
+
+extern "C" int fgb_subm_conv_fprop(const void* feats, const void* weight, const void* bias, const uint32_t* neighbor_map,
+                                   const int64_t* sorted_idx, const uint32_t* tile_masks, const uint32_t* block_order, void* out,
+                                   int64_t n, int Ci, int Co, int V, int dtype, void* workspace, int64_t workspace_bytes,
+                                   int32_t* status, void* stream) {
+  return fgb::fprop_impl(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, out, n, n, Ci, Co, V, dtype, workspace,
+                         workspace_bytes, status, stream);
+}
+
+extern "C" int fgb_sparse_conv_fprop(const void* feats, const void* weight, const void* bias, const uint32_t* neighbor_map,
+                                     const int64_t* sorted_idx, const uint32_t* tile_masks, const uint32_t* block_order, void* out,
+                                     int64_t n_out, int64_t n_in, int Ci, int Co, int V, int dtype, void* workspace,
+                                     int64_t workspace_bytes, int32_t* status, void* stream) {
+  return fgb::fprop_impl(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, out, n_out, n_in, Ci, Co, V, dtype,
+                         workspace, workspace_bytes, status, stream);
+}
+
+namespace fgb {
+
+// n rows of the map / of `grad_feats`; n_src rows of `grad_out`; mirror = the map is the forward map of a submanifold
+// conv, whose row for offset v is the backward map's row for offset V-1-v
+static int dgrad_impl(const void* grad_out, const void* weight, const uint32_t* neighbor_map, const int64_t* sorted_idx,
+                      const uint32_t* tile_masks, const uint32_t* block_order, void* grad_feats, int64_t n, int64_t n_src, int Ci, int Co,
+                      int V, int dtype, int mirror, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
   const int eb = elem_bytes(dtype);
   if (eb == 0) return FGB_E_DTYPE;
-  if (n < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
+  if (n < 0 || n_src < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
   if (n == 0) return FGB_OK;
   if (!weight || !workspace) return FGB_E_NULL;
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return FGB_E_ALIGN;
   const int64_t wt_bytes = align256(int64_t(Ci) * V * Co * eb);
   const bool ieee = dtype == FGB_F32_IEEE;
   const int64_t w3_bytes = ieee ? align256(int64_t(Ci) * V * 3 * Co * 4) : 0;
-  const int64_t g3_bytes = ieee ? align256(n * 3 * Co * 4) : 0;
+  const int64_t g3_bytes = ieee ? align256(n_src * 3 * Co * 4) : 0;
   if (workspace_bytes < kWsHeader + wt_bytes + w3_bytes + g3_bytes) return FGB_E_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint32_t* ticket = static_cast<uint32_t*>(workspace);
@@ -685,15 +707,33 @@ extern "C" int fgb_subm_conv_dgrad(const void* grad_out, const void* weight, con
   int rc = launch_status();
   if (rc != FGB_OK) return rc;
   if (!ieee)
-    return run_igemm(grad_out, wt, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, ticket, grad_feats, n, Co, Ci, V, dtype, 1,
-                     status, s);
+    return run_igemm(grad_out, wt, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, ticket, grad_feats, n, Co, Ci, V, dtype,
+                     mirror, status, s);
   if (!grad_out) return FGB_E_NULL;
   float* w3 = reinterpret_cast<float*>(wt + wt_bytes);
   float* g3 = reinterpret_cast<float*>(wt + wt_bytes + w3_bytes);
   rc = launch_split3(reinterpret_cast<const float*>(wt), w3, int64_t(Ci) * V, Co, kSplitWeights, s);
   if (rc != FGB_OK) return rc;
-  rc = launch_split3(static_cast<const float*>(grad_out), g3, n, Co, kSplitActivations, s);
+  if (n_src > 0) rc = launch_split3(static_cast<const float*>(grad_out), g3, n_src, Co, kSplitActivations, s);
   if (rc != FGB_OK) return rc;
-  return run_igemm(g3, w3, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, ticket, grad_feats, n, 3 * Co, Ci, V, FGB_F32_TF32, 1,
-                   status, s);
+  return run_igemm(g3, w3, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, ticket, grad_feats, n, 3 * Co, Ci, V, FGB_F32_TF32,
+                   mirror, status, s);
+}
+
+}  // namespace fgb
+
+extern "C" int fgb_subm_conv_dgrad(const void* grad_out, const void* weight, const uint32_t* neighbor_map,
+                                   const int64_t* sorted_idx, const uint32_t* tile_masks, const uint32_t* block_order,
+                                   void* grad_feats, int64_t n, int Ci, int Co, int V, int dtype, void* workspace,
+                                   int64_t workspace_bytes, int32_t* status, void* stream) {
+  return fgb::dgrad_impl(grad_out, weight, neighbor_map, sorted_idx, tile_masks, block_order, grad_feats, n, n, Ci, Co, V, dtype, 1,
+                         workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int fgb_sparse_conv_dgrad(const void* grad_out, const void* weight, const uint32_t* neighbor_map_bwd,
+                                     const int64_t* sorted_idx_bwd, const uint32_t* tile_masks_bwd, const uint32_t* block_order_bwd,
+                                     void* grad_feats, int64_t n_in, int64_t n_out, int Ci, int Co, int V, int dtype, void* workspace,
+                                     int64_t workspace_bytes, int32_t* status, void* stream) {
+  return fgb::dgrad_impl(grad_out, weight, neighbor_map_bwd, sorted_idx_bwd, tile_masks_bwd, block_order_bwd, grad_feats, n_in, n_out, Ci,
+                         Co, V, dtype, 0, workspace, workspace_bytes, status, stream);
 }

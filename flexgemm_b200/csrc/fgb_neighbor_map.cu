@@ -19,23 +19,6 @@
 
 namespace fgb {
 
-__device__ __forceinline__ uint32_t fmix32(uint32_t k) {
-  k ^= k >> 16;
-  k *= 0x85ebca6bu;
-  k ^= k >> 13;
-  k *= 0xc2b2ae35u;
-  k ^= k >> 16;
-  return k;
-}
-__device__ __forceinline__ uint32_t fmix64_hi(uint64_t k) {
-  k ^= k >> 33;
-  k *= 0xff51afd7ed558ccdULL;
-  k ^= k >> 33;
-  k *= 0xc4ceb9fe1a85ec53ULL;
-  k ^= k >> 33;
-  return static_cast<uint32_t>(k >> 32) ^ static_cast<uint32_t>(k);
-}
-
 template <int kKeyBits>
 struct Table;
 
@@ -136,16 +119,26 @@ __global__ void __launch_bounds__(kMapBlock) hash_insert_kernel(const int4* __re
 
 struct Stencil {
   int Kw, Kh, Kd, Dw, Dh, Dd, V;
+  int Sw = 1, Sh = 1, Sd = 1;     // generic sparse conv only: stride
+  int Pw = 0, Ph = 0, Pd = 0;     // generic sparse conv only: padding
 };
 
 // One CTA per 256 voxels; thread t handles the flattened (voxel, offset) items
 // t, t+256, ... of the CTA, i.e. exactly the words t, t+256, ... of the CTA's
 // slice of the map.
-template <int kKeyBits>
+//
+// kGeneral = false: submanifold conv.  The rows are the table's own voxels, the
+// probed coordinate is coords[i] + (k - K/2) * dilation and the centre offset
+// is the row itself.
+// kGeneral = true: generic sparse conv.  The rows are output voxels, the table
+// holds the input voxels, the probed coordinate is coords[i] * stride - padding
+// + k * dilation, and every hit is also scattered into the backward map
+// nbr_bwd[input row, v] = output row (when nbr_bwd is non-null).
+template <int kKeyBits, bool kGeneral>
 __global__ void __launch_bounds__(kMapBlock)
     subm_lookup_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, Stencil st, void* table_mem, uint32_t slots,
-                       uint32_t* __restrict__ nbr, int32_t* __restrict__ gray_out, int32_t* __restrict__ binary_out,
-                       uint32_t* __restrict__ block_counts, uint32_t nblk) {
+                       uint32_t* __restrict__ nbr, uint32_t* __restrict__ nbr_bwd, int32_t* __restrict__ gray_out,
+                       int32_t* __restrict__ binary_out, uint32_t* __restrict__ block_counts, uint32_t nblk) {
   __shared__ int4 s_coord[kMapBlock];
   __shared__ uint32_t s_gray[kMapBlock];
   __shared__ uint32_t s_count[32];
@@ -154,13 +147,18 @@ __global__ void __launch_bounds__(kMapBlock)
   const uint32_t nv = min(static_cast<uint32_t>(kMapBlock), n - n0);
   const int t = threadIdx.x;
   const int V = st.V;
-  if (t < nv) s_coord[t] = __ldg(&coords[n0 + t]);
+  if (t < nv) {
+    int4 c = __ldg(&coords[n0 + t]);
+    if constexpr (kGeneral) c.y *= st.Sw, c.z *= st.Sh, c.w *= st.Sd;
+    s_coord[t] = c;
+  }
   s_gray[t] = 0;
   if (t < 32) {
     s_count[t] = 0;
     const int KhKd = st.Kh * st.Kd;
     const int kx = t / KhKd, ky = (t / st.Kd) % st.Kh, kz = t % st.Kd;
-    s_delta[t] = make_int4((kx - st.Kw / 2) * st.Dw, (ky - st.Kh / 2) * st.Dh, (kz - st.Kd / 2) * st.Dd, 0);
+    if constexpr (kGeneral) s_delta[t] = make_int4(kx * st.Dw - st.Pw, ky * st.Dh - st.Ph, kz * st.Dd - st.Pd, 0);
+    else s_delta[t] = make_int4((kx - st.Kw / 2) * st.Dw, (ky - st.Kh / 2) * st.Dh, (kz - st.Kd / 2) * st.Dd, 0);
   }
   __syncthreads();
 
@@ -175,7 +173,7 @@ __global__ void __launch_bounds__(kMapBlock)
   int v = t - lv * V;
   for (uint32_t item = t; item < items; item += kMapBlock) {
     uint32_t val;
-    if (v == centre) {
+    if (!kGeneral && v == centre) {
       val = n0 + lv;
     } else {
       const int4 c = s_coord[lv];
@@ -186,6 +184,9 @@ __global__ void __launch_bounds__(kMapBlock)
     }
     out[item] = val;
     if (val != kInvalid) {
+      if constexpr (kGeneral) {
+        if (nbr_bwd) nbr_bwd[static_cast<size_t>(val) * V + v] = n0 + lv;
+      }
       atomicOr(&s_gray[lv], 1u << v);
       atomicAdd(&s_count[v], 1u);
     }
@@ -267,11 +268,59 @@ static int build_impl(const int32_t* coords, uint32_t n, Grid3 g, Stencil st, vo
                       int32_t* gray, int32_t* binary, uint32_t* block_counts, uint32_t* seg, int32_t* status, cudaStream_t s) {
   const uint32_t nblk = static_cast<uint32_t>(ceil_div(n, kMapBlock));
   hash_insert_kernel<kKeyBits><<<nblk, kMapBlock, 0, s>>>(reinterpret_cast<const int4*>(coords), n, g, table, slots, status);
-  subm_lookup_kernel<kKeyBits><<<nblk, kMapBlock, 0, s>>>(reinterpret_cast<const int4*>(coords), n, g, st, table, slots, nbr, gray,
-                                                         binary, block_counts, nblk);
+  subm_lookup_kernel<kKeyBits, false><<<nblk, kMapBlock, 0, s>>>(reinterpret_cast<const int4*>(coords), n, g, st, table, slots, nbr,
+                                                                nullptr, gray, binary, block_counts, nblk);
   block_scan_kernel<<<st.V, 1024, 0, s>>>(block_counts, nblk, seg);
   seg_prefix_kernel<<<1, 32, 0, s>>>(seg, st.V);
   return launch_status();
+}
+
+// generic sparse conv: table over the input voxels, rows = output voxels
+template <int kKeyBits>
+static int build_general_impl(const int32_t* in_coords, uint32_t n_in, const int32_t* out_coords, uint32_t n_out, Grid3 g, Stencil st,
+                              void* table, uint32_t slots, uint32_t* nbr, uint32_t* nbr_bwd, int32_t* gray, int32_t* binary,
+                              uint32_t* block_counts, uint32_t* seg, int32_t* status, cudaStream_t s) {
+  if (n_in > 0)
+    hash_insert_kernel<kKeyBits><<<static_cast<unsigned>(ceil_div(n_in, kMapBlock)), kMapBlock, 0, s>>>(
+        reinterpret_cast<const int4*>(in_coords), n_in, g, table, slots, status);
+  const uint32_t nblk = static_cast<uint32_t>(ceil_div(n_out, kMapBlock));
+  subm_lookup_kernel<kKeyBits, true><<<nblk, kMapBlock, 0, s>>>(reinterpret_cast<const int4*>(out_coords), n_out, g, st, table, slots,
+                                                               nbr, nbr_bwd, gray, binary, block_counts, nblk);
+  block_scan_kernel<<<st.V, 1024, 0, s>>>(block_counts, nblk, seg);
+  seg_prefix_kernel<<<1, 32, 0, s>>>(seg, st.V);
+  return launch_status();
+}
+
+// gray[i] = mask of the valid offsets of map row i, binary[i] = its Gray-to-binary decode
+__global__ void __launch_bounds__(256) gray_from_map_kernel(const uint32_t* __restrict__ nbr, uint32_t n, int V,
+                                                            int32_t* __restrict__ gray_out, int32_t* __restrict__ binary_out) {
+  // a warp covers 32 consecutive map words at a time; lanes vote the validity bits of each row
+  __shared__ uint32_t s_gray[256];
+  const uint32_t n0 = blockIdx.x * 256u;
+  const uint32_t nv = min(256u, n - n0);
+  const int t = threadIdx.x;
+  s_gray[t] = 0;
+  __syncthreads();
+  const uint32_t items = nv * V;
+  const uint32_t* in = nbr + static_cast<size_t>(n0) * V;
+  for (uint32_t item = t; item < items; item += 256) {
+    if (__ldg(&in[item]) != kInvalid) {
+      const uint32_t lv = item / V;
+      atomicOr(&s_gray[lv], 1u << (item - lv * V));
+    }
+  }
+  __syncthreads();
+  if (t < nv) {
+    const uint32_t gray = s_gray[t];
+    uint32_t binary = gray;
+    binary ^= binary >> 1;
+    binary ^= binary >> 2;
+    binary ^= binary >> 4;
+    binary ^= binary >> 8;
+    binary ^= binary >> 16;
+    gray_out[n0 + t] = static_cast<int32_t>(gray);
+    binary_out[n0 + t] = static_cast<int32_t>(binary);
+  }
 }
 
 }  // namespace fgb
@@ -313,4 +362,55 @@ extern "C" int fgb_subm_build_neighbor_map(const int32_t* coords, int64_t n, int
                           binary_code, block_counts, valid_signal_seg, status, s);
   return build_impl<64>(coords, static_cast<uint32_t>(n), g, st, table, static_cast<uint32_t>(slots), neighbor_map, gray_code,
                         binary_code, block_counts, valid_signal_seg, status, s);
+}
+
+extern "C" int fgb_sparse_build_neighbor_map(const int32_t* in_coords, int64_t n_in, const int32_t* out_coords, int64_t n_out, int W,
+                                             int H, int D, int Kw, int Kh, int Kd, int Sw, int Sh, int Sd, int Pw, int Ph, int Pd,
+                                             int Dw, int Dh, int Dd, void* table, int64_t slots, int key_bits, uint32_t* neighbor_map,
+                                             uint32_t* neighbor_map_bwd, int32_t* gray_code, int32_t* binary_code,
+                                             uint32_t* block_counts, uint32_t* valid_signal_seg, int32_t* status, void* stream) {
+  using namespace fgb;
+  const int64_t lim = (int64_t(1) << 32) - 1;
+  if (n_in < 0 || n_in >= lim || n_out < 0 || n_out >= lim) return FGB_E_SIZE;
+  if (W <= 0 || H <= 0 || D <= 0) return FGB_E_SIZE;
+  if (Kw <= 0 || Kh <= 0 || Kd <= 0 || Sw <= 0 || Sh <= 0 || Sd <= 0 || Dw <= 0 || Dh <= 0 || Dd <= 0) return FGB_E_SIZE;
+  if (Pw < 0 || Ph < 0 || Pd < 0) return FGB_E_SIZE;
+  const int64_t V = int64_t(Kw) * Kh * Kd;
+  if (V > 32) return FGB_E_SIZE;
+  if (key_bits != 32 && key_bits != 64) return FGB_E_DTYPE;
+  if (slots < n_in || slots < 1 || slots >= (int64_t(1) << 31)) return FGB_E_SIZE;
+  if (valid_signal_seg == nullptr) return FGB_E_NULL;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc;
+  if (neighbor_map_bwd && n_in > 0) {
+    rc = cuda_status(cudaMemsetAsync(neighbor_map_bwd, 0xFF, static_cast<size_t>(n_in) * V * sizeof(uint32_t), s));
+    if (rc != FGB_OK) return rc;
+  }
+  if (n_out == 0) return cuda_status(cudaMemsetAsync(valid_signal_seg, 0, (V + 1) * sizeof(uint32_t), s));
+  if (!out_coords || !table || !neighbor_map || !gray_code || !binary_code || !block_counts) return FGB_E_NULL;
+  if (n_in > 0 && !in_coords) return FGB_E_NULL;
+  if ((reinterpret_cast<uintptr_t>(in_coords) | reinterpret_cast<uintptr_t>(out_coords)) & 15) return FGB_E_ALIGN;
+  if (reinterpret_cast<uintptr_t>(table) & 7) return FGB_E_ALIGN;
+  rc = cuda_status(cudaMemsetAsync(table, 0xFF, static_cast<size_t>(fgb_hash_table_bytes(slots, key_bits)), s));
+  if (rc != FGB_OK) return rc;
+  const Grid3 g{W, H, D};
+  Stencil st{Kw, Kh, Kd, Dw, Dh, Dd, static_cast<int>(V)};
+  st.Sw = Sw, st.Sh = Sh, st.Sd = Sd, st.Pw = Pw, st.Ph = Ph, st.Pd = Pd;
+  if (key_bits == 32)
+    return build_general_impl<32>(in_coords, static_cast<uint32_t>(n_in), out_coords, static_cast<uint32_t>(n_out), g, st, table,
+                                  static_cast<uint32_t>(slots), neighbor_map, neighbor_map_bwd, gray_code, binary_code, block_counts,
+                                  valid_signal_seg, status, s);
+  return build_general_impl<64>(in_coords, static_cast<uint32_t>(n_in), out_coords, static_cast<uint32_t>(n_out), g, st, table,
+                                static_cast<uint32_t>(slots), neighbor_map, neighbor_map_bwd, gray_code, binary_code, block_counts,
+                                valid_signal_seg, status, s);
+}
+
+extern "C" int fgb_pp_gray_code(const uint32_t* neighbor_map, int64_t n, int V, int32_t* gray_code, int32_t* binary_code, void* stream) {
+  using namespace fgb;
+  if (n < 0 || n >= (int64_t(1) << 32) - 1 || V < 1 || V > 32) return FGB_E_SIZE;
+  if (n == 0) return FGB_OK;
+  if (!neighbor_map || !gray_code || !binary_code) return FGB_E_NULL;
+  gray_from_map_kernel<<<static_cast<unsigned>(ceil_div(n, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      neighbor_map, static_cast<uint32_t>(n), V, gray_code, binary_code);
+  return launch_status();
 }

@@ -456,20 +456,24 @@ extern "C" int fgb_wgrad_default_splitk(int64_t n_pairs, int Ci, int Co, int V, 
 }
 
 extern "C" int64_t fgb_conv_workspace_bytes(int pass, int64_t n, int Ci, int Co, int V, int dtype, int splitk) {
+  return fgb_sparse_conv_workspace_bytes(pass, n, n, Ci, Co, V, dtype, splitk);
+}
+
+extern "C" int64_t fgb_sparse_conv_workspace_bytes(int pass, int64_t n_out, int64_t n_in, int Ci, int Co, int V, int dtype, int splitk) {
   using namespace fgb;
   const int eb = elem_bytes(dtype);
   if (eb == 0) return FGB_E_DTYPE;
-  if (n < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
+  if (n_out < 0 || n_in < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
   const int64_t w_elems = int64_t(Ci) * V * Co;
   const bool ieee = dtype == FGB_F32_IEEE;
   switch (pass) {
     case 0:  // header with the ticket counter (+ fp32-accurate mode: tripled activations and weights)
-      return 256 + (ieee ? align256(n * 3 * Ci * 4) + align256(w_elems * 3 * 4) : 0);
+      return 256 + (ieee ? align256(n_in * 3 * Ci * 4) + align256(w_elems * 3 * 4) : 0);
     case 1:  // header, re-laid-out weight (+ its tripled copy and the tripled grad_out)
-      return 256 + align256(w_elems * eb) + (ieee ? align256(w_elems * 3 * 4) + align256(n * 3 * Co * 4) : 0);
+      return 256 + align256(w_elems * eb) + (ieee ? align256(w_elems * 3 * 4) + align256(n_out * 3 * Co * 4) : 0);
     case 2:  // slabs [Co, Ci] for up to (splitk + 1) * V units (+ hi/lo copies of both operands)
       if (splitk < 1 || splitk > 1024) return FGB_E_SIZE;
-      return align256(w_elems * 4 * (int64_t(splitk) + 1)) + (ieee ? 2 * align256(n * Ci * 4) + 2 * align256(n * Co * 4) : 0);
+      return align256(w_elems * 4 * (int64_t(splitk) + 1)) + (ieee ? 2 * align256(n_in * Ci * 4) + 2 * align256(n_out * Co * 4) : 0);
     default:
       return FGB_E_SIZE;
   }
@@ -533,10 +537,19 @@ extern "C" int fgb_subm_conv_wgrad(const void* grad_out, const void* feats, cons
                                    const uint32_t* valid_signal_o, const uint32_t* valid_signal_seg, void* grad_weight,
                                    float* grad_weight_f32, int64_t n, int64_t n_pairs, int Ci, int Co, int V, int dtype, int splitk,
                                    void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+  return fgb_sparse_conv_wgrad(grad_out, feats, valid_signal_i, valid_signal_o, valid_signal_seg, grad_weight, grad_weight_f32, n, n,
+                               n_pairs, Ci, Co, V, dtype, splitk, workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int fgb_sparse_conv_wgrad(const void* grad_out, const void* feats, const uint32_t* valid_signal_i,
+                                     const uint32_t* valid_signal_o, const uint32_t* valid_signal_seg, void* grad_weight,
+                                     float* grad_weight_f32, int64_t n_out, int64_t n_in, int64_t n_pairs, int Ci, int Co, int V,
+                                     int dtype, int splitk, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
   using namespace fgb;
   const int eb = elem_bytes(dtype);
   if (eb == 0) return FGB_E_DTYPE;
-  if (n < 0 || n_pairs < 0 || n_pairs > n * V || Ci <= 0 || Co <= 0 || V < 1 || V > 32 || splitk < 1 || splitk > 1024) return FGB_E_SIZE;
+  if (n_out < 0 || n_in < 0 || n_pairs < 0 || n_pairs > n_out * V || Ci <= 0 || Co <= 0 || V < 1 || V > 32 || splitk < 1 || splitk > 1024)
+    return FGB_E_SIZE;
   if ((Ci * eb) % 16 || (Co * eb) % 16) return FGB_E_ALIGN;
   if (!valid_signal_seg || !workspace) return FGB_E_NULL;
   if (n_pairs > 0 && (!grad_out || !feats || !valid_signal_i || !valid_signal_o)) return FGB_E_NULL;
@@ -545,7 +558,7 @@ extern "C" int fgb_subm_conv_wgrad(const void* grad_out, const void* feats, cons
        reinterpret_cast<uintptr_t>(grad_weight_f32)) & 15)
     return FGB_E_ALIGN;
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return FGB_E_ALIGN;
-  if (workspace_bytes < fgb_conv_workspace_bytes(2, n, Ci, Co, V, dtype, splitk)) return FGB_E_WORKSPACE;
+  if (workspace_bytes < fgb_sparse_conv_workspace_bytes(2, n_out, n_in, Ci, Co, V, dtype, splitk)) return FGB_E_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* slabs = static_cast<float*>(workspace);
   if (dtype != FGB_F32_IEEE)
@@ -554,12 +567,13 @@ extern "C" int fgb_subm_conv_wgrad(const void* grad_out, const void* feats, cons
   // fp32-accurate: g_hi*x_hi + g_hi*x_lo + g_lo*x_hi, three passes adding into the fp32 output
   char* base = static_cast<char*>(workspace) + align256(int64_t(Ci) * V * Co * 4 * (int64_t(splitk) + 1));
   float* x_hi = reinterpret_cast<float*>(base);
-  float* x_lo = reinterpret_cast<float*>(base + align256(n * Ci * 4));
-  float* g_hi = reinterpret_cast<float*>(base + 2 * align256(n * Ci * 4));
-  float* g_lo = reinterpret_cast<float*>(base + 2 * align256(n * Ci * 4) + align256(n * Co * 4));
-  int rc = launch_split2(static_cast<const float*>(feats), x_hi, x_lo, n * Ci, s);
+  float* x_lo = reinterpret_cast<float*>(base + align256(n_in * Ci * 4));
+  float* g_hi = reinterpret_cast<float*>(base + 2 * align256(n_in * Ci * 4));
+  float* g_lo = reinterpret_cast<float*>(base + 2 * align256(n_in * Ci * 4) + align256(n_out * Co * 4));
+  int rc = FGB_OK;
+  if (n_in > 0) rc = launch_split2(static_cast<const float*>(feats), x_hi, x_lo, n_in * Ci, s);
   if (rc != FGB_OK) return rc;
-  rc = launch_split2(static_cast<const float*>(grad_out), g_hi, g_lo, n * Co, s);
+  if (n_out > 0) rc = launch_split2(static_cast<const float*>(grad_out), g_hi, g_lo, n_out * Co, s);
   if (rc != FGB_OK) return rc;
   const float* ga[3] = {g_hi, g_hi, g_lo};
   const float* xa[3] = {x_hi, x_lo, x_hi};

@@ -123,6 +123,104 @@ def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table:
     return out
 
 
+def sparse_out_grid(shape, ksize, stride, padding, dilation) -> Tuple[int, int, int]:
+    import ctypes
+    _, _, W, H, D = [int(s) for s in shape]
+    wo, ho, do = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    rc = _cabi.lib().fgb_sparse_out_grid(W, H, D, *[int(v) for v in (*ksize, *stride, *padding, *dilation)],
+                                         ctypes.byref(wo), ctypes.byref(ho), ctypes.byref(do))
+    _cabi.check(rc, "fgb_sparse_out_grid")
+    return wo.value, ho.value, do.value
+
+
+def sparse_out_coords(coords: torch.Tensor, shape, ksize, stride, padding, dilation, ratio: float, mode: int) -> torch.Tensor:
+    """Output coordinates [L,4] int32 of a generic sparse conv, sorted by the
+    serialisation key of ``mode`` (0 bxyz, 1 Morton, 2 Hilbert).  One host read
+    (the count) between the two library calls."""
+    _require_cuda(coords, "coords")
+    lib = _cabi.lib()
+    dev = coords.device
+    n = coords.shape[0]
+    B, _, W, H, D = [int(s) for s in shape]
+    geom = [int(v) for v in (*ksize, *stride, *padding, *dilation)]
+    Wo, Ho, Do = sparse_out_grid(shape, ksize, stride, padding, dilation)
+    if n == 0 or min(Wo, Ho, Do) <= 0:
+        return torch.empty((0, 4), dtype=torch.int32, device=dev)
+    V = geom[0] * geom[1] * geom[2]
+    vol = B * Wo * Ho * Do
+    key_bits = 32 if vol < 2 ** 32 - 1 else 64
+    # as many slots as the reference gives its set (ratio * V / prod(stride) per input voxel), but never fewer
+    # than the candidates that can be distinct
+    import math
+    per_axis = [-(-k // (s // math.gcd(s, d))) for k, s, d in zip(geom[0:3], geom[3:6], geom[9:12])]
+    distinct = min(n * per_axis[0] * per_axis[1] * per_axis[2], vol)
+    slots = max(int(ratio * V / (geom[3] * geom[4] * geom[5]) * n), int(1.1 * distinct) + 16)
+    words = torch.empty((2 * slots * (key_bits // 8) + 7) // 8 + 1, dtype=torch.int64, device=dev)
+    set_mem, keys = words, words[(slots * (key_bits // 8) + 7) // 8:]
+    count = torch.zeros(2, dtype=torch.int32, device=dev)  # [count, status]
+    rc = lib.fgb_sparse_out_coords_collect(_ptr(coords), n, W, H, D, *geom, set_mem.data_ptr(), slots, key_bits, keys.data_ptr(),
+                                           count.data_ptr(), count.data_ptr() + 4, _stream(dev))
+    _cabi.check(rc, "fgb_sparse_out_coords_collect")
+    _count(1)
+    host = count.cpu()
+    raise_for_status(int(host[1]))
+    L = int(host[0])
+    out = torch.empty((L, 4), dtype=torch.int32, device=dev)
+    if L == 0:
+        return out
+    nbytes = _cabi.check_size(lib.fgb_sparse_out_coords_workspace_bytes(L, key_bits, int(mode)), "fgb_sparse_out_coords_workspace_bytes")
+    ws = workspace(dev, "out_coords", nbytes)
+    coord_bits = max((max(W, H, D) - 1).bit_length(), 1)
+    rc = lib.fgb_sparse_out_coords_finalize(keys.data_ptr(), L, key_bits, int(mode), coord_bits, B, W, H, D, *geom, ws.data_ptr(),
+                                            ws.numel() * 8, out.data_ptr(), _stream(dev))
+    _cabi.check(rc, "fgb_sparse_out_coords_finalize")
+    _count(2 if mode else 1)
+    return out
+
+
+def sparse_build_neighbor_map(coords: torch.Tensor, out_coords: torch.Tensor, shape, ksize, stride, padding, dilation,
+                              table: torch.Tensor, key_bits: int, slots: int, include_bwd: bool) -> Dict[str, torch.Tensor]:
+    """Forward map [L,V] (+ backward map [M,V]) of a generic sparse conv with the
+    same side products as ``subm_build_neighbor_map`` (they describe the forward map)."""
+    _require_cuda(coords, "coords")
+    lib = _cabi.lib()
+    dev = coords.device
+    m, n = coords.shape[0], out_coords.shape[0]
+    _, _, W, H, D = [int(s) for s in shape]
+    geom = [int(v) for v in (*ksize, *stride, *padding, *dilation)]
+    V = geom[0] * geom[1] * geom[2]
+    nblk = _cabi.check_size(lib.fgb_map_num_blocks(n), "fgb_map_num_blocks")
+    meta = torch.zeros(V + 2, dtype=torch.uint32, device=dev)
+    out = {
+        "neighbor_map": torch.empty((n, V), dtype=torch.uint32, device=dev),
+        "neighbor_map_bwd": torch.empty((m, V), dtype=torch.uint32, device=dev) if include_bwd else None,
+        "gray_code": torch.empty(n, dtype=torch.int32, device=dev),
+        "binary_code": torch.empty(n, dtype=torch.int32, device=dev),
+        "block_offsets": torch.empty(max(V * nblk, 1), dtype=torch.uint32, device=dev),
+        "valid_signal_seg": meta[:V + 1],
+        "meta": meta,
+    }
+    rc = lib.fgb_sparse_build_neighbor_map(
+        _ptr(coords), m, _ptr(out_coords), n, W, H, D, *geom, table.data_ptr(), int(slots), int(key_bits),
+        _ptr(out["neighbor_map"]), _ptr(out["neighbor_map_bwd"]), _ptr(out["gray_code"]), _ptr(out["binary_code"]),
+        out["block_offsets"].data_ptr(), meta.data_ptr(), meta.data_ptr() + 4 * (V + 1), _stream(dev))
+    _cabi.check(rc, "fgb_sparse_build_neighbor_map")
+    _count(4)
+    return out
+
+
+def gray_code_from_map(neighbor_map: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(gray_code, binary_code), int32 [rows] each, of an existing map."""
+    dev = neighbor_map.device
+    n, V = neighbor_map.shape
+    gray = torch.empty(n, dtype=torch.int32, device=dev)
+    binary = torch.empty(n, dtype=torch.int32, device=dev)
+    rc = _cabi.lib().fgb_pp_gray_code(_ptr(neighbor_map), n, V, _ptr(gray), _ptr(binary), _stream(dev))
+    _cabi.check(rc, "fgb_pp_gray_code")
+    _count(1)
+    return gray, binary
+
+
 def raise_for_status(code: int) -> None:
     if code != 0:
         what = {_cabi.S_TABLE_FULL: "hash table full (raise the hashmap ratio)",
@@ -208,37 +306,57 @@ def conv_tile_rows() -> int:
 
 
 def conv_fprop(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks, order=None) -> torch.Tensor:
-    """feats [N,Ci], weight_cvc [Co,V,Ci] -> out [N,Co]."""
+    """feats [N_in,Ci], weight_cvc [Co,V,Ci], neighbor_map [N_out,V] -> out [N_out,Co]
+    (N_in = N_out for a submanifold conv)."""
     lib = _cabi.lib()
     dev = feats.device
-    n, Ci = feats.shape
+    n_in, Ci = feats.shape
+    n = neighbor_map.shape[0]
     Co, V, _ = weight_cvc.shape
     code = dtype_code(feats.dtype)
     out = torch.empty((n, Co), dtype=feats.dtype, device=dev)
-    nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(0, n, Ci, Co, V, code, 1), "fgb_conv_workspace_bytes")
+    nbytes = _cabi.check_size(lib.fgb_sparse_conv_workspace_bytes(0, n, n_in, Ci, Co, V, code, 1), "fgb_sparse_conv_workspace_bytes")
     ws = workspace(dev, "fprop", nbytes)
-    rc = lib.fgb_subm_conv_fprop(_ptr(feats), weight_cvc.data_ptr(), _ptr(bias), _ptr(neighbor_map), _ptr(sorted_idx),
-                                 _ptr(masks), _ptr(order), _ptr(out), n, Ci, Co, V, code, ws.data_ptr(), ws.numel() * 8,
-                                 status_word(dev).data_ptr(), _stream(dev))
-    _cabi.check(rc, "fgb_subm_conv_fprop")
+    if n_in == n:
+        rc = lib.fgb_subm_conv_fprop(_ptr(feats), weight_cvc.data_ptr(), _ptr(bias), _ptr(neighbor_map), _ptr(sorted_idx),
+                                     _ptr(masks), _ptr(order), _ptr(out), n, Ci, Co, V, code, ws.data_ptr(), ws.numel() * 8,
+                                     status_word(dev).data_ptr(), _stream(dev))
+        _cabi.check(rc, "fgb_subm_conv_fprop")
+    else:
+        rc = lib.fgb_sparse_conv_fprop(_ptr(feats), weight_cvc.data_ptr(), _ptr(bias), _ptr(neighbor_map), _ptr(sorted_idx),
+                                       _ptr(masks), _ptr(order), _ptr(out), n, n_in, Ci, Co, V, code, ws.data_ptr(),
+                                       ws.numel() * 8, status_word(dev).data_ptr(), _stream(dev))
+        _cabi.check(rc, "fgb_sparse_conv_fprop")
     _count(1)
     return out
 
 
-def conv_dgrad(grad_out, weight_cvc, neighbor_map, sorted_idx, masks, order=None) -> torch.Tensor:
-    """grad_out [N,Co], weight_cvc [Co,V,Ci] -> grad_feats [N,Ci]."""
+def conv_dgrad(grad_out, weight_cvc, neighbor_map, sorted_idx, masks, order=None, mirror: bool = True) -> torch.Tensor:
+    """grad_out [N_out,Co], weight_cvc [Co,V,Ci] -> grad_feats [N_in,Ci].
+
+    ``mirror=True``: ``neighbor_map`` is the forward map of a submanifold conv
+    (N_in = N_out; offset v pairs with weight slot V-1-v).  ``mirror=False``:
+    it is the backward map [N_in, V] of a generic sparse conv (slot v)."""
     lib = _cabi.lib()
     dev = grad_out.device
-    n, Co = grad_out.shape
+    n_out, Co = grad_out.shape
+    n = neighbor_map.shape[0]
     _, V, Ci = weight_cvc.shape
     code = dtype_code(grad_out.dtype)
     out = torch.empty((n, Ci), dtype=grad_out.dtype, device=dev)
-    nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(1, n, Ci, Co, V, code, 1), "fgb_conv_workspace_bytes")
+    nbytes = _cabi.check_size(lib.fgb_sparse_conv_workspace_bytes(1, n_out, n, Ci, Co, V, code, 1), "fgb_sparse_conv_workspace_bytes")
     ws = workspace(dev, "dgrad", nbytes)
-    rc = lib.fgb_subm_conv_dgrad(_ptr(grad_out), weight_cvc.data_ptr(), _ptr(neighbor_map), _ptr(sorted_idx), _ptr(masks),
-                                 _ptr(order), _ptr(out), n, Ci, Co, V, code, ws.data_ptr(), ws.numel() * 8,
-                                 status_word(dev).data_ptr(), _stream(dev))
-    _cabi.check(rc, "fgb_subm_conv_dgrad")
+    if mirror:
+        assert n == n_out, "a mirrored (submanifold) dgrad needs as many map rows as grad_out rows"
+        rc = lib.fgb_subm_conv_dgrad(_ptr(grad_out), weight_cvc.data_ptr(), _ptr(neighbor_map), _ptr(sorted_idx), _ptr(masks),
+                                     _ptr(order), _ptr(out), n, Ci, Co, V, code, ws.data_ptr(), ws.numel() * 8,
+                                     status_word(dev).data_ptr(), _stream(dev))
+        _cabi.check(rc, "fgb_subm_conv_dgrad")
+    else:
+        rc = lib.fgb_sparse_conv_dgrad(_ptr(grad_out), weight_cvc.data_ptr(), _ptr(neighbor_map), _ptr(sorted_idx), _ptr(masks),
+                                       _ptr(order), _ptr(out), n, n_out, Ci, Co, V, code, ws.data_ptr(), ws.numel() * 8,
+                                       status_word(dev).data_ptr(), _stream(dev))
+        _cabi.check(rc, "fgb_sparse_conv_dgrad")
     _count(2)
     return out
 
@@ -248,8 +366,8 @@ def conv_wgrad(grad_out, feats, vs_i, vs_o, vs_seg, splitk: Optional[int] = None
     """-> (grad_weight [Co,V,Ci] in the feature dtype or None, fp32 copy or None)."""
     lib = _cabi.lib()
     dev = feats.device
-    n, Ci = feats.shape
-    Co = grad_out.shape[1]
+    n_in, Ci = feats.shape
+    n_out, Co = grad_out.shape
     V = vs_seg.shape[0] - 1
     code = dtype_code(feats.dtype)
     if splitk is None:
@@ -258,12 +376,19 @@ def conv_wgrad(grad_out, feats, vs_i, vs_o, vs_seg, splitk: Optional[int] = None
             _cabi.check(splitk, "fgb_wgrad_default_splitk")
     gw = torch.empty((Co, V, Ci), dtype=feats.dtype, device=dev) if want_dtype else None
     gw32 = torch.empty((Co, V, Ci), dtype=torch.float32, device=dev) if want_f32 else None
-    nbytes = _cabi.check_size(lib.fgb_conv_workspace_bytes(2, n, Ci, Co, V, code, splitk), "fgb_conv_workspace_bytes")
+    nbytes = _cabi.check_size(lib.fgb_sparse_conv_workspace_bytes(2, n_out, n_in, Ci, Co, V, code, splitk),
+                              "fgb_sparse_conv_workspace_bytes")
     ws = workspace(dev, "wgrad", nbytes)
-    rc = lib.fgb_subm_conv_wgrad(_ptr(grad_out), _ptr(feats), _ptr(vs_i), _ptr(vs_o), vs_seg.data_ptr(), _ptr(gw), _ptr(gw32),
-                                 n, int(vs_i.shape[0]), Ci, Co, V, code, int(splitk), ws.data_ptr(), ws.numel() * 8,
-                                 status_word(dev).data_ptr(), _stream(dev))
-    _cabi.check(rc, "fgb_subm_conv_wgrad")
+    if n_in == n_out:
+        rc = lib.fgb_subm_conv_wgrad(_ptr(grad_out), _ptr(feats), _ptr(vs_i), _ptr(vs_o), vs_seg.data_ptr(), _ptr(gw), _ptr(gw32),
+                                     n_out, int(vs_i.shape[0]), Ci, Co, V, code, int(splitk), ws.data_ptr(), ws.numel() * 8,
+                                     status_word(dev).data_ptr(), _stream(dev))
+        _cabi.check(rc, "fgb_subm_conv_wgrad")
+    else:
+        rc = lib.fgb_sparse_conv_wgrad(_ptr(grad_out), _ptr(feats), _ptr(vs_i), _ptr(vs_o), vs_seg.data_ptr(), _ptr(gw),
+                                       _ptr(gw32), n_out, n_in, int(vs_i.shape[0]), Ci, Co, V, code, int(splitk), ws.data_ptr(),
+                                       ws.numel() * 8, status_word(dev).data_ptr(), _stream(dev))
+        _cabi.check(rc, "fgb_sparse_conv_wgrad")
     _count(2)
     return gw, gw32
 

@@ -244,6 +244,96 @@ int fgb_subm_conv_bias_grad_noalloc(const void* grad_out, void* grad_bias, float
  * an all-reduced fp32 gradient. */
 int fgb_cast_from_f32(const float* src, void* dst, int64_t count, int dtype, void* stream);
 
+/* ------------------------------------------------------------------------
+ * Generic sparse convolution (stride / padding / dilation, output voxels that
+ * differ from the input voxels): the caller on either side of a submanifold
+ * conv in a network (down- and up-sampling).  Same hash table, sort,
+ * pair-list and GEMM kernels; separate forward and backward maps.
+ * Reference: flex_gemm/ops/spconv/sparse_conv3d.py:59-539,
+ * flex_gemm/kernels/cuda/spconv/sparse_neighbor_map.cu.
+ * --------------------------------------------------------------------- */
+
+/* Output grid extents: Wo = (W + 2*Pw - Dw*(Kw-1) - 1) / Sw + 1, etc.
+ * (sparse_neighbor_map.cu:89-91). */
+int fgb_sparse_out_grid(int W, int H, int D, int Kw, int Kh, int Kd, int Sw, int Sh, int Sd,
+                        int Pw, int Ph, int Pd, int Dw, int Dh, int Dd, int* Wo, int* Ho, int* Do);
+
+/* Output coordinates, step 1 of 2.  Every input voxel proposes, for every
+ * kernel offset k, the output voxel (c + P - k*Dil) / S when that is integral
+ * and inside the output grid; a hash set (`set`: `slots` words of key_bits
+ * bits, any contents) removes duplicates and `keys` (capacity `slots` words of
+ * key_bits bits) receives the flat (b, x, y, z) index of each distinct output
+ * voxel in arbitrary order; *count (device) = how many.  key_bits is 32 when
+ * B*Wo*Ho*Do < 2^32 - 1, else 64.  A set that fills up records
+ * FGB_S_TABLE_FULL.  Stands in for the insert half of
+ * hashmap_build_sparse_conv_out_coords (sparse_neighbor_map.cu:18-56, 103-124). */
+int fgb_sparse_out_coords_collect(const int32_t* in_coords, int64_t n_in, int W, int H, int D,
+                                  int Kw, int Kh, int Kd, int Sw, int Sh, int Sd,
+                                  int Pw, int Ph, int Pd, int Dw, int Dh, int Dd,
+                                  void* set, int64_t slots, int key_bits,
+                                  void* keys, uint32_t* count, int32_t* status, void* stream);
+
+/* Output coordinates, step 2 of 2 (after the caller has read *count): sorts
+ * the keys by serialisation key and decodes them to out_coords (int32
+ * [count, 4], rows (b, x, y, z)).  mode 0 = flat bxyz index, 1 = Morton code,
+ * 2 = Hilbert index; for modes 1 and 2 coord_bits is the bit length of
+ * max(W, H, D) - 1 and the batch index sits above 3*coord_bits bits
+ * (sparse_neighbor_map.cu:126-196, utils.h:24-106).  B = batch size. */
+int64_t fgb_sparse_out_coords_workspace_bytes(int64_t count, int key_bits, int mode);
+int fgb_sparse_out_coords_finalize(const void* keys, int64_t count, int key_bits, int mode, int coord_bits,
+                                   int B, int W, int H, int D, int Kw, int Kh, int Kd, int Sw, int Sh, int Sd,
+                                   int Pw, int Ph, int Pd, int Dw, int Dh, int Dd,
+                                   void* workspace, int64_t workspace_bytes, int32_t* out_coords, void* stream);
+
+/* Forward map neighbor_map[o, v] = row of the input voxel at
+ * out_coords[o] * S - P + k * Dil (v = (kx*Kh + ky)*Kd + kz) or 0xffffffff, and
+ * -- when neighbor_map_bwd is non-null -- the backward map
+ * neighbor_map_bwd[i, v] = o for every hit (other entries 0xffffffff).  The
+ * table (fgb_hash_table_bytes(slots, key_bits) bytes, slots >= n_in) is built
+ * over the input voxels.  gray_code / binary_code / block_counts /
+ * valid_signal_seg describe the FORWARD map exactly as in
+ * fgb_subm_build_neighbor_map (block_counts sized by fgb_map_num_blocks(n_out)).
+ * Stands in for hashmap_build_sparse_conv_neighbour_map
+ * (sparse_neighbor_map.cu:405-568). */
+int fgb_sparse_build_neighbor_map(const int32_t* in_coords, int64_t n_in,
+                                  const int32_t* out_coords, int64_t n_out,
+                                  int W, int H, int D, int Kw, int Kh, int Kd, int Sw, int Sh, int Sd,
+                                  int Pw, int Ph, int Pd, int Dw, int Dh, int Dd,
+                                  void* table, int64_t slots, int key_bits,
+                                  uint32_t* neighbor_map, uint32_t* neighbor_map_bwd,
+                                  int32_t* gray_code, int32_t* binary_code,
+                                  uint32_t* block_counts, uint32_t* valid_signal_seg,
+                                  int32_t* status, void* stream);
+
+/* gray_code / binary_code of an existing map (used for the backward map, whose
+ * entries are scattered and therefore cannot be summarised while it is built).
+ * Stands in for the mask half of ..._1_no_bwd (migemm_neighmap_pp.cu:58-82). */
+int fgb_pp_gray_code(const uint32_t* neighbor_map, int64_t n, int V,
+                     int32_t* gray_code, int32_t* binary_code, void* stream);
+
+/* The conv passes with distinct input and output row counts.  fprop: the map
+ * has n_out rows and feats n_in rows.  dgrad: the BACKWARD map has n_in rows,
+ * grad_out n_out rows, and offset v uses weight slot v (no mirroring).  wgrad:
+ * pair lists from the forward map.  Workspaces are sized by
+ * fgb_sparse_conv_workspace_bytes (pass 0/1/2 as in fgb_conv_workspace_bytes). */
+int fgb_sparse_conv_fprop(const void* feats, const void* weight, const void* bias,
+                          const uint32_t* neighbor_map, const int64_t* sorted_idx,
+                          const uint32_t* tile_masks, const uint32_t* block_order,
+                          void* out, int64_t n_out, int64_t n_in, int Ci, int Co, int V, int dtype,
+                          void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+int fgb_sparse_conv_dgrad(const void* grad_out, const void* weight,
+                          const uint32_t* neighbor_map_bwd, const int64_t* sorted_idx_bwd,
+                          const uint32_t* tile_masks_bwd, const uint32_t* block_order_bwd,
+                          void* grad_feats, int64_t n_in, int64_t n_out, int Ci, int Co, int V, int dtype,
+                          void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+int fgb_sparse_conv_wgrad(const void* grad_out, const void* feats,
+                          const uint32_t* valid_signal_i, const uint32_t* valid_signal_o,
+                          const uint32_t* valid_signal_seg,
+                          void* grad_weight, float* grad_weight_f32,
+                          int64_t n_out, int64_t n_in, int64_t n_pairs, int Ci, int Co, int V, int dtype, int splitk,
+                          void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+int64_t fgb_sparse_conv_workspace_bytes(int pass, int64_t n_out, int64_t n_in, int Ci, int Co, int V, int dtype, int splitk);
+
 #ifdef __cplusplus
 }
 #endif
