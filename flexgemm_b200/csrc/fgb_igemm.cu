@@ -8,11 +8,15 @@
 // weight tile fetched once feeds two MMAs, and each half skips the offsets that
 // are absent from its own 27-bit mask (no gather, no MMA for it).
 //
-// Warp roles (448 threads):
-//   warps 0-3   epilogue: tcgen05.ld -> +bias -> convert -> staged through a
+// Warp roles (576 threads):
+//   warps 0-3, 14-17
+//               epilogue: tcgen05.ld -> +bias -> convert -> staged through a
 //               small swizzled shared-memory buffer so that every global store
 //               instruction writes whole 128-byte lines of out[sorted_idx[row]];
-//               runs while the next block is gathered;
+//               runs while the next block is gathered.  Two warps per quarter
+//               of the accumulator rows, alternating 64-column passes: the MMA
+//               lane waits for the drain (one accumulator pair fills TMEM at
+//               BN = 256), so halving it is worth the extra warps;
 //   warp 4      one lane streams the dense weight tile [BN x 128 B] of the
 //               current (offset, channel slice) with a tiled TMA load;
 //   warp 5      owns the TMEM allocation; one lane issues tcgen05.mma and
@@ -44,11 +48,12 @@ constexpr int kTileM = 128;             // rows per accumulator (and per tile ma
 constexpr int kBlockM = 2 * kTileM;     // rows per work item
 constexpr int kMaxStages = 6;
 constexpr int kSchedRing = 16;  // deeper than the gather front can ever run ahead of the epilogue (stages + accumulator sets + 1 blocks)
-constexpr int kSchedReaders = 14;  // 8 gather warps, the TMA lane, the MMA lane, 4 epilogue warps
-constexpr int kIgemmThreads = 448;
+constexpr int kSchedReaders = 18;  // 8 gather warps, the TMA lane, the MMA lane, 8 epilogue warps
+constexpr int kIgemmThreads = 576;
+constexpr int kEpilogueWarp1 = 14;  // second group of epilogue warps: 14..17 (the first is 0..3)
 constexpr int kGatherWarp0 = 6;
 constexpr int kGatherThreads = 256;
-constexpr int kStoreStageBytes = 4 * 4096;  // per epilogue warp: 32 rows x 128 bytes
+constexpr int kStoreStageBytes = 8 * 4096;  // per epilogue warp: 32 rows x 128 bytes
 constexpr int kCtrlBytes = 1024;        // barriers, TMEM holder, abort flag
 constexpr int kATileBytes = kTileM * 128;
 constexpr int kSmemBudget = 226 * 1024;
@@ -164,7 +169,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&ctl->acc_full[a], 1);   // tcgen05.commit after the block's last MMA
-      mbar_init(&ctl->acc_empty[a], 4);  // the four epilogue warps
+      mbar_init(&ctl->acc_empty[a], 8);  // the eight epilogue warps
     }
     for (int k = 0; k < kSchedRing; ++k) {
       mbar_init(&ctl->sched_full[k], 1);
@@ -224,7 +229,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     m1 = t0 + 1 < p.num_tiles ? __ldg(&p.tile_masks[t0 + 1]) : 0u;
   };
 
-  if (warp >= kGatherWarp0) {
+  if (warp >= kGatherWarp0 && warp < kEpilogueWarp1) {
     // ---------------------------------------------------------------- gather
     const int piece = lane & 7;
     const int g = (warp - kGatherWarp0) * 4 + (lane >> 3);  // 0..31: rows g, g+32, ... of the block
@@ -382,7 +387,11 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     // time go through a per-warp staging buffer [32 rows][128 or 256 bytes] whose
     // 16-byte pieces are XOR-swizzled, and come back so that eight (fp32: sixteen)
     // consecutive lanes hold one row's contiguous bytes.
-    uint8_t* stage_out = smem + kCtrlBytes + size_t(S) * stage_bytes + warp * 4096;
+    // Two warps share each quarter of the accumulator rows (a warp reads TMEM lanes 32 * (warp % 4) ...): the
+    // first group takes the even 64-column passes, the second the odd ones.
+    const int quarter = warp & 3;
+    const int group = warp >= kEpilogueWarp1 ? 1 : 0;
+    uint8_t* stage_out = smem + kCtrlBytes + size_t(S) * stage_bytes + (group * 4 + quarter) * 4096;
     constexpr int kColsPerPass = 4096 / 32 / kElem;  // 64 columns of 16-bit, 32 columns of fp32: 128 bytes per row
     constexpr int kChunksPerPass = kColsPerPass / 32 > 0 ? kColsPerPass / 32 : 1;
     uint32_t item = 0;
@@ -395,7 +404,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
       uint32_t sr[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const uint32_t r = mblk * kBlockM + h * kTileM + warp * 32 + lane;
+        const uint32_t r = mblk * kBlockM + h * kTileM + quarter * 32 + lane;
         sr[h] = r < p.n ? static_cast<uint32_t>(__ldg(&p.sorted_idx[r])) : kInvalid;
       }
       mbar_wait(&ctl->acc_full[set], (item / p.acc_sets) & 1, abort_flag);
@@ -403,8 +412,8 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const bool has_acc = (h == 0 ? m0 : m1) != 0u;  // a half without offsets holds no rows
-        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + set * 2 * p.bn + h * p.bn;
-        for (int c0 = 0; c0 < p.bn; c0 += kColsPerPass) {
+        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + set * 2 * p.bn + h * p.bn;
+        for (int c0 = group * kColsPerPass; c0 < p.bn; c0 += 2 * kColsPerPass) {
           uint32_t acc[kChunksPerPass][32];
           if (has_acc) {
 #pragma unroll
