@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     if (!one_lane) __syncwarp();
     if (one_lane || lane == 0) mbar_arrive(&ctl->sched_empty[slot]);
     if (e == kInvalid) return false;
-    mblk = e / p.n_tiles_n;
+    mblk = p.n_tiles_n == 1 ? e : e / p.n_tiles_n;  // once per work item
     ntile = e - mblk * p.n_tiles_n;
     return true;
   };
@@ -254,7 +254,9 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
         idx[j] = (need && rows[j] != kInvalid) ? __ldg(&p.nbr[size_t(rows[j]) * V + v]) : kInvalid;
       }
     };
-    uint32_t it = 0;
+    // ring position of the next stage and its phase bit, advanced by hand: a division by the runtime stage count
+    // in this loop costs several XU-pipe instructions per stage and starves the epilogue's conversions
+    uint32_t s = 0, ph = 0;
     uint32_t rows[8], nrows[8], idx[8], nidx[8];
     uint32_t m0 = 0, m1 = 0, nm0 = 0, nm1 = 0;
     uint32_t mblk = 0, ntile = 0;
@@ -292,9 +294,8 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
         const char* src[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) src[j] = p.x + size_t(idx[j] != kInvalid ? idx[j] : 0u) * p.row_bytes + piece * 16;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-          const uint32_t s = it % S;
-          mbar_wait(&ctl->empty[s], ((it / S) & 1) ^ 1, abort_flag);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag);
           const uint32_t a_base = smem_u32(stages + size_t(s) * stage_bytes);
           const bool col_ok = kb * 128 + piece * 16 < p.row_bytes;
 #pragma unroll
@@ -305,6 +306,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
             }
           }
           cp_async_arrive(&ctl->full[s]);
+          if (++s == static_cast<uint32_t>(S)) s = 0, ph ^= 1;
         }
       }
       m0 = nm0, m1 = nm1;
@@ -315,7 +317,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
   } else if (warp == 4) {
     // ------------------------------------------------------------ weight TMA
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t s = 0, ph = 0;
       uint32_t mblk = 0, ntile = 0;
       for (uint32_t pass = 0; work_of(pass, mblk, ntile, true); ++pass) {
         const int n0 = static_cast<int>(ntile) * p.bn;
@@ -326,11 +328,11 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
           const int v = __ffs(un) - 1;
           un &= un - 1;
           const int wv = p.flip ? V - 1 - v : v;
-          for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-            const uint32_t s = it % S;
-            mbar_wait(&ctl->empty[s], ((it / S) & 1) ^ 1, abort_flag);
+          for (int kb = 0; kb < p.num_kb; ++kb) {
+            mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag);
             mbar_arrive_expect_tx(&ctl->full[s], static_cast<uint32_t>(p.bn) * 128u);
             tma_load_3d(smem_u32(stages + size_t(s) * stage_bytes + 2 * kATileBytes), &tmap_w, &ctl->full[s], kb * (128 / kElem), wv, n0);
+            if (++s == static_cast<uint32_t>(S)) s = 0, ph ^= 1;
           }
         }
       }
@@ -338,15 +340,15 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
   } else if (warp == 5) {
     // ------------------------------------------------------------------- MMA
     if (lane == 0) {
-      uint32_t it = 0, item = 0;
+      uint32_t s = 0, ph = 0, item = 0;
+      uint32_t set = 0, set_ph = 0;  // accumulator set of the item and its phase bit
       uint32_t mblk = 0, ntile = 0;
       for (; work_of(item, mblk, ntile, true); ++item) {
         uint32_t m0, m1;
         masks_of(mblk, m0, m1);
-        const uint32_t set = item % p.acc_sets;
         const uint32_t acc_tmem = tmem_base + set * 2 * p.bn;
         // the epilogue must have drained this accumulator pair
-        mbar_wait(&ctl->acc_empty[set], ((item / p.acc_sets) & 1) ^ 1, abort_flag);
+        mbar_wait(&ctl->acc_empty[set], set_ph ^ 1, abort_flag);
         tc_fence_after_sync();
         uint32_t acc0 = 0, acc1 = 0;
         uint32_t un = m0 | m1;
@@ -354,9 +356,8 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
           const int v = __ffs(un) - 1;
           un &= un - 1;
           const bool need0 = (m0 >> v) & 1u, need1 = (m1 >> v) & 1u;
-          for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-            const uint32_t s = it % S;
-            mbar_wait(&ctl->full[s], (it / S) & 1, abort_flag);
+          for (int kb = 0; kb < p.num_kb; ++kb) {
+            mbar_wait(&ctl->full[s], ph, abort_flag);
             tc_fence_after_sync();
             const uint32_t a_addr = smem_u32(stages + size_t(s) * stage_bytes);
             const uint64_t da0 = make_smem_desc(a_addr, 16, 1024);
@@ -376,9 +377,11 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
               }
             }
             umma_commit(&ctl->empty[s]);
+            if (++s == static_cast<uint32_t>(S)) s = 0, ph ^= 1;
           }
         }
         umma_commit(&ctl->acc_full[set]);
+        if (++set == static_cast<uint32_t>(p.acc_sets)) set = 0, set_ph ^= 1;
       }
     }
   } else {
@@ -395,19 +398,19 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     constexpr int kColsPerPass = 4096 / 32 / kElem;  // 64 columns of 16-bit, 32 columns of fp32: 128 bytes per row
     constexpr int kChunksPerPass = kColsPerPass / 32 > 0 ? kColsPerPass / 32 : 1;
     uint32_t item = 0;
+    uint32_t set = 0, set_ph = 0;
     uint32_t mblk = 0, ntile = 0;
     for (; work_of(item, mblk, ntile, false); ++item) {
       const int n0 = static_cast<int>(ntile) * p.bn;
       uint32_t m0, m1;
       masks_of(mblk, m0, m1);
-      const uint32_t set = item % p.acc_sets;
       uint32_t sr[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const uint32_t r = mblk * kBlockM + h * kTileM + quarter * 32 + lane;
         sr[h] = r < p.n ? static_cast<uint32_t>(__ldg(&p.sorted_idx[r])) : kInvalid;
       }
-      mbar_wait(&ctl->acc_full[set], (item / p.acc_sets) & 1, abort_flag);
+      mbar_wait(&ctl->acc_full[set], set_ph, abort_flag);
       tc_fence_after_sync();
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -442,6 +445,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->acc_empty[set]);
+      if (++set == static_cast<uint32_t>(p.acc_sets)) set = 0, set_ph ^= 1;
     }
   }
 

@@ -197,8 +197,9 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
     };
     uint32_t io[kRows], ii[kRows], nio[kRows], nii[kRows];
     load_pairs(k_begin, nio, nii);
+    int s = 0;
+    uint32_t ph = 0;  // ring position and phase bit, advanced by hand (no division by the runtime stage count per stage)
     for (int it = 0; it < total; ++it) {
-      const int s = it % S;
 #pragma unroll
       for (int j = 0; j < kRows; ++j) io[j] = nio[j], ii[j] = nii[j];
       if (it + 1 < total) load_pairs(k_begin + it + 1, nio, nii);  // one stage ahead
@@ -209,7 +210,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
         srca[j] = p.gout + size_t(io[j] != kInvalid ? io[j] : 0u) * a_row_bytes + co0 * kElem + piece * 16;
         srcb[j] = p.x + size_t(ii[j] != kInvalid ? ii[j] : 0u) * b_row_bytes + ci0 * kElem + piece * 16;
       }
-      mbar_wait(&ctl->empty[s], ((it / S) & 1) ^ 1, abort_flag);
+      mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag);
       const uint32_t st_base = smem_u32(stages + size_t(s) * stage_bytes);
       for (int c = 0; c < p.a_chunks; ++c) {
         const bool col_ok = co0 * kElem + c * 128 + piece * 16 < a_row_bytes;
@@ -224,15 +225,17 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
           cp_async_16(st_base + a_bytes + c * chunk_bytes + row_off[j], srcb[j] + c * 128, (col_ok && ii[j] != kInvalid) ? 16u : 0u);
       }
       cp_async_arrive(&ctl->full[s]);
+      if (++s == S) s = 0, ph ^= 1;
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------------- MMA
     if (lane == 0) {
       uint32_t accumulate = 0;
       const int chunks_per_m = 128 / kChunkElems;  // 128-byte chunks per 128 accumulator rows
+      int s = 0;
+      uint32_t ph = 0;
       for (int it = 0; it < total; ++it) {
-        const int s = it % S;
-        mbar_wait(&ctl->full[s], (it / S) & 1, abort_flag);
+        mbar_wait(&ctl->full[s], ph, abort_flag);
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(stages + size_t(s) * stage_bytes);
         const uint32_t b_addr = a_addr + a_bytes;
@@ -246,6 +249,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
           accumulate = 1;
         }
         umma_commit(&ctl->empty[s]);
+        if (++s == S) s = 0, ph ^= 1;
       }
       umma_commit(&ctl->acc_full);
     }
