@@ -190,8 +190,8 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
 
   // Work distribution.  Row blocks are handed out dynamically, in descending
   // cost order, from a global ticket counter: lane 0 of the first gather warp
-  // claims the ticket of the CTA's next block when the gather front starts the
-  // current one, and publishes it (block x column tile, or "no more work") in a
+  // claims the ticket of the CTA's next block when the gather front is about to
+  // finish the current one, and publishes it (block x column tile, or "no more work") in a
   // small shared-memory ring that every role reads in order.  So each role walks
   // the same sequence of work items, an SM that got cheap blocks simply takes
   // more of them, and within an item all roles enumerate the offsets of the
@@ -270,20 +270,27 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
       if (m0 | m1) load_idx(rows, __ffs(m0 | m1) - 1, m0, m1, nidx);
     }
     for (uint32_t pass = 0; has_work; ++pass) {
-      // rows and masks of the next work item, fetched a whole block ahead
+      // The next work item is claimed late -- when at most one more offset of the current block is left to
+      // gather -- so that near the end of the launch no CTA sits on a block while another SM is already idle;
+      // its rows and masks then arrive while the last offsets are gathered.
       uint32_t mblk_n = 0, ntile_n = 0;
-      if (publisher) publish_work(pass + 1, pub_block, pub_ntile);
-      const bool has_next = work_of(pass + 1, mblk_n, ntile_n, false);
-      if (has_next) {
-        masks_of(mblk_n, nm0, nm1);
-        load_rows(mblk_n, nrows);
-      }
+      bool has_next = false, claimed = false;
+      auto claim_next = [&]() {
+        if (publisher) publish_work(pass + 1, pub_block, pub_ntile);
+        has_next = work_of(pass + 1, mblk_n, ntile_n, false);
+        if (has_next) {
+          masks_of(mblk_n, nm0, nm1);
+          load_rows(mblk_n, nrows);
+        }
+        claimed = true;
+      };
       uint32_t un = m0 | m1;
       while (un) {
         const int v = __ffs(un) - 1;
         un &= un - 1;
 #pragma unroll
         for (int j = 0; j < 8; ++j) idx[j] = nidx[j];
+        if (!claimed && (un & (un - 1)) == 0u) claim_next();
         // neighbour indices one offset ahead (or the first offset of the next block)
         if (un) {
           load_idx(rows, __ffs(un) - 1, m0, m1, nidx);
@@ -308,6 +315,10 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
           cp_async_arrive(&ctl->full[s]);
           if (++s == static_cast<uint32_t>(S)) s = 0, ph ^= 1;
         }
+      }
+      if (!claimed) {  // a block without any offset (rows with no neighbour at all)
+        claim_next();
+        if (has_next && (nm0 | nm1)) load_idx(nrows, __ffs(nm0 | nm1) - 1, nm0, nm1, nidx);
       }
       m0 = nm0, m1 = nm1;
 #pragma unroll
