@@ -408,6 +408,35 @@ def bias_grad(grad_out, want_f32: bool = False, want_dtype: bool = True):
     return gb, gb32
 
 
+_side_streams: Dict[int, "torch.cuda.Stream"] = {}
+
+
+def bias_grad_overlapped(grad_out, want_f32: bool = False, want_dtype: bool = True):
+    """Starts the bias gradient on a side stream so that it runs in the shadow of
+    the persistent conv kernels (which hold one CTA per SM but leave room for the
+    small reduction CTAs), and returns ``(grad_bias, grad_bias_f32, join)``: call
+    ``join()`` on the launching stream after the other backward kernels have been
+    queued and before the gradient is used."""
+    dev = grad_out.device
+    cur = torch.cuda.current_stream(dev)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    side = _side_streams.get(idx)
+    if side is None:
+        side = _side_streams[idx] = torch.cuda.Stream(device=dev)
+    side.wait_stream(cur)                  # grad_out is ready once the launching stream gets here
+    with torch.cuda.stream(side):
+        gb, gb32 = bias_grad(grad_out, want_f32=want_f32, want_dtype=want_dtype)
+    grad_out.record_stream(side)
+
+    def join():
+        cur.wait_stream(side)
+        for t in (gb, gb32):
+            if t is not None:
+                t.record_stream(cur)
+
+    return gb, gb32, join
+
+
 def cast_from_f32(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     out = torch.empty(src.shape, dtype=dtype, device=src.device)
     code = _DTYPES.get(dtype, _cabi.F32_TF32)

@@ -285,6 +285,9 @@ class SparseConv3dFunction(Function):
             assert feats.is_contiguous(), "Matrix input must be contiguous"
             assert weight.is_contiguous(), "Matrix weight must be contiguous"
             w = weight.reshape(Co, V, Ci)
+            join = None
+            if bias is not None and bias.requires_grad:   # a small reduction: runs beside the conv kernels
+                grad_bias, _, join = kernels.cuda.bias_grad_overlapped(grad_output)
             if feats.requires_grad:
                 tile = kernels.cuda.conv_tile_rows()
                 neighbor_cache._ensure_bwd_order()
@@ -295,8 +298,8 @@ class SparseConv3dFunction(Function):
                 gw, _ = kernels.cuda.conv_wgrad(grad_output, feats, neighbor_cache["valid_signal_i"], neighbor_cache["valid_signal_o"],
                                                 neighbor_cache["valid_signal_seg"])
                 grad_weight = gw.reshape(Co, Kw, Kh, Kd, Ci)
-            if bias is not None and bias.requires_grad:
-                grad_bias, _ = kernels.cuda.bias_grad(grad_output)
+            if join is not None:
+                join()
             return grad_input, grad_weight, grad_bias
         raise ValueError(f"Unsupported algorithm {spconv.ALGORITHM}")
 

@@ -201,6 +201,9 @@ class SubMConv3dFunction(Function):
             assert feats.is_contiguous(), "Matrix input must be contiguous"
             assert weight.is_contiguous(), "Matrix weight must be contiguous"
             w = weight.reshape(Co, V, Ci)
+            join = None
+            if bias is not None and bias.requires_grad:   # a small reduction: runs beside the conv kernels
+                grad_bias, _, join = kernels.cuda.bias_grad_overlapped(grad_output)
             if feats.requires_grad:
                 tile = kernels.cuda.conv_tile_rows()
                 grad_input = kernels.cuda.conv_dgrad(grad_output, w, neighbor_cache["neighbor_map"], neighbor_cache["sorted_idx"],
@@ -209,8 +212,8 @@ class SubMConv3dFunction(Function):
                 gw, _ = kernels.cuda.conv_wgrad(grad_output, feats, neighbor_cache["valid_signal_i"], neighbor_cache["valid_signal_o"],
                                                 neighbor_cache["valid_signal_seg"])
                 grad_weight = gw.reshape(Co, Kw, Kh, Kd, Ci)
-            if bias is not None and bias.requires_grad:
-                grad_bias, _ = kernels.cuda.bias_grad(grad_output)
+            if join is not None:
+                join()
             return grad_input, grad_weight, grad_bias
         raise ValueError(f"Unsupported algorithm {spconv.ALGORITHM}")
 

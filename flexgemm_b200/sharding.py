@@ -105,10 +105,15 @@ def sharded_backward(grad_out: torch.Tensor, feats: torch.Tensor, cache, weight:
     grad_in = None
     if local_grads is None:
         from .kernels import cuda as K
+        gb32, join = None, None
+        if bias is not None:  # small reduction: runs beside the conv kernels on a side stream
+            _, gb32, join = K.bias_grad_overlapped(grad_out, want_f32=True, want_dtype=False)
         if want_input_grad:
             tile = K.conv_tile_rows()
             grad_in = K.conv_dgrad(grad_out, w, cache["neighbor_map"], cache["sorted_idx"], cache.tile_masks(tile), cache.block_order(tile))
-        gw32, gb32 = _cuda_local_grads(grad_out, feats, cache, w, bias is not None)
+        gw32, _ = _cuda_local_grads(grad_out, feats, cache, w, False)
+        if join is not None:
+            join()
     else:
         grad_in, gw32, gb32 = local_grads(grad_out, feats, cache, w, bias is not None)
     gw32, gb32 = allreduce_param_grads(gw32, gb32, group)
