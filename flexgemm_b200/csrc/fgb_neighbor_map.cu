@@ -15,6 +15,18 @@
 // derives everything the later passes need from it: the per-voxel validity
 // mask (gray code), its Gray-to-binary decode, and per-(offset, block) valid
 // counts that a small scan turns into the offsets of the wgrad pair lists.
+//
+// Sorted input (the common case: coordinates in lexicographic (b, x, y, z)
+// order, which is ascending flat-index order) needs no table at all for the
+// 3x3x3, dilation-1 stencil: a row's position in the input IS its rank among
+// the keys, and the neighbours of 256 consecutive voxels lie in nine short
+// windows of the same array (one per (dx, dy); the three dz neighbours are
+// adjacent keys).  A check kernel decides on the device which path runs -- the
+// kernels of the other path return at once -- so no host round trip is added;
+// both paths produce the same map.
+#include <algorithm>
+#include <type_traits>
+
 #include "fgb_common.cuh"
 
 namespace fgb {
@@ -107,9 +119,12 @@ struct Grid3 {
 };
 
 // one thread per voxel, 16-byte coordinate loads
+// `unsorted` (may be null): device word, 0 when the sorted-input path builds the map instead -- then the table is not needed
 template <int kKeyBits>
 __global__ void __launch_bounds__(kMapBlock) hash_insert_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g,
-                                                                void* table_mem, uint32_t slots, int32_t* status) {
+                                                                void* table_mem, uint32_t slots, int32_t* status,
+                                                                const uint32_t* __restrict__ unsorted) {
+  if (unsorted != nullptr && *unsorted == 0u) return;
   const uint32_t i = blockIdx.x * kMapBlock + threadIdx.x;
   if (i >= n) return;
   const int4 c = __ldg(&coords[i]);
@@ -138,7 +153,9 @@ template <int kKeyBits, bool kGeneral>
 __global__ void __launch_bounds__(kMapBlock)
     subm_lookup_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, Stencil st, void* table_mem, uint32_t slots,
                        uint32_t* __restrict__ nbr, uint32_t* __restrict__ nbr_bwd, int32_t* __restrict__ gray_out,
-                       int32_t* __restrict__ binary_out, uint32_t* __restrict__ block_counts, uint32_t nblk) {
+                       int32_t* __restrict__ binary_out, uint32_t* __restrict__ block_counts, uint32_t nblk,
+                       const uint32_t* __restrict__ unsorted) {
+  if (unsorted != nullptr && *unsorted == 0u) return;  // the sorted-input kernel builds the map
   __shared__ int4 s_coord[kMapBlock];
   __shared__ uint32_t s_gray[kMapBlock];
   __shared__ uint32_t s_count[32];
@@ -263,13 +280,177 @@ __global__ void seg_prefix_kernel(uint32_t* seg, int V) {
   }
 }
 
+// ------------------------------------------------------------------ sorted-input path
+constexpr int kWinMax = 320;   // keys of one (dx, dy) window held in shared memory (sized so that five CTAs fit an SM); longer windows are searched in global memory
+constexpr int kCombos = 9;     // (dx, dy) pairs of the 3x3x3 stencil
+
+// *unsorted = 1 when some key is not greater than its predecessor (the word must be 0 on entry)
+template <int kKeyBits>
+__global__ void __launch_bounds__(256) sorted_check_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, uint32_t* unsorted) {
+  const uint32_t i = blockIdx.x * 256u + threadIdx.x;
+  if (i == 0 || i >= n) return;
+  const int4 a = __ldg(&coords[i - 1]), b = __ldg(&coords[i]);
+  if (g.template key<kKeyBits>(a.x, a.y, a.z, a.w) >= g.template key<kKeyBits>(b.x, b.y, b.z, b.w)) *unsorted = 1u;
+}
+
+// fills the table with the empty pattern unless the sorted-input path runs
+__global__ void __launch_bounds__(256) table_clear_kernel(uint32_t* __restrict__ words, size_t count, const uint32_t* __restrict__ unsorted) {
+  if (unsorted != nullptr && *unsorted == 0u) return;
+  for (size_t i = blockIdx.x * size_t(256) + threadIdx.x; i < count; i += size_t(gridDim.x) * 256) words[i] = 0xFFFFFFFFu;
+}
+
+template <int kKeyBits>
+__device__ __forceinline__ long long key_at(const int4* __restrict__ coords, uint32_t i, const Grid3& g) {
+  const int4 c = __ldg(&coords[i]);
+  return static_cast<long long>(g.template key<kKeyBits>(c.x, c.y, c.z, c.w));
+}
+
+// One CTA per 256 voxels (the blocking of the hash lookup, so the side products
+// are the same), thread t owns voxel t.  For each (dx, dy) the keys the CTA can
+// ask for lie between key_first + delta - 1 and key_last + delta + 1: two
+// binary searches in the sorted input bound that window, its keys go to shared
+// memory, and each thread then finds key + delta - 1 by binary search in the
+// window; key + delta and key + delta + 1, when present, are the next entries.
+// The position of a hit in the input is the neighbour's row.
+template <int kKeyBits>
+__global__ void __launch_bounds__(kMapBlock)
+    subm_sorted_lookup_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, uint32_t* __restrict__ nbr,
+                              int32_t* __restrict__ gray_out, int32_t* __restrict__ binary_out, uint32_t* __restrict__ block_counts,
+                              uint32_t nblk, const uint32_t* __restrict__ unsorted) {
+  using K = typename std::conditional<kKeyBits == 32, uint32_t, unsigned long long>::type;
+  if (*unsorted != 0u) return;  // the hash kernels build the map
+  extern __shared__ __align__(16) uint8_t dyn_smem[];
+  int4* s_coord = reinterpret_cast<int4*>(dyn_smem);                       // [256]
+  uint32_t* s_nbr = reinterpret_cast<uint32_t*>(dyn_smem + kMapBlock * 16);  // [256 * 27]
+  K* s_win = reinterpret_cast<K*>(dyn_smem + kMapBlock * 16 + kMapBlock * 27 * 4);  // [9][kWinMax]
+  __shared__ uint32_t s_lo[kCombos], s_hi[kCombos];
+  __shared__ uint32_t s_count[32];
+  const uint32_t n0 = blockIdx.x * kMapBlock;
+  const uint32_t nv = min(static_cast<uint32_t>(kMapBlock), n - n0);
+  const int t = threadIdx.x, lane = t & 31;
+  if (t < nv) s_coord[t] = __ldg(&coords[n0 + t]);
+  if (t < 32) s_count[t] = 0;
+  __syncthreads();
+
+  const long long HD = static_cast<long long>(g.H) * g.D;
+  if (t < 2 * kCombos) {
+    // window bounds: thread 2c finds the first row with key >= key_first + delta - 1, thread 2c + 1 the first
+    // row with key > key_last + delta + 1
+    const int c = t >> 1;
+    const bool upper = t & 1;
+    const long long delta = (c / 3 - 1) * HD + (c % 3 - 1) * static_cast<long long>(g.D);
+    const int4 e = upper ? s_coord[nv - 1] : s_coord[0];
+    const long long target = static_cast<long long>(g.template key<kKeyBits>(e.x, e.y, e.z, e.w)) + delta + (upper ? 1 : -1);
+    uint32_t lo = 0, hi = n;
+    while (lo < hi) {
+      const uint32_t mid = lo + ((hi - lo) >> 1);
+      const long long km = key_at<kKeyBits>(coords, mid, g);
+      if (upper ? km <= target : km < target) lo = mid + 1;
+      else hi = mid;
+    }
+    if (upper) s_hi[c] = lo;
+    else s_lo[c] = lo;
+  }
+  __syncthreads();
+  // all windows as one flat list of kCombos * kWinMax slots, so that a thread's loads are independent of one another
+#pragma unroll 4
+  for (uint32_t slot = t; slot < kCombos * kWinMax; slot += kMapBlock) {
+    const uint32_t c = slot / kWinMax, j = slot - c * kWinMax;
+    const uint32_t ws = s_lo[c], len = s_hi[c] > ws ? s_hi[c] - ws : 0u;
+    if (len <= kWinMax && j < len) s_win[slot] = static_cast<K>(key_at<kKeyBits>(coords, ws + j, g));
+  }
+  __syncthreads();
+
+  uint32_t gray = 0;
+  if (t < nv) {
+    const int4 cc = s_coord[t];
+    const long long key = static_cast<long long>(g.template key<kKeyBits>(cc.x, cc.y, cc.z, cc.w));
+#pragma unroll 1
+    for (int c = 0; c < kCombos; ++c) {
+      const int dx = c / 3 - 1, dy = c % 3 - 1;
+      uint32_t res[3] = {kInvalid, kInvalid, kInvalid};
+      const int x = cc.y + dx, y = cc.z + dy;
+      const uint32_t ws = s_lo[c], len = s_hi[c] > ws ? s_hi[c] - ws : 0u;
+      if (x >= 0 && x < g.W && y >= 0 && y < g.H && len > 0) {
+        const long long mid_key = key + dx * HD + dy * static_cast<long long>(g.D);  // key of (x + dx, y + dy, z)
+        const bool in_smem = len <= kWinMax;
+        const K* win = s_win + c * kWinMax;
+        auto read = [&](uint32_t j) -> long long {
+          return in_smem ? static_cast<long long>(win[j]) : key_at<kKeyBits>(coords, ws + j, g);
+        };
+        uint32_t lo = 0, hi = len;  // first entry >= mid_key - 1
+        while (lo < hi) {
+          const uint32_t m = lo + ((hi - lo) >> 1);
+          if (read(m) < mid_key - 1) lo = m + 1;
+          else hi = m;
+        }
+        uint32_t pos = lo;
+#pragma unroll
+        for (int dz = -1; dz <= 1; ++dz) {
+          if (pos < len && read(pos) == mid_key + dz) {
+            const int z = cc.w + dz;
+            if (z >= 0 && z < g.D) res[dz + 1] = ws + pos;  // otherwise the key belongs to a voxel of another row of the grid
+            ++pos;
+          }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 3; ++k) {
+        s_nbr[t * 27 + c * 3 + k] = res[k];
+        if (res[k] != kInvalid) gray |= 1u << (c * 3 + k);
+      }
+    }
+  }
+  // per-offset valid counts of the CTA (for the pair-list offsets)
+  for (int v = 0; v < 27; ++v) {
+    const uint32_t b = __ballot_sync(0xffffffffu, (gray >> v) & 1u);
+    if (lane == 0 && b != 0u) atomicAdd(&s_count[v], static_cast<uint32_t>(__popc(b)));
+  }
+  __syncthreads();
+  uint32_t* out = nbr + static_cast<size_t>(n0) * 27;
+  for (uint32_t item = t; item < nv * 27; item += kMapBlock) out[item] = s_nbr[item];
+  if (t < nv) {
+    uint32_t binary = gray;
+    binary ^= binary >> 1;
+    binary ^= binary >> 2;
+    binary ^= binary >> 4;
+    binary ^= binary >> 8;
+    binary ^= binary >> 16;
+    gray_out[n0 + t] = static_cast<int32_t>(gray);
+    binary_out[n0 + t] = static_cast<int32_t>(binary);
+  }
+  if (t < 27) block_counts[static_cast<size_t>(t) * nblk + blockIdx.x] = s_count[t];
+}
+
 template <int kKeyBits>
 static int build_impl(const int32_t* coords, uint32_t n, Grid3 g, Stencil st, void* table, uint32_t slots, uint32_t* nbr,
                       int32_t* gray, int32_t* binary, uint32_t* block_counts, uint32_t* seg, int32_t* status, cudaStream_t s) {
   const uint32_t nblk = static_cast<uint32_t>(ceil_div(n, kMapBlock));
-  hash_insert_kernel<kKeyBits><<<nblk, kMapBlock, 0, s>>>(reinterpret_cast<const int4*>(coords), n, g, table, slots, status);
-  subm_lookup_kernel<kKeyBits, false><<<nblk, kMapBlock, 0, s>>>(reinterpret_cast<const int4*>(coords), n, g, st, table, slots, nbr,
-                                                                nullptr, gray, binary, block_counts, nblk);
+  const int4* c4 = reinterpret_cast<const int4*>(coords);
+  const size_t table_words = static_cast<size_t>(fgb_hash_table_bytes(slots, kKeyBits)) / 4;
+  const unsigned clear_grid = static_cast<unsigned>(std::min<size_t>(ceil_div(static_cast<int64_t>(table_words), 256 * 8), 148 * 16));
+  // The sorted-input path serves the 3x3x3, dilation-1 stencil with keys that fit a signed 64-bit range; seg[0]
+  // (rewritten by the scan at the end) carries the device-side decision between the two paths.
+  const bool try_sorted = st.Kw == 3 && st.Kh == 3 && st.Kd == 3 && st.Dw == 1 && st.Dh == 1 && st.Dd == 1 &&
+                          (kKeyBits == 32 || static_cast<double>(g.W) * g.H * g.D < 1e15);
+  uint32_t* unsorted = try_sorted ? seg : nullptr;
+  if (try_sorted) {
+    cudaError_t e = cudaMemsetAsync(seg, 0, sizeof(uint32_t), s);
+    if (e != cudaSuccess) return cuda_status(e);
+    sorted_check_kernel<kKeyBits><<<static_cast<unsigned>(ceil_div(n, 256)), 256, 0, s>>>(c4, n, g, unsorted);
+  }
+  table_clear_kernel<<<clear_grid > 0 ? clear_grid : 1, 256, 0, s>>>(static_cast<uint32_t*>(table), table_words, unsorted);
+  hash_insert_kernel<kKeyBits><<<nblk, kMapBlock, 0, s>>>(c4, n, g, table, slots, status, unsorted);
+  subm_lookup_kernel<kKeyBits, false><<<nblk, kMapBlock, 0, s>>>(c4, n, g, st, table, slots, nbr, nullptr, gray, binary, block_counts,
+                                                                nblk, unsorted);
+  if (try_sorted) {
+    const int smem = kMapBlock * 16 + kMapBlock * 27 * 4 + kCombos * kWinMax * (kKeyBits / 8);
+    cudaError_t e = cudaFuncSetAttribute(subm_sorted_lookup_kernel<kKeyBits>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return cuda_status(e);
+    e = cudaFuncSetAttribute(subm_sorted_lookup_kernel<kKeyBits>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e != cudaSuccess) return cuda_status(e);
+    subm_sorted_lookup_kernel<kKeyBits><<<nblk, kMapBlock, smem, s>>>(c4, n, g, nbr, gray, binary, block_counts, nblk, unsorted);
+  }
   block_scan_kernel<<<st.V, 1024, 0, s>>>(block_counts, nblk, seg);
   seg_prefix_kernel<<<1, 32, 0, s>>>(seg, st.V);
   return launch_status();
@@ -282,10 +463,10 @@ static int build_general_impl(const int32_t* in_coords, uint32_t n_in, const int
                               uint32_t* block_counts, uint32_t* seg, int32_t* status, cudaStream_t s) {
   if (n_in > 0)
     hash_insert_kernel<kKeyBits><<<static_cast<unsigned>(ceil_div(n_in, kMapBlock)), kMapBlock, 0, s>>>(
-        reinterpret_cast<const int4*>(in_coords), n_in, g, table, slots, status);
+        reinterpret_cast<const int4*>(in_coords), n_in, g, table, slots, status, nullptr);
   const uint32_t nblk = static_cast<uint32_t>(ceil_div(n_out, kMapBlock));
   subm_lookup_kernel<kKeyBits, true><<<nblk, kMapBlock, 0, s>>>(reinterpret_cast<const int4*>(out_coords), n_out, g, st, table, slots,
-                                                               nbr, nbr_bwd, gray, binary, block_counts, nblk);
+                                                               nbr, nbr_bwd, gray, binary, block_counts, nblk, nullptr);
   block_scan_kernel<<<st.V, 1024, 0, s>>>(block_counts, nblk, seg);
   seg_prefix_kernel<<<1, 32, 0, s>>>(seg, st.V);
   return launch_status();
@@ -353,8 +534,6 @@ extern "C" int fgb_subm_build_neighbor_map(const int32_t* coords, int64_t n, int
   if (!coords || !table || !neighbor_map || !gray_code || !binary_code || !block_counts) return FGB_E_NULL;
   if (reinterpret_cast<uintptr_t>(coords) & 15) return FGB_E_ALIGN;
   if (reinterpret_cast<uintptr_t>(table) & 7) return FGB_E_ALIGN;
-  int rc = cuda_status(cudaMemsetAsync(table, 0xFF, static_cast<size_t>(fgb_hash_table_bytes(slots, key_bits)), s));
-  if (rc != FGB_OK) return rc;
   const Grid3 g{W, H, D};
   const Stencil st{Kw, Kh, Kd, Dw, Dh, Dd, static_cast<int>(V)};
   if (key_bits == 32)

@@ -119,7 +119,8 @@ def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table:
         out["block_offsets"].data_ptr(), meta.data_ptr(),
         meta.data_ptr() + 4 * (V + 1), _stream(dev))
     _cabi.check(rc, "fgb_subm_build_neighbor_map")
-    _count(4)
+    # table clear, insert, hash lookup, block scan, prefix (+ order check and sorted-input lookup for the 3x3x3 stencil)
+    _count(7 if (tuple(int(k) for k in ksize), tuple(int(d) for d in dilation)) == ((3, 3, 3), (1, 1, 1)) else 5)
     return out
 
 
@@ -219,6 +220,25 @@ def gray_code_from_map(neighbor_map: torch.Tensor) -> Tuple[torch.Tensor, torch.
     _cabi.check(rc, "fgb_pp_gray_code")
     _count(1)
     return gray, binary
+
+
+_meta_host: Dict[tuple, tuple] = {}
+
+
+def fetch_meta_async(meta: torch.Tensor):
+    """Queues the device-to-host copy of a build's ``meta`` words into a pinned
+    buffer that is reused between builds (the previous build's read has always
+    completed: every build waits for its own copy) and returns ``(host, event)``;
+    ``event.synchronize()`` makes ``host`` valid."""
+    dev = meta.device
+    key = (dev.index, int(meta.numel()))
+    entry = _meta_host.get(key)
+    if entry is None:
+        entry = _meta_host[key] = (torch.empty(meta.shape, dtype=meta.dtype, pin_memory=True), torch.cuda.Event())
+    host, event = entry
+    host.copy_(meta, non_blocking=True)
+    event.record(torch.cuda.current_stream(dev))
+    return host, event
 
 
 def raise_for_status(code: int) -> None:

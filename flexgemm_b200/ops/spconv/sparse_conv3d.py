@@ -182,10 +182,7 @@ class SparseConv3dFunction(Function):
 
         if needs_grad:
             # one host round trip: pair count + the build's status word, overlapped with the sort
-            meta_host = torch.empty(built["meta"].shape, dtype=built["meta"].dtype, pin_memory=True)
-            meta_host.copy_(built["meta"], non_blocking=True)
-            copied = torch.cuda.Event()
-            copied.record(torch.cuda.current_stream(coords.device))
+            meta_host, copied = kernels.cuda.fetch_meta_async(built["meta"])
         sorted_idx = kernels.cuda.sorted_idx_from_binary(built["binary_code"], V)
         cache = SparseConv3dNeighborCache(neighbor_map=built["neighbor_map"], neighbor_map_bwd=built["neighbor_map_bwd"],
                                           gray_code=built["gray_code"], sorted_idx=sorted_idx)

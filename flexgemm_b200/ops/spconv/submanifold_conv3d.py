@@ -104,10 +104,7 @@ class SubMConv3dFunction(Function):
             # The one host round trip of the build: the pair count sizes the lists, and
             # the same copy brings the build's status word (hash table overflow).  The
             # copy is queued before the sort so that the host wait overlaps the sort.
-            meta_host = torch.empty(built["meta"].shape, dtype=built["meta"].dtype, pin_memory=True)
-            meta_host.copy_(built["meta"], non_blocking=True)
-            copied = torch.cuda.Event()
-            copied.record(torch.cuda.current_stream(coords.device))
+            meta_host, copied = kernels.cuda.fetch_meta_async(built["meta"])
         sorted_idx = kernels.cuda.sorted_idx_from_binary(built["binary_code"], V)
         cache = SubMConv3dNeighborCache(neighbor_map=built["neighbor_map"], gray_code=built["gray_code"], sorted_idx=sorted_idx)
         if needs_grad:

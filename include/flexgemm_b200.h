@@ -78,7 +78,14 @@ int64_t fgb_map_num_blocks(int64_t n);
  * (kernels/cuda/spconv/migemm_neighmap_pp.cu:19-44, 85-154).
  *
  * coords: int32 [n,4] (b,x,y,z), 16-byte aligned.  table: fgb_hash_table_bytes
- * bytes; its content on entry is ignored.  slots >= n.  V <= 32. */
+ * bytes; its content on entry is ignored.  slots >= n.  V <= 32.
+ *
+ * Rows that arrive in ascending flat-index order -- lexicographic (b, x, y, z),
+ * without duplicates -- need no table for the 3x3x3, dilation-1 stencil (a
+ * row's position is its rank among the keys): a check kernel decides on the
+ * device, without a host round trip, whether the map is built by windowed
+ * binary searches in the sorted input or by the hash table; the table memory
+ * is then left untouched.  The map is the same either way. */
 int fgb_subm_build_neighbor_map(const int32_t* coords, int64_t n,
                                 int W, int H, int D,
                                 int Kw, int Kh, int Kd,
