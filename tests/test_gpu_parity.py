@@ -121,6 +121,48 @@ def test_cache_tight_table_and_unsorted(K):
     check_cache(build_cache(coords, (1, 0, 32, 32, 32)), orc.neighbor_cache(coords, (1, 0, 32, 32, 32)), 27)
 
 
+def test_sorted_and_hash_paths_agree(K):
+    """Input in ascending key order takes the table-free path, anything else the
+    hash table: the same voxels shuffled give the same map up to the row
+    permutation, and sorted 64-bit keys work too."""
+    rng = np.random.default_rng(11)
+    base = orc.shell_coords(40, batch=2, scales=(1.0, 0.6))
+    shape = (2, 0, 40, 40, 40)
+    ref = orc.neighbor_cache(base, shape)
+    check_cache(build_cache(base, shape), ref, 27)                       # sorted
+    perm = rng.permutation(base.shape[0])
+    shuffled = np.ascontiguousarray(base[perm])
+    got = u32(build_cache(shuffled, shape)["neighbor_map"])              # hash path
+    inv = np.empty_like(perm)
+    inv[perm] = np.arange(perm.size)
+    want = ref["neighbor_map"][perm]                                     # rows follow the voxels ...
+    want = np.where(want == orc.INVALID, orc.INVALID, inv[np.minimum(want, perm.size - 1)].astype(np.uint32))  # ... so do the entries
+    assert np.array_equal(got, want)
+    # sorted coordinates whose flat index needs 64 bits
+    far = base.copy()
+    far[:, 0] += 6
+    far[:, 1:] += 1024 - 40
+    big = (8, 0, 1024, 1024, 1024)
+    check_cache(build_cache(far, big), orc.neighbor_cache(far, big), 27)
+
+
+def test_sorted_path_windows_longer_than_shared_memory(K):
+    """A sparse plane between two dense ones: the 256 voxels of a block span the
+    whole sparse plane, so the window of the next plane holds thousands of keys
+    and is searched in global memory."""
+    g = np.arange(64)
+    yy, zz = np.meshgrid(g, g, indexing="ij")
+    dense = np.stack([yy.ravel(), zz.ravel()], axis=1)
+    sparse = dense[(dense[:, 0] % 5 == 0) & (dense[:, 1] % 3 == 0)]
+    planes = []
+    for x, pts in ((10, dense), (11, sparse), (12, dense), (13, sparse[::7]), (14, dense)):
+        planes.append(np.concatenate([np.zeros((len(pts), 1), int), np.full((len(pts), 1), x), pts], axis=1))
+    coords = np.ascontiguousarray(np.concatenate(planes).astype(np.int32))
+    shape = (1, 0, 64, 64, 64)
+    assert np.all(np.diff(((coords[:, 1].astype(np.int64) * 64) + coords[:, 2]) * 64 + coords[:, 3]) > 0)
+    check_cache(build_cache(coords, shape), orc.neighbor_cache(coords, shape), 27)
+
+
 def test_cache_deterministic(K):
     coords = orc.shell_coords(64)
     a = build_cache(coords, (1, 0, 64, 64, 64))
