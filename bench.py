@@ -21,6 +21,8 @@ number of kernels launched and the SM clocks sampled during the timed region.
 --workload res1024_batch8 runs the high-resolution sharded batch instead (8
 shells at RES=1024, C=64, fp16, whole samples dealt to the ranks, strong
 scaling); its line carries the metric, the per-rank balance and the clocks only.
+--workload res1024_map [--unsorted] times the neighbour-cache build alone on two
+shells at RES=1024 and reports its algorithmic GB/s against the HBM peak.
 """
 import argparse
 import json
@@ -463,6 +465,59 @@ def run_sharded_batch(args):
         dist.destroy_process_group()
 
 
+def run_map_build(args):
+    """Neighbour-cache build alone at a size where HBM matters: two shells at
+    RES=1024 (5.3 M voxels, 56 M pairs, 32-bit keys), rows in key order (the
+    table-free path) or shuffled (``--unsorted``: the hash-table path).  Reports
+    the algorithmic bytes of the build per second against the measured HBM peak."""
+    from flexgemm_b200 import workloads
+    from flexgemm_b200.kernels import cuda as K
+    from flexgemm_b200.ops import spconv
+    from flexgemm_b200.ops.spconv import SubMConv3dFunction as F
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    spconv.set_algorithm(spconv.Algorithm.MASKED_IMPLICIT_GEMM_SPLITK)
+    B, res = 2, 1024
+    coords_h = torch.from_numpy(workloads.shell_coords(res, B, [1.0] * B))
+    if args.unsorted:
+        coords_h = coords_h[torch.randperm(coords_h.shape[0], generator=torch.Generator().manual_seed(1))].contiguous()
+    coords = coords_h.to(dev)
+    n = coords.shape[0]
+    shape = torch.Size((B, 64, res, res, res))
+
+    def build():
+        return F._compute_neighbor_cache(coords, shape, (3, 3, 3), (1, 1, 1), True)
+
+    for _ in range(max(args.warmup, 3)):
+        cache = build()
+    K.check_status(dev)
+    launches0 = K.launch_count
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    ms = time_loop(build, args.steps)
+    launches = K.launch_count - launches0
+    clocks = sampler.stop()
+    pairs = int(cache["valid_signal_i"].shape[0])
+    V, k = 27, 4
+    slots = int(spconv.HASHMAP_RATIO * n)
+    nbytes = (16 * n + k * slots + (k + 4) * n) + (16 * n + 13 * n * k + 4 * (pairs - n) // 2 + 4 * V * n) + \
+             (4 * V * n + 4 * n + 8 * n + 8 * pairs)
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    peak = float(peaks["hbm_gbs"])
+    print(json.dumps({
+        "metric": "neighbor-cache build, algorithmic GB/s (2 shells at RES=1024)", "value": gbs, "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+        "config": {"workload": f"hash/neighbour map + sort + pair lists, N={n} voxels, L={pairs} pairs, 32-bit keys, "
+                               f"rows {'shuffled (hash-table path)' if args.unsorted else 'in key order (table-free path)'}",
+                   "l2": "working set (coords, table, map, lists: ~1.5 GB) far exceeds the 126 MB L2; no flush"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                     "algorithmic_bytes": nbytes, "peak_source": peaks["source"]},
+        "gpu_launches": launches, "clocks": clocks}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -470,13 +525,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="res256", choices=["res256", "res1024_batch8"],
-                    help="res256: the headline single-sample workload (default); res1024_batch8: the sharded high-resolution batch")
+    ap.add_argument("--workload", default="res256", choices=["res256", "res1024_batch8", "res1024_map"],
+                    help="res256: the headline single-sample workload (default); res1024_batch8: the sharded high-resolution "
+                         "batch; res1024_map: the neighbour-cache build alone at a size where HBM matters")
+    ap.add_argument("--unsorted", action="store_true", help="res1024_map: shuffle the rows (hash-table path)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.workload == "res1024_batch8":
         run_sharded_batch(args)
+    elif args.workload == "res1024_map":
+        run_map_build(args)
     else:
         run_gpu_arm(args)
 

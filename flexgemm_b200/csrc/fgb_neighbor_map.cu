@@ -288,9 +288,13 @@ constexpr int kCombos = 9;     // (dx, dy) pairs of the 3x3x3 stencil
 template <int kKeyBits>
 __global__ void __launch_bounds__(256) sorted_check_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, uint32_t* unsorted) {
   const uint32_t i = blockIdx.x * 256u + threadIdx.x;
-  if (i == 0 || i >= n) return;
-  const int4 a = __ldg(&coords[i - 1]), b = __ldg(&coords[i]);
-  if (g.template key<kKeyBits>(a.x, a.y, a.z, a.w) >= g.template key<kKeyBits>(b.x, b.y, b.z, b.w)) *unsorted = 1u;
+  bool bad = false;
+  if (i > 0 && i < n) {
+    const int4 a = __ldg(&coords[i - 1]), b = __ldg(&coords[i]);
+    bad = g.template key<kKeyBits>(a.x, a.y, a.z, a.w) >= g.template key<kKeyBits>(b.x, b.y, b.z, b.w);
+  }
+  // one store per warp at most, and none once the word is set (with shuffled input every thread would store otherwise)
+  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0 && *reinterpret_cast<volatile uint32_t*>(unsorted) == 0u) *unsorted = 1u;
 }
 
 // fills the table with the empty pattern unless the sorted-input path runs
