@@ -67,9 +67,34 @@ def test_argument_validation_without_launch(lib):
     assert lib.fgb_subm_conv_wgrad(16, 16, 16, 16, 16, 16, 0, 10, 100, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -5  # workspace
 
 
+def test_sparse_conv_entry_points_validate_without_launch(lib):
+    import ctypes
+    wo, ho, do = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    g = (3, 3, 3, 2, 2, 2, 1, 1, 1, 1, 1, 1)
+    assert lib.fgb_sparse_out_grid(16, 17, 9, *g, ctypes.byref(wo), ctypes.byref(ho), ctypes.byref(do)) == 0
+    assert (wo.value, ho.value, do.value) == (8, 9, 5)   # (n + 2p - d(k-1) - 1) // s + 1
+    assert lib.fgb_sparse_out_grid(16, 17, 9, 3, 3, 3, 0, 2, 2, 1, 1, 1, 1, 1, 1, ctypes.byref(wo), ctypes.byref(ho), ctypes.byref(do)) == -2
+    assert lib.fgb_sparse_out_coords_collect(0, 10, 8, 8, 8, *g, 0, 100, 48, 0, 16, 0, 0) == -3     # key width
+    assert lib.fgb_sparse_out_coords_collect(0, 10, 8, 8, 8, 3, 3, 4, 2, 2, 2, 1, 1, 1, 1, 1, 1, 0, 100, 32, 0, 16, 0, 0) == -2  # V > 32
+    assert lib.fgb_sparse_out_coords_collect(0, 10, 8, 8, 8, *g, 0, 100, 32, 0, 0, 0, 0) == -1      # null count
+    assert lib.fgb_sparse_out_coords_workspace_bytes(0, 32, 0) == 0
+    assert lib.fgb_sparse_out_coords_workspace_bytes(10, 32, 3) == -2
+    assert lib.fgb_sparse_out_coords_finalize(16, 5, 32, 1, 0, 1, 8, 8, 8, *g, 256, 1 << 20, 16, 0) == -2   # coord_bits for Morton
+    assert lib.fgb_sparse_build_neighbor_map(16, 10, 16, 5, 8, 8, 8, *g, 16, 5, 32, 16, 0, 16, 16, 16, 16, 0, 0) == -2   # slots < n_in
+    assert lib.fgb_sparse_build_neighbor_map(16, 10, 16, 5, 8, 8, 8, *g, 16, 20, 32, 16, 0, 16, 16, 16, 0, 0, 0) == -1   # null seg
+    assert lib.fgb_pp_gray_code(0, 10, 40, 0, 0, 0) == -2
+    assert lib.fgb_sparse_conv_workspace_bytes(0, 1000, 500, 64, 64, 27, _cabi.F32_IEEE, 1) == 256 + 500 * 3 * 64 * 4 + 64 * 64 * 27 * 3 * 4
+    assert lib.fgb_sparse_conv_workspace_bytes(1, 1000, 500, 64, 32, 27, _cabi.F32_IEEE, 1) == \
+        256 + 64 * 32 * 27 * 4 + 64 * 32 * 27 * 3 * 4 + 1000 * 3 * 32 * 4
+    assert lib.fgb_sparse_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 20, 60, 64, 27, _cabi.F16, 256, 256, 0, 0) == -4  # Ci % 8
+    assert lib.fgb_sparse_conv_wgrad(16, 16, 16, 16, 16, 16, 0, 10, 20, 500, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -2  # pairs > n_out*V
+
+
 def test_python_surface_matches_reference_names():
     for name in ("Algorithm", "ALGORITHM", "HASHMAP_RATIO", "set_algorithm", "set_hashmap_ratio", "SubMConv3dFunction",
-                 "SubMConv3dNeighborCache", "sparse_submanifold_conv3d"):
+                 "SubMConv3dNeighborCache", "sparse_submanifold_conv3d", "SparseConv3dFunction", "SparseConv3dNeighborCache",
+                 "sparse_conv3d", "SerializationMode", "SparseConv3dOutCoordAlgorithm", "OUT_COORD_ALGO", "OUT_COORD_HASHMAP_RATIO",
+                 "SERIALIZATION_MODE"):
         assert hasattr(spconv, name), name
     for name in ("_compute_neighbor_cache", "_compute_neighbor_cache_torch", "_sparse_submanifold_conv_forward",
                  "_sparse_submanifold_conv_backward"):

@@ -83,3 +83,32 @@ def test_serialised_orders_are_permutations_of_the_bxyz_order():
         assert got.shape == base.shape and not np.array_equal(got, base)
         assert np.array_equal(np.unique(got, axis=0), base)
         assert np.all(np.diff(got[:, 0]) >= 0)  # batch index sits on top of the key
+
+
+@pytest.mark.parametrize("tag", [t for t in TAGS if t + ".out" in SP.files])
+def test_host_side_torch_path_of_the_package_matches_reference(tag):
+    """The package's own library-only helpers (the torch constructions the
+    reference also ships, usable without a GPU) against the golden vectors:
+    output coordinates, both maps, explicit forward and backward."""
+    from flexgemm_b200.ops import spconv
+    from flexgemm_b200.ops.spconv import SparseConv3dFunction as F
+    spconv.set_algorithm(spconv.Algorithm.EXPLICIT_GEMM)
+    try:
+        coords = torch.from_numpy(np.ascontiguousarray(SP[tag + ".coords"]))
+        shape = torch.Size([int(v) for v in SP[tag + ".shape"]])
+        k, s, p, d = geom_of(tag)
+        oc = F._get_output_coords_torch(coords, shape, k, s, p, d)
+        assert np.array_equal(oc.numpy(), SP[tag + ".out_coords"])
+        cache = F._compute_neighbor_cache_torch(coords, oc, shape, k, s, p, d, True)
+        assert np.array_equal(cache["neighbor_map"].view(torch.int32).numpy().view(np.uint32), SP[tag + ".nbr"])
+        assert np.array_equal(cache["neighbor_map_bwd"].view(torch.int32).numpy().view(np.uint32), SP[tag + ".nbr_bwd"])
+        f = torch.from_numpy(SP[tag + ".feats"]).requires_grad_(True)
+        w = torch.from_numpy(SP[tag + ".weight"]).requires_grad_(True)
+        b = torch.from_numpy(SP[tag + ".bias"]).requires_grad_(True)
+        out = F._sparse_conv_forward(f, cache, w, b)
+        gin, gw, gb = F._sparse_conv_backward(torch.from_numpy(SP[tag + ".gout"]), f, cache, w, b)
+        for got, name in ((out, ".out"), (gin, ".gin"), (gw, ".gw"), (gb, ".gb")):
+            want = torch.from_numpy(SP[tag + name])
+            assert (got.detach() - want).abs().max() <= 1e-5 * want.abs().max().clamp_min(1.0)
+    finally:
+        spconv.set_algorithm(spconv.Algorithm.MASKED_IMPLICIT_GEMM_SPLITK)
