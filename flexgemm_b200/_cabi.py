@@ -37,6 +37,11 @@ _PROTOTYPES = {
     "fgb_bias_grad_workspace_bytes": (c_int64, [c_int]),
     "fgb_subm_conv_bias_grad": (c_int, [_P, _P, _P, c_int64, c_int, c_int, _P, c_int64, _P]),
     "fgb_cast_from_f32": (c_int, [_P, _P, c_int64, c_int, _P]),
+    "fgb_hash_insert_3d_idx_as_val": (c_int, [_P, c_int64, c_int, c_int, c_int, _P, c_int64, c_int, _P, _P]),
+    "fgb_hash_lookup_3d": (c_int, [_P, c_int64, c_int, c_int, c_int, _P, c_int64, c_int, _P, _P]),
+    "fgb_grid_sample_neighbor_map": (c_int, [_P, c_int64, c_int64, c_int, c_int, c_int, _P, c_int64, c_int, c_int, _P, _P, _P]),
+    "fgb_indice_weighted_sum_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int, c_int, _P]),
+    "fgb_indice_weighted_sum_bwd": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, _P]),
     "fgb_sparse_out_grid": (c_int, [c_int] * 15 + [_P, _P, _P]),
     "fgb_sparse_out_coords_collect": (c_int, [_P, c_int64] + [c_int] * 15 + [_P, c_int64, c_int, _P, _P, _P, _P]),
     "fgb_sparse_out_coords_workspace_bytes": (c_int64, [c_int64, c_int, c_int]),

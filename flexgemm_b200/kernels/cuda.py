@@ -464,3 +464,81 @@ def cast_from_f32(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     _cabi.check(rc, "fgb_cast_from_f32")
     _count(1)
     return out
+
+
+# --------------------------------------------------------------------------
+# generic table use and grid sample
+# --------------------------------------------------------------------------
+def hashmap_insert_3d_idx_as_val(table: torch.Tensor, key_bits: int, slots: int, coords: torch.Tensor, W: int, H: int, D: int) -> torch.Tensor:
+    """Clears ``table`` and inserts ``coords[i] -> i``; returns this call's device status word."""
+    _require_cuda(coords, "coords")
+    dev = coords.device
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    rc = _cabi.lib().fgb_hash_insert_3d_idx_as_val(_ptr(coords), coords.shape[0], int(W), int(H), int(D), table.data_ptr(), int(slots),
+                                                   int(key_bits), status.data_ptr(), _stream(dev))
+    _cabi.check(rc, "fgb_hash_insert_3d_idx_as_val")
+    _count(2)
+    return status
+
+
+def hashmap_lookup_3d(table: torch.Tensor, key_bits: int, slots: int, query_coords: torch.Tensor, W: int, H: int, D: int) -> torch.Tensor:
+    """uint32 [M]: row stored for each (b, x, y, z) query row, 0xffffffff where absent."""
+    dev = query_coords.device
+    out = torch.empty(query_coords.shape[0], dtype=torch.uint32, device=dev)
+    rc = _cabi.lib().fgb_hash_lookup_3d(_ptr(query_coords), query_coords.shape[0], int(W), int(H), int(D), table.data_ptr(), int(slots),
+                                        int(key_bits), _ptr(out), _stream(dev))
+    _cabi.check(rc, "fgb_hash_lookup_3d")
+    _count(1)
+    return out
+
+
+def grid_sample_neighbor_map(table: torch.Tensor, key_bits: int, slots: int, query: torch.Tensor, W: int, H: int, D: int,
+                             trilinear: bool):
+    """``query`` fp32 [B, L, 3] -> neighbor uint32 [B, L] (nearest) or (neighbor [B, L, 8], weight fp32 [B, L, 8])."""
+    dev = query.device
+    B, L = query.shape[:2]
+    if trilinear:
+        nb = torch.empty((B, L, 8), dtype=torch.uint32, device=dev)
+        w = torch.empty((B, L, 8), dtype=torch.float32, device=dev)
+    else:
+        nb = torch.empty((B, L), dtype=torch.uint32, device=dev)
+        w = None
+    rc = _cabi.lib().fgb_grid_sample_neighbor_map(_ptr(query), B, L, int(W), int(H), int(D), table.data_ptr(), int(slots), int(key_bits),
+                                                  1 if trilinear else 0, _ptr(nb), _ptr(w), _stream(dev))
+    _cabi.check(rc, "fgb_grid_sample_neighbor_map")
+    _count(1)
+    return (nb, w) if trilinear else nb
+
+
+def _elem_code(dtype: torch.dtype) -> int:
+    if dtype in _DTYPES:
+        return _DTYPES[dtype]
+    if dtype == torch.float32:
+        return _cabi.F32_IEEE
+    raise TypeError(f"unsupported feature dtype {dtype}: expected float16, bfloat16 or float32")
+
+
+def indice_weighted_sum_fwd(feats: torch.Tensor, indices: torch.Tensor, weight: Optional[torch.Tensor]) -> torch.Tensor:
+    """feats [N, C], indices uint32 [M, V], weight fp32 [M, V] or None -> [M, C]."""
+    dev = feats.device
+    M, V = indices.shape
+    C = feats.shape[1]
+    out = torch.empty((M, C), dtype=feats.dtype, device=dev)
+    rc = _cabi.lib().fgb_indice_weighted_sum_fwd(_ptr(feats), _ptr(indices), _ptr(weight), _ptr(out), M, C, V, _elem_code(feats.dtype),
+                                                 _stream(dev))
+    _cabi.check(rc, "fgb_indice_weighted_sum_fwd")
+    _count(1)
+    return out
+
+
+def indice_weighted_sum_bwd(grad_out: torch.Tensor, indices: torch.Tensor, weight: Optional[torch.Tensor], n: int) -> torch.Tensor:
+    """grad_out [M, C] -> fp32 [n, C]: the scatter-add of the weighted rows."""
+    dev = grad_out.device
+    M, V = indices.shape
+    C = grad_out.shape[1]
+    out = torch.empty((n, C), dtype=torch.float32, device=dev)
+    rc = _cabi.lib().fgb_indice_weighted_sum_bwd(_ptr(grad_out), _ptr(indices), _ptr(weight), _ptr(out), M, n, C, V,
+                                                 _elem_code(grad_out.dtype), _stream(dev))
+    _cabi.check(rc, "fgb_indice_weighted_sum_bwd")
+    _count(1)
+    return out

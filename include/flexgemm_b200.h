@@ -341,6 +341,49 @@ int fgb_sparse_conv_wgrad(const void* grad_out, const void* feats,
                           void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
 int64_t fgb_sparse_conv_workspace_bytes(int pass, int64_t n_out, int64_t n_in, int Ci, int Co, int V, int dtype, int splitk);
 
+/* ------------------------------------------------------------------------
+ * Generic use of the coordinate table, and the sparse grid sample built on it
+ * (flex_gemm/ops/grid_sample/grid_sample.py, kernels/cuda/grid_sample/
+ * grid_sample.cu, kernels/cuda/hash/hash.cu, kernels/triton/grid_sample/).
+ * --------------------------------------------------------------------- */
+
+/* Clears the table and inserts coords[i] -> i.  Stands in for
+ * hashmap_insert_3d_idx_as_val (hash/hash.cu:369-449).  slots >= n. */
+int fgb_hash_insert_3d_idx_as_val(const int32_t* coords, int64_t n, int W, int H, int D,
+                                  void* table, int64_t slots, int key_bits, int32_t* status, void* stream);
+
+/* out_rows[i] = row stored for query_coords[i] (int32 [m,4] rows (b,x,y,z)) or
+ * 0xffffffff; coordinates outside the grid are reported as absent.  Stands in
+ * for hashmap_lookup_3d (hash/hash.cu:296-365). */
+int fgb_hash_lookup_3d(const int32_t* query_coords, int64_t m, int W, int H, int D,
+                       void* table, int64_t slots, int key_bits, uint32_t* out_rows, void* stream);
+
+/* Neighbour map of B*L float query points (x, y, z) in voxel units, batch b =
+ * point / L, against a table built by fgb_hash_insert_3d_idx_as_val.
+ * trilinear == 0: neighbor[q] = row of the voxel (int)x, (int)y, (int)z
+ * (grid_sample.cu:26-55).  trilinear != 0: neighbor[q, 0..7] / weight[q, 0..7]
+ * = rows and normalised trilinear weights of the eight voxels around the point,
+ * corner k at floor(q - 0.5) + (k & 1, (k >> 1) & 1, (k >> 2) & 1)
+ * (grid_sample.cu:149-194); absent corners get 0xffffffff and weight 0 (the
+ * reference leaves row 0 there for corners 1..7; their weight is 0 either way). */
+int fgb_grid_sample_neighbor_map(const float* query, int64_t B, int64_t L, int W, int H, int D,
+                                 void* table, int64_t slots, int key_bits, int trilinear,
+                                 uint32_t* neighbor, float* weight, void* stream);
+
+/* out[m, :] = sum_k weight[m, k] * feats[indices[m, k], :] over the valid
+ * entries (weight may be null: all ones).  feats [*, C], out [M, C] of element
+ * type dtype, indices uint32 [M, V], weight fp32 [M, V]; C % 4 == 0.  Stands in
+ * for indice_weighed_sum_fwd (kernels/triton/grid_sample/indice_weighed_sum_fwd.py). */
+int fgb_indice_weighted_sum_fwd(const void* feats, const uint32_t* indices, const float* weight, void* out,
+                                int64_t M, int C, int V, int dtype, void* stream);
+
+/* grad_feats_f32[indices[m, k], :] += weight[m, k] * grad_out[m, :]; the fp32
+ * buffer [N, C] is zeroed by the call and filled with atomic adds.  Stands in
+ * for indice_weighed_sum_bwd_input (…/indice_weighed_sum_bwd.py), which adds
+ * in the feature dtype. */
+int fgb_indice_weighted_sum_bwd(const void* grad_out, const uint32_t* indices, const float* weight,
+                                float* grad_feats_f32, int64_t M, int64_t N, int C, int V, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
