@@ -8,13 +8,15 @@
 // (the K index) holding 128 bytes of channels, i.e. both operands are MN-major
 // for tcgen05.mma.  A CTA owns (offset, split, group of up to 256 output
 // channels, tile of up to 256 input channels); its accumulators (one or two
-// 128-row blocks) fill up to all 512 TMEM columns.  The pair range of an
-// offset is cut into `splitk` parts; each CTA writes an fp32 partial slab and
-// a second kernel adds the slabs in a fixed order.
+// 128-row blocks) fill up to all 512 TMEM columns.  The pair lists are cut into
+// units of equal length (about `splitk` per offset on average, an offset with
+// more pairs gets more units); each CTA writes an fp32 partial slab and a
+// second kernel adds the slabs of an offset in a fixed order.
 //
-// Warp roles (192 threads): warps 0-3 gather (cp.async 16 B, pair indices
-// double-buffered in shared memory) and run the epilogue, warp 5 lane 0 issues
-// the MMAs; warp 4 is idle (kept so the role layout matches the fprop kernel).
+// Warp roles (416 threads): warps 0-3 epilogue (tcgen05.ld -> fp32 slab),
+// warp 4 owns the TMEM allocation and lane 0 issues the MMAs, warps 5-12 gather
+// both operands (cp.async 16 B, pair indices prefetched into registers one stage
+// ahead, completion signalled per thread on the stage's mbarrier).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
