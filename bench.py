@@ -282,25 +282,58 @@ def run_gpu_arm(args):
     loss_h = torch.empty(1, dtype=torch.float32).pin_memory()
     gw_h = torch.empty(weight.shape, dtype=torch.float16).pin_memory()
 
-    def e2e_step():
-        c = coords_h.to(dev, non_blocking=True)
-        f = feats_h.to(dev, non_blocking=True).requires_grad_(True)
-        w = weight.detach().requires_grad_(True)
-        bb = bias.detach().requires_grad_(True)
-        out, _ = spconv.sparse_submanifold_conv3d(f, c, shape, w, bb)
-        loss = out.float().sum()
-        loss.backward()
-        gw = w.grad
-        if world > 1:
-            dist.all_reduce(gw)
-        loss_h.copy_(loss.detach().reshape(1), non_blocking=True)
-        gw_h.copy_(gw, non_blocking=True)
+    copy_stream = torch.cuda.Stream(device=dev)
 
-    for _ in range(2):
-        e2e_step()
+    def start_copies():
+        """Queues one step's host-to-device copies on the copy stream: coordinates first (the
+        neighbour cache needs only them), then the 32x larger features."""
+        main = torch.cuda.current_stream(dev)
+        with torch.cuda.stream(copy_stream):
+            c = coords_h.to(dev, non_blocking=True)
+            c_ready = torch.cuda.Event()
+            c_ready.record(copy_stream)
+            f = feats_h.to(dev, non_blocking=True)
+            f_ready = torch.cuda.Event()
+            f_ready.record(copy_stream)
+        c.record_stream(main)
+        f.record_stream(main)
+        return c, c_ready, f, f_ready
+
+    def e2e_run(iters: int):
+        """``iters`` steps through the public API.  Every step's inputs come from pinned host memory
+        and its loss and weight gradient go back to the host; as an input pipeline would, the copies of
+        step k+1 are queued while step k computes."""
+        main = torch.cuda.current_stream(dev)
+        pending = start_copies()
+        for k in range(iters):
+            c, c_ready, f, f_ready = pending
+            if k + 1 < iters:
+                pending = start_copies()
+            main.wait_event(c_ready)
+            cache_e = F._compute_neighbor_cache(c, shape, (3, 3, 3), (1, 1, 1), True)
+            main.wait_event(f_ready)
+            f.requires_grad_(True)
+            w = weight.detach().requires_grad_(True)
+            bb = bias.detach().requires_grad_(True)
+            out, _ = spconv.sparse_submanifold_conv3d(f, c, shape, w, bb, neighbor_cache=cache_e)
+            loss = out.float().sum()
+            loss.backward()
+            gw = w.grad
+            if world > 1:
+                dist.all_reduce(gw)
+            loss_h.copy_(loss.detach().reshape(1), non_blocking=True)
+            gw_h.copy_(gw, non_blocking=True)
+
+    e2e_run(2)
     if world > 1:
         dist.barrier()
-    e2e_ms = time_loop(e2e_step, e2e_steps)
+    torch.cuda.synchronize()
+    ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ea.record()
+    e2e_run(e2e_steps)
+    eb.record()
+    torch.cuda.synchronize()
+    e2e_ms = ea.elapsed_time(eb) / e2e_steps
     t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -356,7 +389,7 @@ def run_gpu_arm(args):
         "map_build_ms": map_ms,
         "roofline": roofline, "roofline_map_build": roofline_map, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": t.item(), "includes": "H2D of coords+feats, neighbour-map build, fwd, bwd, D2H of loss and grad_weight"},
+                "ms_per_step": t.item(), "includes": "per step: H2D of coords+feats from pinned memory on a copy stream (the next step's copies are queued while the current step computes), neighbour-map build, fwd, bwd, D2H of loss and grad_weight"},
         "gpu_launches": launches, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
