@@ -79,17 +79,21 @@ def _cuda_local_grads(grad_out, feats, cache, weight_cvc, has_bias):
     return gw32, gb32
 
 
-def allreduce_param_grads(gw32: torch.Tensor, gb32: Optional[torch.Tensor], group=None):
+def allreduce_param_grads(gw32: torch.Tensor, gb32: Optional[torch.Tensor], group=None, async_op: bool = False):
     """Sum the fp32 weight (and bias) gradient over the ranks with a single
-    all-reduce of one flat buffer; returns views of the reduced buffer."""
+    all-reduce of one flat buffer; returns views of the reduced buffer (and,
+    with ``async_op``, the work handle to wait on before they are read -- None
+    when there is nothing to reduce)."""
     nw = gw32.numel()
     flat = torch.empty(nw + (gb32.numel() if gb32 is not None else 0), dtype=torch.float32, device=gw32.device)
     flat[:nw].copy_(gw32.reshape(-1))
     if gb32 is not None:
         flat[nw:].copy_(gb32.reshape(-1))
+    work = None
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
-    return flat[:nw].view_as(gw32), (flat[nw:].view_as(gb32) if gb32 is not None else None)
+        work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+    views = (flat[:nw].view_as(gw32), (flat[nw:].view_as(gb32) if gb32 is not None else None))
+    return (*views, work) if async_op else views
 
 
 def sharded_backward(grad_out: torch.Tensor, feats: torch.Tensor, cache, weight: torch.Tensor, bias: Optional[torch.Tensor],
@@ -108,15 +112,19 @@ def sharded_backward(grad_out: torch.Tensor, feats: torch.Tensor, cache, weight:
         gb32, join = None, None
         if bias is not None:  # small reduction: runs beside the conv kernels on a side stream
             _, gb32, join = K.bias_grad_overlapped(grad_out, want_f32=True, want_dtype=False)
-        if want_input_grad:
-            tile = K.conv_tile_rows()
-            grad_in = K.conv_dgrad(grad_out, w, cache["neighbor_map"], cache["sorted_idx"], cache.tile_masks(tile), cache.block_order(tile))
+        # parameter gradients first, so that their all-reduce travels while the input gradient is computed
         gw32, _ = _cuda_local_grads(grad_out, feats, cache, w, False)
         if join is not None:
             join()
+        gw32, gb32, work = allreduce_param_grads(gw32, gb32, group, async_op=True)
+        if want_input_grad:
+            tile = K.conv_tile_rows()
+            grad_in = K.conv_dgrad(grad_out, w, cache["neighbor_map"], cache["sorted_idx"], cache.tile_masks(tile), cache.block_order(tile))
+        if work is not None:
+            work.wait()
     else:
         grad_in, gw32, gb32 = local_grads(grad_out, feats, cache, w, bias is not None)
-    gw32, gb32 = allreduce_param_grads(gw32, gb32, group)
+        gw32, gb32 = allreduce_param_grads(gw32, gb32, group)
     if gw32.is_cuda and weight.dtype != torch.float32:
         from .kernels import cuda as K
         gw = K.cast_from_f32(gw32, weight.dtype)

@@ -430,3 +430,29 @@ def test_residual_stack_with_shared_cache(K):
     assert rel_err(xd.grad, xr.grad) <= 2e-2
     for a, b in zip(wd + bd, wr + br):
         assert rel_err(a.grad, b.grad) <= 2e-2
+
+
+def test_sharded_backward_on_the_kernels_matches_the_sum_over_shards(K):
+    """The multi-GPU backward (fp32 parameter gradients, one all-reduce, cast) run
+    as a single rank per shard on one GPU: summing the shards' fp32 gradients by
+    hand must give the unsharded gradient, and each shard's feature gradient must
+    equal the rows of the unsharded one."""
+    from flexgemm_b200 import sharding
+    from flexgemm_b200.ops.spconv import SubMConv3dFunction as F
+    coords_np, feats, weight, bias, shape = orc.make_problem(24, 64, 64, "float16", seed=12, batch=3, scales=(1.0, 0.8, 0.6))
+    g = torch.Generator().manual_seed(2)
+    gout = torch.randn(coords_np.shape[0], 64, generator=g).half()
+    nbr = orc.neighbor_map(coords_np.numpy(), shape)
+    ref_gin, ref_gw, ref_gb = orc.conv_backward(gout.double(), feats.double(), nbr, weight.double())
+    w, b = weight.to(DEV), bias.to(DEV)
+    total_w = torch.zeros_like(ref_gw)
+    total_b = torch.zeros_like(ref_gb)
+    for rank in range(2):
+        c, f, lshape, rows = sharding.local_shard(coords_np, feats, shape, rank, 2)
+        cache = F._compute_neighbor_cache(c.to(DEV), lshape, (3, 3, 3), (1, 1, 1), True)
+        gin, gw, gb = sharding.sharded_backward(gout[rows].to(DEV), f.to(DEV), cache, w, b)   # no process group: world of one
+        assert gw.dtype == torch.float16 and gw.shape == weight.shape
+        assert rel_err(gin, ref_gin[rows]) <= 1e-2
+        total_w += gw.double().cpu()
+        total_b += gb.double().cpu()
+    assert rel_err(total_w, ref_gw) <= 1e-2 and rel_err(total_b, ref_gb) <= 1e-2
