@@ -181,8 +181,8 @@ __global__ void seg_prefix_kernel(uint32_t* seg, int V) {
 }
 
 // ------------------------------------------------------------------ sorted-input path
-constexpr int kWinMax = 320;   // keys of one (dx, dy) window held in shared memory (sized so that five CTAs fit an SM); longer windows are searched in global memory
-constexpr int kCombos = 9;     // (dx, dy) pairs of the 3x3x3 stencil
+constexpr int kCombos = 9;          // (dx, dy) pairs of the 3x3x3 stencil
+constexpr int kLocalSlots = 1024;   // slots of a CTA's own shared-memory table over its 256 voxels (load factor 1/4)
 
 // *unsorted = 1 when some key is not greater than its predecessor (the word must be 0 on entry)
 template <int kKeyBits>
@@ -209,13 +209,24 @@ __device__ __forceinline__ long long key_at(const int4* __restrict__ coords, uin
   return static_cast<long long>(g.template key<kKeyBits>(c.x, c.y, c.z, c.w));
 }
 
+template <typename K>
+__device__ __forceinline__ uint32_t local_home(K key) {
+  uint32_t k32 = static_cast<uint32_t>(key);
+  if constexpr (sizeof(K) == 8) k32 ^= static_cast<uint32_t>(static_cast<unsigned long long>(key) >> 32) * 0x85EBCA6Bu;
+  return (k32 * 0x9E3779B1u) >> 22;  // top 10 bits: kLocalSlots = 1024
+}
+static_assert(kLocalSlots == 1024 && kLocalSlots == 4 * kMapBlock, "local_home() returns 10 bits; the table is cleared with one 16-byte store per thread");
+
 // One CTA per 256 voxels (the blocking of the hash lookup, so the side products
-// are the same), thread t owns voxel t.  For each (dx, dy) the keys the CTA can
-// ask for lie between key_first + delta - 1 and key_last + delta + 1: two
-// binary searches in the sorted input bound that window, its keys go to shared
-// memory, and each thread then finds key + delta - 1 by binary search in the
-// window; key + delta and key + delta + 1, when present, are the next entries.
-// The position of a hit in the input is the neighbour's row.
+// are the same).  With the rows in key order a row's position is its rank, so no
+// global table is needed: the voxels that can be neighbours of the CTA's voxels
+// at (dx, dy, *) have keys between key_first + delta - 1 and key_last + delta + 1,
+// a contiguous run of rows whose ends two binary searches find.  The CTA keeps a
+// small shared-memory table over its OWN 256 keys, streams the nine runs once
+// (coalesced) and lets every streamed row look for the up to three voxels it is a
+// neighbour of (itself minus (dx, dy, dz), dz = -1, 0, 1) -- a hit writes the
+// streamed row's number into that voxel's map row.  All probes are independent
+// shared-memory reads; nothing depends on the length of a run.
 template <int kKeyBits>
 __global__ void __launch_bounds__(kMapBlock)
     subm_sorted_lookup_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, uint32_t* __restrict__ nbr,
@@ -223,96 +234,145 @@ __global__ void __launch_bounds__(kMapBlock)
                               uint32_t nblk, const uint32_t* __restrict__ unsorted) {
   using K = typename std::conditional<kKeyBits == 32, uint32_t, unsigned long long>::type;
   if (*unsorted != 0u) return;  // the hash kernels build the map
-  extern __shared__ __align__(16) uint8_t dyn_smem[];
-  int4* s_coord = reinterpret_cast<int4*>(dyn_smem);                       // [256]
-  uint32_t* s_nbr = reinterpret_cast<uint32_t*>(dyn_smem + kMapBlock * 16);  // [256 * 27]
-  K* s_win = reinterpret_cast<K*>(dyn_smem + kMapBlock * 16 + kMapBlock * 27 * 4);  // [9][kWinMax]
+  __shared__ __align__(16) uint32_t s_nbr[kMapBlock * 27];
+  __shared__ __align__(16) uint32_t s_slot[kLocalSlots];  // local voxel index, kInvalid = empty
+  __shared__ K s_key[kMapBlock];
   __shared__ uint32_t s_lo[kCombos], s_hi[kCombos];
   __shared__ uint32_t s_count[32];
   const uint32_t n0 = blockIdx.x * kMapBlock;
   const uint32_t nv = min(static_cast<uint32_t>(kMapBlock), n - n0);
   const int t = threadIdx.x, lane = t & 31;
-  if (t < nv) s_coord[t] = __ldg(&coords[n0 + t]);
+  {
+    const uint4 inv = make_uint4(kInvalid, kInvalid, kInvalid, kInvalid);
+    reinterpret_cast<uint4*>(s_slot)[t] = inv;  // kLocalSlots / 4 == kMapBlock
+#pragma unroll
+    for (int i = t; i < kMapBlock * 27 / 4; i += kMapBlock) reinterpret_cast<uint4*>(s_nbr)[i] = inv;
+  }
   if (t < 32) s_count[t] = 0;
+  K key = 0;
+  if (t < nv) {
+    const int4 cc = __ldg(&coords[n0 + t]);
+    key = g.template key<kKeyBits>(cc.x, cc.y, cc.z, cc.w);
+    s_key[t] = key;
+  }
   __syncthreads();
 
   const long long HD = static_cast<long long>(g.H) * g.D;
-  if (t < 2 * kCombos) {
-    // window bounds: thread 2c finds the first row with key >= key_first + delta - 1, thread 2c + 1 the first
-    // row with key > key_last + delta + 1
-    const int c = t >> 1;
-    const bool upper = t & 1;
-    const long long delta = (c / 3 - 1) * HD + (c % 3 - 1) * static_cast<long long>(g.D);
-    const int4 e = upper ? s_coord[nv - 1] : s_coord[0];
-    const long long target = static_cast<long long>(g.template key<kKeyBits>(e.x, e.y, e.z, e.w)) + delta + (upper ? 1 : -1);
-    uint32_t lo = 0, hi = n;
-    while (lo < hi) {
-      const uint32_t mid = lo + ((hi - lo) >> 1);
-      const long long km = key_at<kKeyBits>(coords, mid, g);
-      if (upper ? km <= target : km < target) lo = mid + 1;
-      else hi = mid;
+  if (t < nv) {  // keys are distinct (strictly increasing), so every insert ends on an empty slot
+    uint32_t slot = local_home<K>(key);
+    while (atomicCAS(&s_slot[slot], kInvalid, static_cast<uint32_t>(t)) != kInvalid) slot = (slot + 1) & (kLocalSlots - 1);
+  }
+  {
+    // Run bounds, one group of eight lanes per bound (18 of the CTA's 32 groups): group 2c finds the first row with
+    // key >= key_first + delta - 1, group 2c + 1 the first row with key > key_last + delta + 1.  Each step the eight
+    // lanes test eight pivots that cut the range into nine parts, so a bound costs about log9(n) dependent loads
+    // instead of log2(n).
+    const int grp = t >> 3, gl = t & 7;
+    if (grp < 2 * kCombos) {
+      const unsigned gmask = 0xFFu << (lane & 24);
+      const int c = grp >> 1;
+      const bool upper = grp & 1;
+      const long long delta = (c / 3 - 1) * HD + (c % 3 - 1) * static_cast<long long>(g.D);
+      const long long target = static_cast<long long>(upper ? s_key[nv - 1] : s_key[0]) + delta + (upper ? 1 : -1);
+      // invariant: rows < lo go left of the bound, rows >= hi do not
+      uint32_t lo = 0, hi = n;
+      while (hi - lo > 8u) {
+        // pivot k of 1..8 sits at lo + floor(span * k / 9) = lo + step * k + floor(rem * k / 9); rem * k <= 72, where
+        // (x * 57) >> 9 equals x / 9
+        const uint32_t span = hi - lo, step = span / 9u, rem = span - step * 9u;
+        auto pivot_at = [&](uint32_t k) { return lo + step * k + ((rem * k * 57u) >> 9); };
+        const uint32_t pivot = pivot_at(gl + 1);  // lo < pivot < hi, increasing in gl
+        const long long km = key_at<kKeyBits>(coords, pivot, g);
+        const bool left = upper ? km <= target : km < target;
+        const unsigned votes = (__ballot_sync(gmask, left) >> (lane & 24)) & 0xFFu;  // monotone: a prefix of ones
+        const int cnt = __popc(votes);
+        const uint32_t p_prev = pivot_at(cnt);      // last pivot that went left (cnt > 0)
+        const uint32_t p_next = pivot_at(cnt + 1);  // first pivot that did not (cnt < 8)
+        if (cnt < 8) hi = p_next;
+        if (cnt > 0) lo = p_prev + 1;
+      }
+      {
+        const uint32_t r = lo + gl;
+        bool left = false;
+        if (r < hi) {
+          const long long km = key_at<kKeyBits>(coords, r, g);
+          left = upper ? km <= target : km < target;
+        }
+        const unsigned votes = (__ballot_sync(gmask, left) >> (lane & 24)) & 0xFFu;
+        lo += __popc(votes);
+      }
+      if (gl == 0) {
+        if (upper) s_hi[c] = lo;
+        else s_lo[c] = lo;
+      }
     }
-    if (upper) s_hi[c] = lo;
-    else s_lo[c] = lo;
   }
   __syncthreads();
-  // all windows as one flat list of kCombos * kWinMax slots, so that a thread's loads are independent of one another
-#pragma unroll 4
-  for (uint32_t slot = t; slot < kCombos * kWinMax; slot += kMapBlock) {
-    const uint32_t c = slot / kWinMax, j = slot - c * kWinMax;
-    const uint32_t ws = s_lo[c], len = s_hi[c] > ws ? s_hi[c] - ws : 0u;
-    if (len <= kWinMax && j < len) s_win[slot] = static_cast<K>(key_at<kKeyBits>(coords, ws + j, g));
+
+  // the nine runs as one flat list, so that every thread gets the same share whatever the runs' lengths
+  uint32_t off[kCombos + 1];
+  off[0] = 0;
+#pragma unroll
+  for (int c = 0; c < kCombos; ++c) off[c + 1] = off[c] + (s_hi[c] > s_lo[c] ? s_hi[c] - s_lo[c] : 0u);
+#pragma unroll 2
+  for (uint32_t f = t; f < off[kCombos]; f += kMapBlock) {
+    // which run f falls into: first dx (runs 0-2, 3-5, 6-8), then dy
+    const int gx = (f >= off[3]) + (f >= off[6]);
+    const uint32_t o1 = gx == 0 ? off[1] : gx == 1 ? off[4] : off[7], o2 = gx == 0 ? off[2] : gx == 1 ? off[5] : off[8];
+    const int gy = (f >= o1) + (f >= o2);
+    const uint32_t base = gy == 0 ? (gx == 0 ? 0u : gx == 1 ? off[3] : off[6]) : gy == 1 ? o1 : o2;
+    const int c = gx * 3 + gy;
+    const uint32_t row = s_lo[c] + (f - base);
+    const int4 e = __ldg(&coords[row]);
+    const int dx = gx - 1, dy = gy - 1;
+    const int xs = e.y - dx, ys = e.z - dy;  // the voxels this row is a (dx, dy, dz) neighbour of: (b, xs, ys, z - dz)
+    if (xs < 0 || xs >= g.W || ys < 0 || ys >= g.H) continue;
+    const K row0 = g.template key<kKeyBits>(e.x, xs, ys, 0);
+#pragma unroll
+    for (int dz = -1; dz <= 1; ++dz) {
+      const int zs = e.w - dz;
+      if (zs < 0 || zs >= g.D) continue;
+      const K want = row0 + static_cast<K>(zs);
+      uint32_t slot = local_home<K>(want);
+      for (int probe = 0; probe < kLocalSlots; ++probe) {
+        const uint32_t i = s_slot[slot];
+        if (i == kInvalid) break;
+        if (s_key[i] == want) {
+          s_nbr[i * 27 + c * 3 + (dz + 1)] = row;
+          break;
+        }
+        slot = (slot + 1) & (kLocalSlots - 1);
+      }
+    }
   }
   __syncthreads();
 
   uint32_t gray = 0;
   if (t < nv) {
-    const int4 cc = s_coord[t];
-    const long long key = static_cast<long long>(g.template key<kKeyBits>(cc.x, cc.y, cc.z, cc.w));
-#pragma unroll 1
-    for (int c = 0; c < kCombos; ++c) {
-      const int dx = c / 3 - 1, dy = c % 3 - 1;
-      uint32_t res[3] = {kInvalid, kInvalid, kInvalid};
-      const int x = cc.y + dx, y = cc.z + dy;
-      const uint32_t ws = s_lo[c], len = s_hi[c] > ws ? s_hi[c] - ws : 0u;
-      if (x >= 0 && x < g.W && y >= 0 && y < g.H && len > 0) {
-        const long long mid_key = key + dx * HD + dy * static_cast<long long>(g.D);  // key of (x + dx, y + dy, z)
-        const bool in_smem = len <= kWinMax;
-        const K* win = s_win + c * kWinMax;
-        auto read = [&](uint32_t j) -> long long {
-          return in_smem ? static_cast<long long>(win[j]) : key_at<kKeyBits>(coords, ws + j, g);
-        };
-        uint32_t lo = 0, hi = len;  // first entry >= mid_key - 1
-        while (lo < hi) {
-          const uint32_t m = lo + ((hi - lo) >> 1);
-          if (read(m) < mid_key - 1) lo = m + 1;
-          else hi = m;
-        }
-        uint32_t pos = lo;
 #pragma unroll
-        for (int dz = -1; dz <= 1; ++dz) {
-          if (pos < len && read(pos) == mid_key + dz) {
-            const int z = cc.w + dz;
-            if (z >= 0 && z < g.D) res[dz + 1] = ws + pos;  // otherwise the key belongs to a voxel of another row of the grid
-            ++pos;
-          }
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < 3; ++k) {
-        s_nbr[t * 27 + c * 3 + k] = res[k];
-        if (res[k] != kInvalid) gray |= 1u << (c * 3 + k);
-      }
+    for (int k = 0; k < 27; ++k) {
+      if (s_nbr[t * 27 + k] != kInvalid) gray |= 1u << k;
     }
   }
-  // per-offset valid counts of the CTA (for the pair-list offsets)
-  for (int v = 0; v < 27; ++v) {
-    const uint32_t b = __ballot_sync(0xffffffffu, (gray >> v) & 1u);
-    if (lane == 0 && b != 0u) atomicAdd(&s_count[v], static_cast<uint32_t>(__popc(b)));
+  // per-offset valid counts of the CTA (for the pair-list offsets): lane v of each warp keeps the warp's count of offset v
+  {
+    uint32_t mine = 0;
+#pragma unroll
+    for (int v = 0; v < 27; ++v) {
+      const uint32_t b = __ballot_sync(0xffffffffu, (gray >> v) & 1u);
+      if (lane == v) mine = static_cast<uint32_t>(__popc(b));
+    }
+    if (lane < 27 && mine != 0u) atomicAdd(&s_count[lane], mine);
   }
   __syncthreads();
-  uint32_t* out = nbr + static_cast<size_t>(n0) * 27;
-  for (uint32_t item = t; item < nv * 27; item += kMapBlock) out[item] = s_nbr[item];
+  {
+    // the CTA's map rows leave as 16-byte pieces (a block starts 256 * 108 bytes after the previous one)
+    uint32_t* out = nbr + static_cast<size_t>(n0) * 27;
+    const uint32_t words = nv * 27;
+    const uint32_t vecs = (reinterpret_cast<uintptr_t>(out) & 15) == 0 ? words >> 2 : 0u;  // a map that is only 4-byte aligned goes word by word
+    for (uint32_t i = t; i < vecs; i += kMapBlock) reinterpret_cast<uint4*>(out)[i] = reinterpret_cast<const uint4*>(s_nbr)[i];
+    for (uint32_t i = vecs * 4 + t; i < words; i += kMapBlock) out[i] = s_nbr[i];
+  }
   if (t < nv) {
     uint32_t binary = gray;
     binary ^= binary >> 1;
@@ -348,12 +408,9 @@ static int build_impl(const int32_t* coords, uint32_t n, Grid3 g, Stencil st, vo
   subm_lookup_kernel<kKeyBits, false><<<nblk, kMapBlock, 0, s>>>(c4, n, g, st, table, slots, nbr, nullptr, gray, binary, block_counts,
                                                                 nblk, unsorted);
   if (try_sorted) {
-    const int smem = kMapBlock * 16 + kMapBlock * 27 * 4 + kCombos * kWinMax * (kKeyBits / 8);
-    cudaError_t e = cudaFuncSetAttribute(subm_sorted_lookup_kernel<kKeyBits>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(subm_sorted_lookup_kernel<kKeyBits>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) return cuda_status(e);
-    e = cudaFuncSetAttribute(subm_sorted_lookup_kernel<kKeyBits>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    if (e != cudaSuccess) return cuda_status(e);
-    subm_sorted_lookup_kernel<kKeyBits><<<nblk, kMapBlock, smem, s>>>(c4, n, g, nbr, gray, binary, block_counts, nblk, unsorted);
+    subm_sorted_lookup_kernel<kKeyBits><<<nblk, kMapBlock, 0, s>>>(c4, n, g, nbr, gray, binary, block_counts, nblk, unsorted);
   }
   block_scan_kernel<<<st.V, 1024, 0, s>>>(block_counts, nblk, seg);
   seg_prefix_kernel<<<1, 32, 0, s>>>(seg, st.V);

@@ -83,9 +83,10 @@ int64_t fgb_map_num_blocks(int64_t n);
  * Rows that arrive in ascending flat-index order -- lexicographic (b, x, y, z),
  * without duplicates -- need no table for the 3x3x3, dilation-1 stencil (a
  * row's position is its rank among the keys): a check kernel decides on the
- * device, without a host round trip, whether the map is built by windowed
- * binary searches in the sorted input or by the hash table; the table memory
- * is then left untouched.  The map is the same either way. */
+ * device, without a host round trip, whether the map is built from the sorted
+ * input itself (each block of rows streams the runs of rows that can hold its
+ * neighbours) or by the hash table; the table memory is then left untouched.
+ * The map is the same either way. */
 int fgb_subm_build_neighbor_map(const int32_t* coords, int64_t n,
                                 int W, int H, int D,
                                 int Kw, int Kh, int Kd,

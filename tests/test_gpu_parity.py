@@ -146,10 +146,10 @@ def test_sorted_and_hash_paths_agree(K):
     check_cache(build_cache(far, big), orc.neighbor_cache(far, big), 27)
 
 
-def test_sorted_path_windows_longer_than_shared_memory(K):
+def test_sorted_path_runs_much_longer_than_a_block(K):
     """A sparse plane between two dense ones: the 256 voxels of a block span the
-    whole sparse plane, so the window of the next plane holds thousands of keys
-    and is searched in global memory."""
+    whole sparse plane, so the run of rows of the next plane that can hold their
+    neighbours is thousands of rows long (and most of those rows find nothing)."""
     g = np.arange(64)
     yy, zz = np.meshgrid(g, g, indexing="ij")
     dense = np.stack([yy.ravel(), zz.ravel()], axis=1)
