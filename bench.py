@@ -23,6 +23,9 @@ shells at RES=1024, C=64, fp16, whole samples dealt to the ranks, strong
 scaling); its line carries the metric, the per-rank balance and the clocks only.
 --workload res1024_map [--unsorted] times the neighbour-cache build alone on two
 shells at RES=1024 and reports its algorithmic GB/s against the HBM peak.
+--workload residual_stack [--fused] times a stack of 8 residual blocks (16 convs,
+C=512, bf16) forward + backward, with the elementwise work between the convs as
+torch kernels or in the conv kernels' epilogue.
 """
 import argparse
 import json
@@ -551,6 +554,71 @@ def run_map_build(args):
         "gpu_launches": launches, "clocks": clocks}), flush=True)
 
 
+def run_residual_stack(args):
+    """Residual stack: 8 blocks [conv, SiLU, conv] + skip on 4 shells at RES=64,
+    C=512, bf16, one shared neighbour cache, forward + backward of the mean.
+    ``--fused``: SiLU and the skip addition run in the conv kernels' epilogue
+    (``sparse_submanifold_conv3d_fused``) instead of torch elementwise kernels."""
+    from flexgemm_b200 import workloads
+    from flexgemm_b200.kernels import cuda as K
+    from flexgemm_b200.ops import spconv
+    from flexgemm_b200.ops.spconv import SubMConv3dFunction as F
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    spconv.set_algorithm(spconv.Algorithm.MASKED_IMPLICIT_GEMM_SPLITK)
+    B, res, C, blocks = 4, 64, 512, 8
+    dt = torch.bfloat16
+    coords = torch.from_numpy(workloads.shell_coords(res, B, [1.0] * B)).to(dev)
+    shape = torch.Size((B, C, res, res, res))
+    g = torch.Generator().manual_seed(5)
+    x0 = torch.randn(coords.shape[0], C, generator=g).to(dt).to(dev)
+    ws = [(torch.randn(C, 3, 3, 3, C, generator=g) / (27 * C) ** 0.5).to(dt).to(dev).requires_grad_(True) for _ in range(2 * blocks)]
+    bs = [torch.zeros(C, dtype=dt, device=dev).requires_grad_(True) for _ in range(2 * blocks)]
+    cache = F._compute_neighbor_cache(coords, shape, (3, 3, 3), (1, 1, 1), True)
+    pairs = int(cache["valid_signal_i"].shape[0])
+
+    def step():
+        h = x0.detach().requires_grad_(True)
+        for i in range(blocks):
+            if args.fused:
+                y, _ = spconv.sparse_submanifold_conv3d_fused(h, coords, shape, ws[2 * i], bs[2 * i], neighbor_cache=cache, activation="silu")
+                h, _ = spconv.sparse_submanifold_conv3d_fused(y, coords, shape, ws[2 * i + 1], bs[2 * i + 1], neighbor_cache=cache, residual=h)
+            else:
+                y, _ = spconv.sparse_submanifold_conv3d(h, coords, shape, ws[2 * i], bs[2 * i], neighbor_cache=cache)
+                y = torch.nn.functional.silu(y)
+                y, _ = spconv.sparse_submanifold_conv3d(y, coords, shape, ws[2 * i + 1], bs[2 * i + 1], neighbor_cache=cache)
+                h = h + y
+        h.float().mean().backward()
+        for t in ws + bs:
+            t.grad = None
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    K.check_status(dev)
+    launches0 = K.launch_count
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    ms = time_loop(step, args.steps)
+    launches = K.launch_count - launches0
+    clocks = sampler.stop()
+    K.check_status(dev)
+    flops = 2 * blocks * 6.0 * pairs * C * C
+    tf = flops / (ms * 1e-3) / 1e12
+    peak = float(peaks["bf16_tflops"])
+    print(json.dumps({
+        "metric": "residual stack fwd+bwd useful TFLOP/s (16 submconvs, C=512 bf16, 4 x RES=64)", "value": tf, "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"8 x ([conv, SiLU, conv] + skip), N={coords.shape[0]} voxels, L={pairs} pairs per conv, shared cache; "
+                               f"elementwise work {'in the conv epilogues' if args.fused else 'as torch kernels'}",
+                   "l2": "activations of one layer (41 MB) fit the 126 MB L2; no flush: the stack streams 16 layers of them"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                     "algorithmic_flops_per_step": flops, "peak_source": peaks["source"]},
+        "gpu_launches": launches, "clocks": clocks}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -558,10 +626,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="res256", choices=["res256", "res1024_batch8", "res1024_map"],
+    ap.add_argument("--workload", default="res256", choices=["res256", "res1024_batch8", "res1024_map", "residual_stack"],
                     help="res256: the headline single-sample workload (default); res1024_batch8: the sharded high-resolution "
-                         "batch; res1024_map: the neighbour-cache build alone at a size where HBM matters")
+                         "batch; res1024_map: the neighbour-cache build alone at a size where HBM matters; residual_stack: 16 convs "
+                         "with SiLU and skip additions between them")
     ap.add_argument("--unsorted", action="store_true", help="res1024_map: shuffle the rows (hash-table path)")
+    ap.add_argument("--fused", action="store_true", help="residual_stack: SiLU and skip additions in the conv epilogues")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -569,6 +639,8 @@ def main():
         run_sharded_batch(args)
     elif args.workload == "res1024_map":
         run_map_build(args)
+    elif args.workload == "residual_stack":
+        run_residual_stack(args)
     else:
         run_gpu_arm(args)
 

@@ -84,6 +84,14 @@ struct IgemmParams {
   int32_t* status;
 };
 
+// what the fused epilogue adds (a kernel parameter of its own: the plain kernel's parameter block, and with it its
+// register allocation, stays as tuned)
+struct FusedEpilogue {
+  const char* residual;      // fused epilogue: [n, nout] added after the activation, or null
+  char* preact;              // fused epilogue: [n, nout] copy of the result before the activation, or null
+  int act;                   // fused epilogue: FGB_ACT_NONE / FGB_ACT_SILU
+};
+
 struct IgemmSmem {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
@@ -139,9 +147,48 @@ __device__ __forceinline__ void stage_row_chunk(uint8_t* stage, int lane, int ch
   }
 }
 
+// Fused epilogue on one 16-byte piece of an output row (8 values of a 16-bit type, 4 of fp32), already rounded to the
+// output type: optionally keeps a copy (what a backward pass of the activation needs), applies the activation in
+// fp32, adds the residual piece, rounds again -- the roundings of the unfused sequence conv -> activation -> add.
 template <int kDtype>
+__device__ __forceinline__ uint4 fuse_piece(uint4 val, int act, const char* residual, char* preact, size_t byte_off) {
+  if (preact != nullptr) *reinterpret_cast<uint4*>(preact + byte_off) = val;
+  uint4 res = make_uint4(0, 0, 0, 0);
+  if (residual != nullptr) res = __ldg(reinterpret_cast<const uint4*>(residual + byte_off));
+  auto f = [&](float x, float r) {
+    if (act == FGB_ACT_SILU) x = x / (1.f + __expf(-x));
+    return x + r;
+  };
+  uint4 o;
+  if constexpr (kDtype == FGB_F16 || kDtype == FGB_BF16) {
+    using T = typename std::conditional<kDtype == FGB_F16, __half, __nv_bfloat16>::type;
+    const T* vt = reinterpret_cast<const T*>(&val);
+    const T* rt = reinterpret_cast<const T*>(&res);
+    T* ot = reinterpret_cast<T*>(&o);
+    const bool two_roundings = act != FGB_ACT_NONE && residual != nullptr;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float x = static_cast<float>(vt[i]);
+      if (two_roundings) {  // activation output rounded to the type before the add, as a separate activation kernel would
+        x = static_cast<float>(static_cast<T>(f(x, 0.f)));
+        ot[i] = static_cast<T>(x + static_cast<float>(rt[i]));
+      } else {
+        ot[i] = static_cast<T>(f(x, residual != nullptr ? static_cast<float>(rt[i]) : 0.f));
+      }
+    }
+  } else {
+    const float* vt = reinterpret_cast<const float*>(&val);
+    const float* rt = reinterpret_cast<const float*>(&res);
+    float* ot = reinterpret_cast<float*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ot[i] = f(vt[i], residual != nullptr ? rt[i] : 0.f);
+  }
+  return o;
+}
+
+template <int kDtype, bool kFused>
 __global__ void __launch_bounds__(kIgemmThreads, 1)
-    subm_igemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const IgemmParams p) {
+    subm_igemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const IgemmParams p, const FusedEpilogue fe) {
   constexpr bool kTF32 = (kDtype == FGB_F32_TF32);
   constexpr int kElem = (kDtype == FGB_F16 || kDtype == FGB_BF16) ? 2 : 4;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -446,8 +493,15 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
               const uint32_t orow = __shfl_sync(0xffffffffu, sr[h], row);
               const int col = n0 + c0 + piece * (16 / kElem);
               const uint4 val = *reinterpret_cast<const uint4*>(stage_out + row * 128 + ((piece ^ (row & 7)) << 4));
-              if (orow != kInvalid && col < p.nout)
-                *reinterpret_cast<uint4*>(p.out + (size_t(orow) * p.nout + col) * kElem) = val;
+              if constexpr (kFused) {
+                if (orow != kInvalid && col < p.nout) {
+                  const size_t byte_off = (size_t(orow) * p.nout + col) * kElem;
+                  *reinterpret_cast<uint4*>(p.out + byte_off) = fuse_piece<kDtype>(val, fe.act, fe.residual, fe.preact, byte_off);
+                }
+              } else {
+                if (orow != kInvalid && col < p.nout)
+                  *reinterpret_cast<uint4*>(p.out + (size_t(orow) * p.nout + col) * kElem) = val;
+              }
             }
           }
           __syncwarp();
@@ -565,25 +619,32 @@ static int sm_count() {
   return sms;
 }
 
-template <int kDtype>
-static int launch_igemm(const CUtensorMap& tmap, const IgemmParams& p, cudaStream_t s) {
+template <int kDtype, bool kFused>
+static int launch_igemm_variant(const CUtensorMap& tmap, const IgemmParams& p, const FusedEpilogue& fe, cudaStream_t s) {
   const size_t smem = 1024 + kCtrlBytes + size_t(p.stages) * (2 * kATileBytes + p.bn * 128) + kStoreStageBytes;
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(subm_igemm_kernel<kDtype>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    cudaError_t e = cudaFuncSetAttribute(subm_igemm_kernel<kDtype, kFused>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return cuda_status(e);
     configured = smem;
   }
   const int64_t work = int64_t(p.num_blocks) * p.n_tiles_n;
   const unsigned grid = static_cast<unsigned>(work < sm_count() ? work : sm_count());
-  subm_igemm_kernel<kDtype><<<grid, kIgemmThreads, smem, s>>>(tmap, p);
+  subm_igemm_kernel<kDtype, kFused><<<grid, kIgemmThreads, smem, s>>>(tmap, p, fe);
   return launch_status();
+}
+
+// the plain kernel carries no trace of the fused epilogue (its register allocation is the tuned one)
+template <int kDtype>
+static int launch_igemm(const CUtensorMap& tmap, const IgemmParams& p, const FusedEpilogue& fe, cudaStream_t s) {
+  if (fe.act != FGB_ACT_NONE || fe.residual != nullptr || fe.preact != nullptr) return launch_igemm_variant<kDtype, true>(tmap, p, fe, s);
+  return launch_igemm_variant<kDtype, false>(tmap, p, fe, s);
 }
 
 // x [n, kc] gathered through nbr; w [nout, V, kc]; out [n, nout]
 int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nbr, const int64_t* sorted_idx,
               const uint32_t* tile_masks, const uint32_t* block_order, uint32_t* ticket, void* out, int64_t n, int kc, int nout, int V, int dtype, int flip, int32_t* status,
-              cudaStream_t s) {
+              cudaStream_t s, int act = FGB_ACT_NONE, const void* residual = nullptr, void* preact = nullptr) {
   const int eb = elem_bytes(dtype);
   if (eb == 0 || dtype == FGB_F32_IEEE) return FGB_E_DTYPE;  // callers expand fp32-accurate mode to TF32 operands
   if (n < 0 || n >= (int64_t(1) << 32) - 1 || kc <= 0 || nout <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
@@ -591,8 +652,13 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   if (!x || !w || !nbr || !sorted_idx || !tile_masks || !out) return FGB_E_NULL;
   if ((kc * eb) % 16 || (nout * eb) % 16) return FGB_E_ALIGN;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out) |
-       reinterpret_cast<uintptr_t>(bias)) & 15)
+       reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(preact)) & 15)
     return FGB_E_ALIGN;
+  if (act != FGB_ACT_NONE && act != FGB_ACT_SILU) return FGB_E_SIZE;
+  FusedEpilogue fe;
+  fe.residual = static_cast<const char*>(residual);
+  fe.preact = static_cast<char*>(preact);
+  fe.act = act;
   IgemmParams p;
   p.x = static_cast<const char*>(x);
   p.bias = bias;
@@ -628,11 +694,11 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   if (rc != FGB_OK) return rc;
   switch (dtype) {
     case FGB_F16:
-      return launch_igemm<FGB_F16>(tmap, p, s);
+      return launch_igemm<FGB_F16>(tmap, p, fe, s);
     case FGB_BF16:
-      return launch_igemm<FGB_BF16>(tmap, p, s);
+      return launch_igemm<FGB_BF16>(tmap, p, fe, s);
     default:
-      return launch_igemm<FGB_F32_TF32>(tmap, p, s);
+      return launch_igemm<FGB_F32_TF32>(tmap, p, fe, s);
   }
 }
 
@@ -659,7 +725,8 @@ namespace fgb {
 // n rows of the map / of `out`; n_src rows of `feats` (equal for a submanifold conv)
 static int fprop_impl(const void* feats, const void* weight, const void* bias, const uint32_t* neighbor_map, const int64_t* sorted_idx,
                       const uint32_t* tile_masks, const uint32_t* block_order, void* out, int64_t n, int64_t n_src, int Ci, int Co, int V,
-                      int dtype, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+                      int dtype, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream, int act = FGB_ACT_NONE,
+                      const void* residual = nullptr, void* preact = nullptr) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (n < 0 || n_src < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
   if (n == 0) return FGB_OK;
@@ -669,7 +736,8 @@ static int fprop_impl(const void* feats, const void* weight, const void* bias, c
   uint32_t* ticket = static_cast<uint32_t*>(workspace);
   char* scratch = static_cast<char*>(workspace) + kWsHeader;
   if (dtype != FGB_F32_IEEE)
-    return run_igemm(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, ticket, out, n, Ci, Co, V, dtype, 0, status, s);
+    return run_igemm(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, ticket, out, n, Ci, Co, V, dtype, 0, status, s, act,
+                     residual, preact);
   // fp32-accurate: one TF32 run over the tripled channel dimension
   if (!feats || !weight) return FGB_E_NULL;
   const int64_t x_bytes = align256(n_src * 3 * Ci * 4), w_bytes = align256(int64_t(Co) * V * 3 * Ci * 4);
@@ -681,7 +749,8 @@ static int fprop_impl(const void* feats, const void* weight, const void* bias, c
   if (rc != FGB_OK) return rc;
   rc = launch_split3(static_cast<const float*>(weight), w3, int64_t(Co) * V, Ci, kSplitWeights, s);
   if (rc != FGB_OK) return rc;
-  return run_igemm(x3, w3, bias, neighbor_map, sorted_idx, tile_masks, block_order, ticket, out, n, 3 * Ci, Co, V, FGB_F32_TF32, 0, status, s);
+  return run_igemm(x3, w3, bias, neighbor_map, sorted_idx, tile_masks, block_order, ticket, out, n, 3 * Ci, Co, V, FGB_F32_TF32, 0, status, s, act,
+                   residual, preact);
 }
 
 }  // namespace fgb
@@ -700,6 +769,16 @@ extern "C" int fgb_sparse_conv_fprop(const void* feats, const void* weight, cons
                                      int64_t workspace_bytes, int32_t* status, void* stream) {
   return fgb::fprop_impl(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, out, n_out, n_in, Ci, Co, V, dtype,
                          workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int fgb_subm_conv_fprop_fused(const void* feats, const void* weight, const void* bias, const void* residual,
+                                         const uint32_t* neighbor_map, const int64_t* sorted_idx, const uint32_t* tile_masks,
+                                         const uint32_t* block_order, void* out, void* preact_out, int64_t n, int Ci, int Co, int V,
+                                         int dtype, int activation, void* workspace, int64_t workspace_bytes, int32_t* status,
+                                         void* stream) {
+  if (activation != FGB_ACT_NONE && activation != FGB_ACT_SILU) return FGB_E_SIZE;
+  return fgb::fprop_impl(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, out, n, n, Ci, Co, V, dtype, workspace,
+                         workspace_bytes, status, stream, activation, residual, preact_out);
 }
 
 namespace fgb {

@@ -351,6 +351,37 @@ def conv_fprop(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks, order=N
     return out
 
 
+ACTIVATIONS = {None: 0, "none": 0, "silu": 1}  # FGB_ACT_*
+
+
+def conv_fprop_fused(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks, order=None, activation=None, residual=None,
+                     keep_preact: bool = False):
+    """Submanifold fprop with ``activation`` (None or "silu") and ``+ residual``
+    [N,Co] done in the kernel's epilogue.  Returns (out, preact): preact is the
+    conv result before the activation when ``keep_preact`` (else None)."""
+    if activation not in ACTIVATIONS:
+        raise ValueError(f"Unsupported activation {activation!r}")
+    lib = _cabi.lib()
+    dev = feats.device
+    n, Ci = feats.shape
+    assert neighbor_map.shape[0] == n, "the fused epilogue serves the submanifold conv (one output row per input row)"
+    Co, V, _ = weight_cvc.shape
+    if residual is not None:
+        assert residual.shape == (n, Co) and residual.dtype == feats.dtype and residual.is_contiguous(), "residual must be [N, Co], contiguous, of the feature dtype"
+    code = dtype_code(feats.dtype)
+    out = torch.empty((n, Co), dtype=feats.dtype, device=dev)
+    preact = torch.empty_like(out) if keep_preact else None
+    nbytes = _cabi.check_size(lib.fgb_sparse_conv_workspace_bytes(0, n, n, Ci, Co, V, code, 1), "fgb_sparse_conv_workspace_bytes")
+    ws = workspace(dev, "fprop", nbytes)
+    rc = lib.fgb_subm_conv_fprop_fused(_ptr(feats), weight_cvc.data_ptr(), _ptr(bias), _ptr(residual), _ptr(neighbor_map),
+                                       _ptr(sorted_idx), _ptr(masks), _ptr(order), _ptr(out), _ptr(preact), n, Ci, Co, V, code,
+                                       ACTIVATIONS[activation], ws.data_ptr(), ws.numel() * 8, status_word(dev).data_ptr(),
+                                       _stream(dev))
+    _cabi.check(rc, "fgb_subm_conv_fprop_fused")
+    _count(1)
+    return out, preact
+
+
 def conv_dgrad(grad_out, weight_cvc, neighbor_map, sorted_idx, masks, order=None, mirror: bool = True) -> torch.Tensor:
     """grad_out [N_out,Co], weight_cvc [Co,V,Ci] -> grad_feats [N_in,Ci].
 

@@ -56,3 +56,4 @@ def set_hashmap_ratio(ratio: float):
 
 from .submanifold_conv3d import SubMConv3dFunction, SubMConv3dNeighborCache, sparse_submanifold_conv3d  # noqa: E402,F401
 from .sparse_conv3d import SparseConv3dFunction, SparseConv3dNeighborCache, sparse_conv3d  # noqa: E402,F401
+from .fused_conv3d import SubMConv3dFusedFunction, sparse_submanifold_conv3d_fused  # noqa: E402,F401

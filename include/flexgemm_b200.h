@@ -46,6 +46,10 @@ extern "C" {
 #define FGB_F32_TF32 2  /* fp32 storage, TF32 tensor-core math (allow_tf32 = True)  */
 #define FGB_F32_IEEE 3  /* fp32 storage, fp32-accurate math   (allow_tf32 = False) */
 
+/* activation of the fused forward epilogue */
+#define FGB_ACT_NONE 0
+#define FGB_ACT_SILU 1  /* x * sigmoid(x) */
+
 const char* fgb_version(void);
 const char* fgb_error_string(int code);
 
@@ -173,6 +177,27 @@ int fgb_subm_conv_fprop(const void* feats, const void* weight, const void* bias,
                         void* out, int64_t n, int Ci, int Co, int V, int dtype,
                         void* workspace, int64_t workspace_bytes,
                         int32_t* status, void* stream);
+
+/* fgb_subm_conv_fprop with the elementwise work that follows a conv in a residual
+ * block done in its epilogue:
+ *   y = conv(feats) + bias                 rounded to `dtype`
+ *   preact_out[r, :] = y                   when preact_out is not null (what the
+ *                                          backward of the activation needs)
+ *   out[r, :] = activation(y) + residual[r, :]
+ * activation: FGB_ACT_NONE or FGB_ACT_SILU, computed in fp32; residual [n, Co] of
+ * `dtype`, 16-byte aligned, or null.  With an activation and a residual the
+ * activation's result is rounded to `dtype` before the add, so the result has
+ * the roundings of the unfused sequence conv -> activation -> add.  The
+ * reference has no such call: its callers run torch elementwise kernels between
+ * convs (the residual stack [conv, SiLU, conv] + skip). */
+int fgb_subm_conv_fprop_fused(const void* feats, const void* weight, const void* bias,
+                              const void* residual,
+                              const uint32_t* neighbor_map, const int64_t* sorted_idx,
+                              const uint32_t* tile_masks, const uint32_t* block_order,
+                              void* out, void* preact_out,
+                              int64_t n, int Ci, int Co, int V, int dtype, int activation,
+                              void* workspace, int64_t workspace_bytes,
+                              int32_t* status, void* stream);
 
 /* grad_feats[r, :] = sum_v grad_out[neighbor_map[r, v], :] * weight[:, V-1-v, :]
  * grad_out [n, Co], weight [Co, V, Ci], grad_feats [n, Ci].  The workspace

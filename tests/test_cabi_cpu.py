@@ -90,6 +90,15 @@ def test_sparse_conv_entry_points_validate_without_launch(lib):
     assert lib.fgb_sparse_conv_wgrad(16, 16, 16, 16, 16, 16, 0, 10, 20, 500, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -2  # pairs > n_out*V
 
 
+def test_fused_fprop_validates_without_launch(lib):
+    args = lambda act, n=10, ci=64, res=16, pre=16: (16, 16, 0, res, 16, 16, 16, 0, 16, pre, n, ci, 64, 27, _cabi.F16, act, 256, 256, 0, 0)
+    assert lib.fgb_subm_conv_fprop_fused(*args(2)) == -2            # unknown activation
+    assert lib.fgb_subm_conv_fprop_fused(*args(1, ci=60)) == -4     # Ci % 8
+    assert lib.fgb_subm_conv_fprop_fused(*args(1, res=8)) == -4     # residual not 16-byte aligned
+    assert lib.fgb_subm_conv_fprop_fused(*args(1, n=0)) == 0        # nothing to do
+    assert hasattr(spconv, "sparse_submanifold_conv3d_fused") and hasattr(spconv, "SubMConv3dFusedFunction")
+
+
 def test_python_surface_matches_reference_names():
     for name in ("Algorithm", "ALGORITHM", "HASHMAP_RATIO", "set_algorithm", "set_hashmap_ratio", "SubMConv3dFunction",
                  "SubMConv3dNeighborCache", "sparse_submanifold_conv3d", "SparseConv3dFunction", "SparseConv3dNeighborCache",

@@ -110,3 +110,24 @@ def test_empty_input():
     assert gray.shape == (0,)
     vs_i, vs_o, seg = orc.valid_signal(nbr)
     assert vs_i.shape == (0,) and np.array_equal(seg, np.zeros(28, np.uint32))
+
+
+def test_residual_block_epilogue_is_the_torch_sequence():
+    """The oracle's epilogue equals what a caller of the reference runs between
+    convs with torch kernels, rounding included (SiLU to one unit in the last place); its SiLU derivative equals autograd's."""
+    g = torch.Generator().manual_seed(0)
+    y32 = torch.randn(257, 40, generator=g) * 3
+    res32 = torch.randn(257, 40, generator=g)
+    for dt in (torch.float16, torch.bfloat16, torch.float32):
+        y, res = y32.to(dt), res32.to(dt)
+        want = torch.nn.functional.silu(y) + res
+        got = orc.residual_block_epilogue(y.float(), "silu", res.float(), dt).to(dt)
+        # torch's silu may round its fp32 intermediate differently: one unit in the last place of the type at most
+        assert torch.allclose(got.double(), want.double(), rtol=2 * torch.finfo(dt).eps, atol=1e-6), dt
+        assert torch.equal(orc.residual_block_epilogue(y.float(), None, res.float(), dt).to(dt), y + res)
+    yd = y32.double().requires_grad_(True)
+    gout = res32.double()
+    torch.nn.functional.silu(yd).backward(gout)
+    assert torch.allclose(orc.silu_backward(y32.double(), gout), yd.grad, rtol=1e-12, atol=1e-12)
+    with pytest.raises(ValueError):
+        orc.residual_block_epilogue(y32, "gelu")
