@@ -34,7 +34,11 @@ import statistics
 import sys
 import time
 
-import torch
+# NCCL writes its version / debug lines to stdout when NCCL_DEBUG is set in the environment; stdout carries the one
+# JSON line, so those lines go to stderr instead
+os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+
+import torch  # noqa: E402
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
