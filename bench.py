@@ -34,11 +34,18 @@ import statistics
 import sys
 import time
 
-# NCCL writes its version / debug lines to stdout when NCCL_DEBUG is set in the environment; stdout carries the one
-# JSON line, so those lines go to stderr instead
-os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+# stdout carries the one JSON line and nothing else: libraries that write there from native code (NCCL prints its
+# version line on the first communicator) get stderr instead, and the line goes out through a copy of the real stdout
+_JSON_OUT = os.fdopen(os.dup(1), "w")
+os.dup2(2, 1)
 
 import torch  # noqa: E402
+
+
+def emit(line: dict) -> None:
+    _JSON_OUT.write(json.dumps(line) + "\n")
+    _JSON_OUT.flush()
+
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
@@ -187,7 +194,7 @@ def run_reference_arm(args):
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -399,7 +406,7 @@ def run_gpu_arm(args):
                 "ms_per_step": t.item(), "includes": "per step: H2D of coords+feats from pinned memory on a copy stream (the next step's copies are queued while the current step computes), neighbour-map build, fwd, bwd, D2H of loss and grad_weight"},
         "gpu_launches": launches, "clocks": clocks,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -500,7 +507,7 @@ def run_sharded_batch(args):
                        "max_rank_voxels": int(mx[2].item()), "load_balance_bound": total_n / max(mx[2].item(), 1.0)},
             "map_build_ms": mx[1].item(), "gpu_launches": launches, "clocks": clocks,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -546,7 +553,7 @@ def run_map_build(args):
              (4 * V * n + 4 * n + 8 * n + 8 * pairs)
     gbs = nbytes / (ms * 1e-3) / 1e9
     peak = float(peaks["hbm_gbs"])
-    print(json.dumps({
+    emit({
         "metric": "neighbor-cache build, algorithmic GB/s (2 shells at RES=1024)", "value": gbs, "unit": "GB/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u32", "data": "synthetic",
@@ -555,7 +562,7 @@ def run_map_build(args):
                    "l2": "working set (coords, table, map, lists: ~1.5 GB) far exceeds the 126 MB L2; no flush"},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
                      "algorithmic_bytes": nbytes, "peak_source": peaks["source"]},
-        "gpu_launches": launches, "clocks": clocks}), flush=True)
+        "gpu_launches": launches, "clocks": clocks})
 
 
 def run_residual_stack(args):
@@ -611,7 +618,7 @@ def run_residual_stack(args):
     flops = 2 * blocks * 6.0 * pairs * C * C
     tf = flops / (ms * 1e-3) / 1e12
     peak = float(peaks["bf16_tflops"])
-    print(json.dumps({
+    emit({
         "metric": "residual stack fwd+bwd useful TFLOP/s (16 submconvs, C=512 bf16, 4 x RES=64)", "value": tf, "unit": "TFLOP/s",
         "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -620,7 +627,7 @@ def run_residual_stack(args):
                    "l2": "activations of one layer (41 MB) fit the 126 MB L2; no flush: the stack streams 16 layers of them"},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
                      "algorithmic_flops_per_step": flops, "peak_source": peaks["source"]},
-        "gpu_launches": launches, "clocks": clocks}), flush=True)
+        "gpu_launches": launches, "clocks": clocks})
 
 
 def main():
