@@ -257,25 +257,35 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
     }
   } else {
     // -------------------------------------------------------------- epilogue
+    // Thread `lane` of warp w holds accumulator row 32 w + lane.  32 columns at a time go through a 4 KB staging
+    // buffer per warp (the pipeline's first stage: once the accumulator is complete every stage has been consumed
+    // and nothing is in flight), 16-byte pieces XOR-swizzled by the row, and come back so that eight consecutive
+    // lanes hold one row's 128 contiguous bytes: every store instruction then writes four whole lines of the slab
+    // instead of one 16-byte piece in each of 32 lines.
     const uint32_t slab = wg_slab_of(p.seg, p.kb, p.unit_kb, v, unit_j);
     mbar_wait(&ctl->acc_full, 0, abort_flag);
     tc_fence_after_sync();
+    uint8_t* stage_out = stages + warp * 4096;
     for (int mt = 0; mt < p.mt; ++mt) {
-      const int co = co0 + mt * 128 + warp * 32 + lane;
-      float* orow = p.partial + (size_t(slab) * p.Co + co) * p.Ci;
+      const int co_base = co0 + mt * 128 + warp * 32;
+      float* obase = p.partial + (size_t(slab) * p.Co + co_base) * p.Ci;
       for (int c0 = 0; c0 < p.bn; c0 += 32) {
         uint32_t acc[32];
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + mt * p.bn + c0, acc);
         tmem_ld_wait();
-        if (co < p.Co) {
 #pragma unroll
-          for (int g4 = 0; g4 < 8; ++g4) {
-            const int ci = ci0 + c0 + g4 * 4;
-            if (ci < p.Ci)
-              *reinterpret_cast<float4*>(orow + ci) = make_float4(__uint_as_float(acc[g4 * 4]), __uint_as_float(acc[g4 * 4 + 1]),
-                                                                  __uint_as_float(acc[g4 * 4 + 2]), __uint_as_float(acc[g4 * 4 + 3]));
-          }
+        for (int g4 = 0; g4 < 8; ++g4)
+          *reinterpret_cast<uint4*>(stage_out + lane * 128 + ((g4 ^ (lane & 7)) << 4)) =
+              make_uint4(acc[g4 * 4], acc[g4 * 4 + 1], acc[g4 * 4 + 2], acc[g4 * 4 + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = i * 4 + (lane >> 3), piece = lane & 7;
+          const int ci = ci0 + c0 + piece * 4;
+          const uint4 val = *reinterpret_cast<const uint4*>(stage_out + row * 128 + ((piece ^ (row & 7)) << 4));
+          if (co_base + row < p.Co && ci < p.Ci) *reinterpret_cast<uint4*>(obase + size_t(row) * p.Ci + ci) = val;
         }
+        __syncwarp();
       }
     }
   }
