@@ -43,7 +43,7 @@ struct WgradParams {
   const uint32_t* seg;  // [V + 1]
   float* partial;       // [units, Co, Ci] slabs
   int Co, Ci, V;
-  int unit_kb;    // k-blocks (stages of pairs) per unit
+  int target_units;  // the kernel cuts the pair lists into at most this many units (see wg_plan_unit_kb)
   int mt;         // 128-row accumulator blocks per CTA (1 or 2)
   int bn;         // input channels per CTA
   int co_groups;  // ceil(Co / (mt * 128))
@@ -65,8 +65,28 @@ struct WgradSmem {
   uint32_t tmem_base;
   uint32_t abort_flag;
   int unit_v, unit_j;  // the unit this CTA works on (offset, chunk index), -1 if none
+  int unit_kb;         // k-blocks per unit, planned from the segment table
 };
 static_assert(sizeof(WgradSmem) <= 1024, "control block too large");
+
+// k-blocks per unit: the smallest length for which the offsets' pair lists (nk_v k-blocks each) make at most `target`
+// units, sum_v ceil(nk_v / unit_kb) <= target.  The host knows only the total pair count; planning from the segment
+// table itself lets the grid be exactly the number of CTAs that run together (one wave, or a whole number of waves)
+// instead of a worst-case bound whose overshoot would run as a short extra wave.  Called by all 32 lanes of a warp
+// (lane v looks at offset v); every CTA and the reduction compute the same value from the same table.
+__device__ __forceinline__ uint32_t wg_plan_unit_kb(const uint32_t* seg, int V, int kb, uint32_t target, int lane) {
+  uint32_t nk = 0;
+  if (lane < V) nk = (__ldg(&seg[lane + 1]) - __ldg(&seg[lane]) + kb - 1) / kb;
+  uint32_t lo = 1, hi = __reduce_max_sync(0xffffffffu, nk);
+  if (hi < 1u) hi = 1u;
+  while (lo < hi) {  // sum of ceilings does not increase with the unit length; at hi every non-empty offset is one unit
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    const uint32_t units = __reduce_add_sync(0xffffffffu, (nk + mid - 1) / mid);
+    if (units <= target) hi = mid;
+    else lo = mid + 1;
+  }
+  return lo;
+}
 
 // Units: offset v is cut into ceil(nk_v / unit_kb) chunks of unit_kb k-blocks
 // (nk_v = k-blocks of the offset's pair list).  Unit ids enumerate (v, chunk)
@@ -135,14 +155,17 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
   bid /= p.ci_tiles;
   const int co_group = bid % p.co_groups;
   bid /= p.co_groups;
-  if (tid == 0) {
-    int v = -1, j = -1;
-    const bool skip = p.status != nullptr && *reinterpret_cast<volatile const int32_t*>(p.status) != 0;
-    if (skip || !wg_find_unit(p.seg, p.V, p.kb, p.unit_kb, p.order, bid, &v, &j)) v = j = -1;
-    ctl->unit_v = v, ctl->unit_j = j;
+  if (warp == 0) {
+    const uint32_t ukb = wg_plan_unit_kb(p.seg, p.V, p.kb, static_cast<uint32_t>(p.target_units), lane);
+    if (lane == 0) {
+      int v = -1, j = -1;
+      const bool skip = p.status != nullptr && *reinterpret_cast<volatile const int32_t*>(p.status) != 0;
+      if (skip || !wg_find_unit(p.seg, p.V, p.kb, static_cast<int>(ukb), p.order, bid, &v, &j)) v = j = -1;
+      ctl->unit_v = v, ctl->unit_j = j, ctl->unit_kb = static_cast<int>(ukb);
+    }
   }
   __syncthreads();
-  const int v = ctl->unit_v, unit_j = ctl->unit_j;
+  const int v = ctl->unit_v, unit_j = ctl->unit_j, unit_kb = ctl->unit_kb;
   if (v < 0) return;  // grid is sized for the worst case; also the no-op path after a soft error
   const int co0 = co_group * p.mt * 128;
   const int ci0 = ci_tile * p.bn;
@@ -150,8 +173,8 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
   const uint32_t seg_begin = __ldg(&p.seg[v]);
   const uint32_t seg_end = __ldg(&p.seg[v + 1]);
   const uint32_t num_k = (seg_end - seg_begin + p.kb - 1) / p.kb;
-  const uint32_t k_begin = static_cast<uint32_t>(unit_j) * p.unit_kb;
-  const uint32_t k_end = min(num_k, k_begin + p.unit_kb);
+  const uint32_t k_begin = static_cast<uint32_t>(unit_j) * unit_kb;
+  const uint32_t k_end = min(num_k, k_begin + unit_kb);
   const int total = static_cast<int>(k_end - k_begin);  // >= 1 by construction
   volatile uint32_t* abort_flag = &ctl->abort_flag;
 
@@ -262,7 +285,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
     // and nothing is in flight), 16-byte pieces XOR-swizzled by the row, and come back so that eight consecutive
     // lanes hold one row's 128 contiguous bytes: every store instruction then writes four whole lines of the slab
     // instead of one 16-byte piece in each of 32 lines.
-    const uint32_t slab = wg_slab_of(p.seg, p.kb, p.unit_kb, v, unit_j);
+    const uint32_t slab = wg_slab_of(p.seg, p.kb, unit_kb, v, unit_j);
     mbar_wait(&ctl->acc_full, 0, abort_flag);
     tc_fence_after_sync();
     uint8_t* stage_out = stages + warp * 4096;
@@ -302,8 +325,15 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
 // out[co, v, ci] = sum over the slabs of offset v, in slab order; written as dtype and/or fp32
 template <typename T>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, const uint32_t* __restrict__ seg, int kb,
-                                                            int unit_kb, int Co, int V, int Ci, T* __restrict__ out,
+                                                            int target_units, int Co, int V, int Ci, T* __restrict__ out,
                                                             float* __restrict__ out_f32, int accumulate) {
+  __shared__ int s_unit_kb;
+  if (threadIdx.x < 32) {
+    const uint32_t ukb = wg_plan_unit_kb(seg, V, kb, static_cast<uint32_t>(target_units), threadIdx.x);
+    if (threadIdx.x == 0) s_unit_kb = static_cast<int>(ukb);
+  }
+  __syncthreads();
+  const int unit_kb = s_unit_kb;
   const int v = blockIdx.y;
   const int64_t e = (blockIdx.x * int64_t(256) + threadIdx.x) * 4;  // element of the [Co, Ci] slab
   if (e >= int64_t(Co) * Ci) return;
@@ -435,13 +465,22 @@ static WgradPlan plan_wgrad(int Ci, int Co, int eb) {
   return w;
 }
 
-// k-blocks per unit and the worst-case unit count for `splitk` parts per offset on average
-static void unit_plan(int64_t n_pairs, int V, int kb, int splitk, int* unit_kb, int64_t* max_units) {
-  const int64_t nk_total = ceil_div(n_pairs, kb) + V;  // every offset rounds up
-  int64_t ukb = ceil_div(nk_total, int64_t(splitk) * V);
-  if (ukb < 1) ukb = 1;
-  *unit_kb = static_cast<int>(ukb);
-  *max_units = nk_total / ukb + V;
+// CTAs of one (output-channel group, input-channel tile) that run together: one per SM
+static int wave_units(const WgradPlan& w) {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int per_wave = sms / (w.co_groups * w.ci_tiles);
+  return per_wave > 0 ? per_wave : 1;
+}
+
+// Units to cut the pair lists into for `splitk` parts per offset on average: the workspace holds (splitk + 1) * V
+// slabs; of those, a whole number of waves when that is at least one wave (a unit count just above a multiple of the
+// wave runs as one more, nearly empty wave: measured 248 -> 388 us from 5 to 6 parts at RES=256, C=256).
+static int target_units(const WgradPlan& w, int V, int splitk) {
+  const int64_t budget = (int64_t(splitk) + 1) * V;
+  const int64_t wave = wave_units(w);
+  const int64_t t = budget >= wave ? budget / wave * wave : budget;
+  return static_cast<int>(t);
 }
 
 }  // namespace fgb
@@ -452,17 +491,17 @@ extern "C" int fgb_wgrad_default_splitk(int64_t n_pairs, int Ci, int Co, int V, 
   if (eb == 0) return FGB_E_DTYPE;
   if (Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
   const WgradPlan w = plan_wgrad(Ci, Co, eb);
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int64_t base = int64_t(V) * w.co_groups * w.ci_tiles;
-  // About two CTAs per SM in total: measured best on B200 at a few hundred k-blocks per unit (fewer leaves SMs idle
-  // in the second wave, more adds partial slabs without shortening the critical path).  Large inputs get more,
-  // shorter units (about 256 k-blocks each, at most 16 per SM) so that the last wave is a small part of the run.
-  int64_t s = (int64_t(2) * sms) / base;
+  // One wave of CTAs (one per SM) unless the units would be longer than about 256 k-blocks: then more, shorter units,
+  // at most 16 per SM, so that the last wave is a small part of the run.  (Two waves were best while the slab
+  // write-out was slow; with whole-line stores one wave wins at every size measured: RES=256 C=256 248 against 271
+  // us, RES=128 C=256 86 against 104, RES=128 C=64 46 against 53.)  The kernel plans the unit length from the
+  // segment table so that the unit count fills the waves exactly; splitk only has to make room for them.
+  const int64_t wave = wave_units(w);
   const int64_t total_kb = ceil_div(n_pairs, w.kb);
-  const int64_t by_work = total_kb / 256 / base;
-  if (by_work > s) s = by_work;
-  if (s > (int64_t(16) * sms) / base) s = (int64_t(16) * sms) / base;
+  int64_t waves = total_kb / 256 / wave;
+  if (waves < 1) waves = 1;
+  if (waves > 16) waves = 16;
+  int64_t s = ceil_div(waves * wave, V) - 1;  // (s + 1) * V >= waves * wave
   // no more splits than stages of pairs per offset on average
   const int64_t max_s = n_pairs > 0 ? ceil_div(ceil_div(n_pairs, V), w.kb) : 1;
   if (s > max_s) s = max_s;
@@ -510,8 +549,8 @@ static int wgrad_pass(const void* grad_out, const void* feats, const uint32_t* v
   p.seg = seg;
   p.partial = slabs;
   p.Co = Co, p.Ci = Ci, p.V = V;
-  int64_t max_units = 0;
-  unit_plan(n_pairs, V, w.kb, splitk, &p.unit_kb, &max_units);
+  p.target_units = target_units(w, V, splitk);
+  const int64_t max_units = p.target_units;
   p.mt = w.mt, p.bn = w.bn, p.co_groups = w.co_groups, p.ci_tiles = w.ci_tiles;
   p.kb = w.kb, p.stages = w.stages, p.a_chunks = w.a_chunks, p.b_chunks = w.b_chunks;
   const uint32_t fmt = dtype == FGB_F16 ? kFmtF16 : dtype == FGB_BF16 ? kFmtBF16 : kFmtTF32;
@@ -537,13 +576,13 @@ static int wgrad_pass(const void* grad_out, const void* feats, const uint32_t* v
   const dim3 rgrid(static_cast<unsigned>(ceil_div(int64_t(Co) * Ci, 1024)), static_cast<unsigned>(V));
   switch (dtype) {
     case FGB_F16:
-      splitk_reduce_kernel<__half><<<rgrid, 256, 0, s>>>(slabs, seg, p.kb, p.unit_kb, Co, V, Ci, static_cast<__half*>(grad_weight), grad_weight_f32, 0);
+      splitk_reduce_kernel<__half><<<rgrid, 256, 0, s>>>(slabs, seg, p.kb, p.target_units, Co, V, Ci, static_cast<__half*>(grad_weight), grad_weight_f32, 0);
       break;
     case FGB_BF16:
-      splitk_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, s>>>(slabs, seg, p.kb, p.unit_kb, Co, V, Ci, static_cast<__nv_bfloat16*>(grad_weight), grad_weight_f32, 0);
+      splitk_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, s>>>(slabs, seg, p.kb, p.target_units, Co, V, Ci, static_cast<__nv_bfloat16*>(grad_weight), grad_weight_f32, 0);
       break;
     default:
-      splitk_reduce_kernel<float><<<rgrid, 256, 0, s>>>(slabs, seg, p.kb, p.unit_kb, Co, V, Ci, static_cast<float*>(grad_weight), grad_weight_f32, accumulate);
+      splitk_reduce_kernel<float><<<rgrid, 256, 0, s>>>(slabs, seg, p.kb, p.target_units, Co, V, Ci, static_cast<float*>(grad_weight), grad_weight_f32, accumulate);
   }
   return launch_status();
 }
