@@ -491,17 +491,13 @@ extern "C" int fgb_wgrad_default_splitk(int64_t n_pairs, int Ci, int Co, int V, 
   if (eb == 0) return FGB_E_DTYPE;
   if (Ci <= 0 || Co <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
   const WgradPlan w = plan_wgrad(Ci, Co, eb);
-  // One wave of CTAs (one per SM) unless the units would be longer than about 256 k-blocks: then more, shorter units,
-  // at most 16 per SM, so that the last wave is a small part of the run.  (Two waves were best while the slab
-  // write-out was slow; with whole-line stores one wave wins at every size measured: RES=256 C=256 248 against 271
-  // us, RES=128 C=256 86 against 104, RES=128 C=64 46 against 53.)  The kernel plans the unit length from the
-  // segment table so that the unit count fills the waves exactly; splitk only has to make room for them.
+  // One wave of CTAs, one per SM, whatever the input size: the kernel plans the unit length from the segment table so
+  // that the unit count fills the wave exactly, and splitk only has to make room for it.  (Two waves were best while
+  // the slab write-out was slow; with whole-line stores one wave wins at every size measured -- RES=256 C=256 248
+  // against 271 us, RES=128 C=256 86 against 104, RES=128 C=64 46 against 53, RES=1024 C=64 1650 against 1698 for
+  // five waves -- and every further wave costs a little more: partial slabs and a write-out pause per unit.)
   const int64_t wave = wave_units(w);
-  const int64_t total_kb = ceil_div(n_pairs, w.kb);
-  int64_t waves = total_kb / 256 / wave;
-  if (waves < 1) waves = 1;
-  if (waves > 16) waves = 16;
-  int64_t s = ceil_div(waves * wave, V) - 1;  // (s + 1) * V >= waves * wave
+  int64_t s = ceil_div(wave, V) - 1;  // (s + 1) * V >= wave
   // no more splits than stages of pairs per offset on average
   const int64_t max_s = n_pairs > 0 ? ceil_div(ceil_div(n_pairs, V), w.kb) : 1;
   if (s > max_s) s = max_s;
