@@ -216,15 +216,17 @@ int fgb_subm_conv_dgrad(const void* grad_out, const void* weight,
  * hi/lo-split copies of its operands, hence the dependence on n. */
 int64_t fgb_conv_workspace_bytes(int pass, int64_t n, int Ci, int Co, int V, int dtype, int splitk);
 
-/* Split count the library would pick for wgrad on the current device. */
+/* Split count the library would pick for wgrad on the current device (room for one wave of units). */
 int fgb_wgrad_default_splitk(int64_t n_pairs, int Ci, int Co, int V, int dtype);
 
 /* grad_weight[co, v, ci] = sum_{p in segment v} grad_out[valid_signal_o[p], co]
  *                                              * feats[valid_signal_i[p], ci]
- * The pair lists are cut into units of equal length (about `splitk` per offset
- * on average; an offset with more pairs gets more units); each unit's fp32
- * partial [Co, Ci] goes to the workspace and the partials of an offset are then
- * added in a fixed order (deterministic).  n_pairs is the length of the pair
+ * The pair lists are cut into units of equal length (an offset with more pairs
+ * gets more units).  `splitk` is the budget: the workspace holds (splitk + 1) * V
+ * partials, and the kernel uses the largest whole number of waves of CTAs (one
+ * per SM) that fits it, planning the unit length from valid_signal_seg on the
+ * device.  Each unit's fp32 partial [Co, Ci] goes to the workspace and the
+ * partials of an offset are then added in a fixed order (deterministic).  n_pairs is the length of the pair
  * lists (valid_signal_seg[V]).  grad_weight (element type `dtype`) and/or
  * grad_weight_f32 may be null; the fp32 copy is what a multi-GPU caller hands
  * to its all-reduce.
