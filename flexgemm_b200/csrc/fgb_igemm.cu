@@ -36,6 +36,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "fgb_common.cuh"
@@ -610,6 +611,11 @@ static int pick_bn(int nout) {
   return bn;
 }
 
+// Upper bound on the CTAs (= SMs) of the persistent conv kernels; 0 = all.  A caller that has a collective running
+// beside a conv kernel leaves it some SMs this way: the conv CTAs fill their SMs completely (shared memory and
+// registers), so a kernel launched beside them would otherwise wait for the first of them to finish.
+static std::atomic<int> g_cta_limit{0};
+
 static int sm_count() {
   static int sms = []() {
     int dev = 0, n = 148;
@@ -629,7 +635,10 @@ static int launch_igemm_variant(const CUtensorMap& tmap, const IgemmParams& p, c
     configured = smem;
   }
   const int64_t work = int64_t(p.num_blocks) * p.n_tiles_n;
-  const unsigned grid = static_cast<unsigned>(work < sm_count() ? work : sm_count());
+  int ctas = sm_count();
+  const int limit = g_cta_limit.load(std::memory_order_relaxed);
+  if (limit > 0 && limit < ctas) ctas = limit;
+  const unsigned grid = static_cast<unsigned>(work < ctas ? work : ctas);
   subm_igemm_kernel<kDtype, kFused><<<grid, kIgemmThreads, smem, s>>>(tmap, p, fe);
   return launch_status();
 }
@@ -705,6 +714,11 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
 }  // namespace fgb
 
 extern "C" int fgb_conv_tile_rows(void) { return fgb::kTileM; }
+
+extern "C" int fgb_conv_set_cta_limit(int max_ctas) {
+  if (max_ctas < 0) return FGB_E_SIZE;
+  return fgb::g_cta_limit.exchange(max_ctas, std::memory_order_relaxed);
+}
 
 extern "C" int fgb_conv_block_schedule(const uint32_t* tile_masks, int64_t num_tiles, uint32_t* block_order, void* stream) {
   using namespace fgb;

@@ -325,6 +325,19 @@ def conv_tile_rows() -> int:
     return int(_cabi.lib().fgb_conv_tile_rows())
 
 
+def set_conv_cta_limit(max_ctas: int) -> int:
+    """Cap the CTAs (SMs) of the persistent fprop / dgrad kernels launched from now
+    on (0 = no cap); returns the previous cap."""
+    prev = _cabi.lib().fgb_conv_set_cta_limit(int(max_ctas))
+    if prev < 0:
+        _cabi.check(prev, "fgb_conv_set_cta_limit")
+    return prev
+
+
+def sm_count(device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
 def conv_fprop(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks, order=None) -> torch.Tensor:
     """feats [N_in,Ci], weight_cvc [Co,V,Ci], neighbor_map [N_out,V] -> out [N_out,Co]
     (N_in = N_out for a submanifold conv)."""

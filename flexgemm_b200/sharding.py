@@ -8,6 +8,7 @@ sum of the weight (and bias) gradient, done as ONE all-reduce of an fp32 buffer
 ``[Co*V*Ci + Co]`` -- NCCL over NVLink on GPUs.  Outputs and feature gradients
 stay sharded.  The reference has no multi-GPU path; this is an addition.
 """
+import os
 from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
@@ -70,6 +71,12 @@ def local_shard(coords: torch.Tensor, feats: Optional[torch.Tensor], shape, rank
     return coords_l, feats_l, torch.Size((max(len(mine), 1), C, W, H, D)), rows_t
 
 
+# SMs left to the all-reduce of the parameter gradients while dgrad runs (FGB_ALLREDUCE_SMS overrides).  Off by
+# default: measured on B200 with NCCL 2.28 it does not pay (2 GPUs: 0.784 ms/step with 0, 0.786 with 8 or 16, 0.831 with
+# 32 SMs left over; 8 GPUs: 0.787 with 0, 0.793 with 16) -- NCCL's kernel gets onto the SMs beside the dgrad CTAs.
+ALLREDUCE_SMS = int(os.environ.get("FGB_ALLREDUCE_SMS", "0"))
+
+
 def _cuda_local_grads(grad_out, feats, cache, weight_cvc, has_bias):
     """fp32 weight / bias gradient of the local shard through the CUDA kernels."""
     from .kernels import cuda as K
@@ -119,7 +126,15 @@ def sharded_backward(grad_out: torch.Tensor, feats: torch.Tensor, cache, weight:
         gw32, gb32, work = allreduce_param_grads(gw32, gb32, group, async_op=True)
         if want_input_grad:
             tile = K.conv_tile_rows()
-            grad_in = K.conv_dgrad(grad_out, w, cache["neighbor_map"], cache["sorted_idx"], cache.tile_masks(tile), cache.block_order(tile))
+            # the dgrad CTAs fill their SMs: leave the all-reduce a few, or it would only start when dgrad ends
+            reserve = ALLREDUCE_SMS if work is not None else 0
+            prev = K.set_conv_cta_limit(max(K.sm_count(grad_out.device) - reserve, 1)) if reserve > 0 else None
+            try:
+                grad_in = K.conv_dgrad(grad_out, w, cache["neighbor_map"], cache["sorted_idx"], cache.tile_masks(tile),
+                                       cache.block_order(tile))
+            finally:
+                if prev is not None:
+                    K.set_conv_cta_limit(prev)
         if work is not None:
             work.wait()
     else:

@@ -151,6 +151,14 @@ int fgb_pp_valid_kernel(const uint32_t* tile_masks, int64_t nblk,
  * been built with block == fgb_conv_tile_rows(). */
 int fgb_conv_tile_rows(void);
 
+/* Caps the number of CTAs (one per SM) that the persistent fprop / dgrad kernels
+ * launch from now on; 0 lifts the cap.  Returns the previous value.  For callers
+ * that run a collective beside a conv kernel (the multi-GPU backward launches
+ * its all-reduce before dgrad): the conv CTAs fill their SMs, so without a few
+ * SMs left over the collective's kernel would only start when the conv ends.
+ * Process-wide; read when a kernel is launched. */
+int fgb_conv_set_cta_limit(int max_ctas);
+
 /* block_order (uint32 [ceil(num_tiles / 2)]) = the 256-row blocks (pairs of
  * consecutive 128-row tiles) in descending order of work, computed from the tile
  * masks.  The persistent conv kernels deal blocks to the SMs from this list so
