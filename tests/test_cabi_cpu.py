@@ -99,6 +99,13 @@ def test_fused_fprop_validates_without_launch(lib):
     assert hasattr(spconv, "sparse_submanifold_conv3d_fused") and hasattr(spconv, "SubMConv3dFusedFunction")
 
 
+def test_conv_cta_limit_is_a_plain_host_setting(lib):
+    assert lib.fgb_conv_set_cta_limit(100) == 0
+    assert lib.fgb_conv_set_cta_limit(0) == 100
+    assert lib.fgb_conv_set_cta_limit(-1) == -2
+    assert lib.fgb_conv_set_cta_limit(0) == 0
+
+
 def test_python_surface_matches_reference_names():
     for name in ("Algorithm", "ALGORITHM", "HASHMAP_RATIO", "set_algorithm", "set_hashmap_ratio", "SubMConv3dFunction",
                  "SubMConv3dNeighborCache", "sparse_submanifold_conv3d", "SparseConv3dFunction", "SparseConv3dNeighborCache",
