@@ -56,7 +56,7 @@ RES, CI, CO = 256, 256, 256
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at this workload, from the ncu capture summarised in
 # profiles/subm_igemm_and_wgrad_res256_c256_fp16.md
-NCU_DRAM_TRAFFIC_BYTES = {"fprop": 291.9e6, "dgrad": 291.4e6, "wgrad": 862.8e6}
+NCU_DRAM_TRAFFIC_BYTES = {"fprop": 291.9e6, "dgrad": 291.4e6, "wgrad": 522.4e6}
 
 
 def load_peaks():
