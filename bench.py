@@ -34,12 +34,19 @@ import statistics
 import sys
 import time
 
-# stdout carries the one JSON line and nothing else: libraries that write there from native code (NCCL prints its
-# version line on the first communicator) get stderr instead, and the line goes out through a copy of the real stdout
-_JSON_OUT = os.fdopen(os.dup(1), "w")
-os.dup2(2, 1)
+import torch
 
-import torch  # noqa: E402
+_JSON_OUT = sys.stdout
+
+
+def claim_stdout() -> None:
+    """stdout carries the one JSON line and nothing else: libraries that write there from native code (NCCL prints
+    its version line on the first communicator) get stderr instead, and the line goes out through a copy of the real
+    stdout.  Called once by main()."""
+    global _JSON_OUT
+    sys.stdout.flush()
+    _JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
 
 
 def emit(line: dict) -> None:
@@ -644,6 +651,7 @@ def main():
     ap.add_argument("--unsorted", action="store_true", help="res1024_map: shuffle the rows (hash-table path)")
     ap.add_argument("--fused", action="store_true", help="residual_stack: SiLU and skip additions in the conv epilogues")
     args = ap.parse_args()
+    claim_stdout()
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.workload == "res1024_batch8":
