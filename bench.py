@@ -373,7 +373,8 @@ def run_gpu_arm(args):
     it = max(args.steps, 10)
     t_fprop = time_loop(lambda: K.conv_fprop(feats, w_cvc, bias, cache["neighbor_map"], cache["sorted_idx"], masks, order), it)
     t_dgrad = time_loop(lambda: K.conv_dgrad(gout, w_cvc, cache["neighbor_map"], cache["sorted_idx"], masks, order), it)
-    t_wgrad = time_loop(lambda: K.conv_wgrad(gout, feats, cache["valid_signal_i"], cache["valid_signal_o"], cache["valid_signal_seg"]), it)
+    t_wgrad = time_loop(lambda: K.conv_wgrad(gout, feats, cache["valid_signal_i"], cache["valid_signal_o"], cache["valid_signal_seg"],
+                                             block_offsets=cache["pair_block_offsets"]), it)
     kernels = {"fprop": t_fprop, "dgrad": t_dgrad, "wgrad": t_wgrad}
     dom = max(kernels, key=kernels.get)
     pass_flops = 2.0 * pairs * CI * CO

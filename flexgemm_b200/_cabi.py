@@ -18,6 +18,7 @@ _P = c_void_p
 _PROTOTYPES = {
     "fgb_version": (c_char_p, []),
     "fgb_error_string": (c_char_p, [c_int]),
+    "fgb_selftest_device_tables": (c_int, []),
     "fgb_hash_table_bytes": (c_int64, [c_int64, c_int]),
     "fgb_map_num_blocks": (c_int64, [c_int64]),
     "fgb_subm_build_neighbor_map": (c_int, [_P, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -36,7 +37,9 @@ _PROTOTYPES = {
     "fgb_subm_conv_dgrad": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
     "fgb_conv_workspace_bytes": (c_int64, [c_int, c_int64, c_int, c_int, c_int, c_int, c_int]),
     "fgb_wgrad_default_splitk": (c_int, [c_int64, c_int, c_int, c_int, c_int]),
-    "fgb_subm_conv_wgrad": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
+    "fgb_subm_conv_wgrad": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
+    "fgb_wgrad_set_row_bands": (c_int, [c_int]),
+    "fgb_wgrad_plan_host": (c_int, [_P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
     "fgb_bias_grad_workspace_bytes": (c_int64, [c_int]),
     "fgb_subm_conv_bias_grad": (c_int, [_P, _P, _P, c_int64, c_int, c_int, _P, c_int64, _P]),
     "fgb_cast_from_f32": (c_int, [_P, _P, c_int64, c_int, _P]),
@@ -53,7 +56,7 @@ _PROTOTYPES = {
     "fgb_pp_gray_code": (c_int, [_P, c_int64, c_int, _P, _P, _P]),
     "fgb_sparse_conv_fprop": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
     "fgb_sparse_conv_dgrad": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
-    "fgb_sparse_conv_wgrad": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
+    "fgb_sparse_conv_wgrad": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
     "fgb_sparse_conv_workspace_bytes": (c_int64, [c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int]),
     "fgb_noalloc_max_channels": (c_int, []),
     "fgb_subm_conv_bias_grad_noalloc": (c_int, [_P, _P, _P, c_int64, c_int, c_int, _P]),

@@ -40,6 +40,7 @@
 #include <type_traits>
 
 #include "fgb_common.cuh"
+#include "fgb_device.cuh"
 #include "fgb_precision.cuh"
 #include "fgb_umma.cuh"
 
@@ -106,39 +107,46 @@ struct IgemmSmem {
 };
 static_assert(sizeof(IgemmSmem) <= kCtrlBytes, "control block too large");
 
-// Adds the bias to 32 accumulator columns of one row, converts them and writes
-// them as 16-byte pieces into the warp's staging buffer: row `lane`, pieces
+// Converts 32 accumulator columns of one row, adds the bias and writes them as
+// 16-byte pieces into the warp's staging buffer: row `lane`, pieces
 // chunk*4 .. chunk*4+3 (16-bit types: two chunks fill a 128-byte row) or 0 .. 7
 // (fp32: one chunk is a whole 128-byte row); piece p of row r sits at p ^ (r & 7).
+// 16-bit types: two columns are rounded per instruction and the bias is added to
+// the rounded pair in the output type (what a bias add after the conversion does);
+// fp32 adds in fp32.  The epilogue runs while the MMA lane waits for the
+// accumulator, so its length in instructions is time the tensor pipe idles.
 template <int kDtype>
 __device__ __forceinline__ void stage_row_chunk(uint8_t* stage, int lane, int chunk, const uint32_t (&acc)[32], const void* bias,
-                                                int col0, int nout, bool zero_acc) {
-  float v[32];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = zero_acc ? 0.f : __uint_as_float(acc[i]);
+                                                int col0, int nout) {
   uint8_t* row = stage + lane * 128;
   if constexpr (kDtype == FGB_F16 || kDtype == FGB_BF16) {
     using T = typename std::conditional<kDtype == FGB_F16, __half, __nv_bfloat16>::type;
+    using T2 = typename std::conditional<kDtype == FGB_F16, __half2, __nv_bfloat162>::type;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {  // 8 columns = 16 bytes
       const int c = col0 + g * 8;
+      uint4 o;
+      T2* o2 = reinterpret_cast<T2*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float lo = __uint_as_float(acc[g * 8 + 2 * i]), hi = __uint_as_float(acc[g * 8 + 2 * i + 1]);
+        if constexpr (kDtype == FGB_F16) o2[i] = __floats2half2_rn(lo, hi);
+        else o2[i] = __floats2bfloat162_rn(lo, hi);
+      }
       if (bias != nullptr && c < nout) {
         const uint4 bw = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(bias) + c));
-        const T* bt = reinterpret_cast<const T*>(&bw);
+        const T2* b2 = reinterpret_cast<const T2*>(&bw);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[g * 8 + i] += static_cast<float>(bt[i]);
+        for (int i = 0; i < 4; ++i) o2[i] = __hadd2(o2[i], b2[i]);
       }
-      uint4 o;
-      T* ot = reinterpret_cast<T*>(&o);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ot[i] = static_cast<T>(v[g * 8 + i]);
       *reinterpret_cast<uint4*>(row + (((chunk * 4 + g) ^ (lane & 7)) << 4)) = o;
     }
   } else {
 #pragma unroll
     for (int g = 0; g < 8; ++g) {  // 4 columns = 16 bytes
       const int c = col0 + g * 4;
-      float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+      float4 o = make_float4(__uint_as_float(acc[g * 4]), __uint_as_float(acc[g * 4 + 1]), __uint_as_float(acc[g * 4 + 2]),
+                             __uint_as_float(acc[g * 4 + 3]));
       if (bias != nullptr && c < nout) {
         const float4 b = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(bias) + c));
         o.x += b.x, o.y += b.y, o.z += b.z, o.w += b.w;
@@ -417,6 +425,8 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
           const bool need0 = (m0 >> v) & 1u, need1 = (m1 >> v) & 1u;
           for (int kb = 0; kb < p.num_kb; ++kb) {
             mbar_wait(&ctl->full[s], ph, abort_flag);
+            // the activation rows were written by cp.async (generic proxy), the MMA reads them through the async proxy
+            fence_proxy_async_smem();
             tc_fence_after_sync();
             const uint32_t a_addr = smem_u32(stages + size_t(s) * stage_bytes);
             const uint64_t da0 = make_smem_desc(a_addr, 16, 1024);
@@ -481,27 +491,34 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
 #pragma unroll
             for (int cc = 0; cc < kChunksPerPass; ++cc) tmem_ld_32x32(t_addr + c0 + cc * 32, acc[cc]);
             tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int cc = 0; cc < kChunksPerPass; ++cc)
+#pragma unroll
+              for (int i = 0; i < 32; ++i) acc[cc][i] = 0u;
           }
 #pragma unroll
           for (int cc = 0; cc < kChunksPerPass; ++cc)
-            stage_row_chunk<kDtype>(stage_out, lane, cc, acc[cc], p.bias, n0 + c0 + cc * 32, p.nout, !has_acc);
+            stage_row_chunk<kDtype>(stage_out, lane, cc, acc[cc], p.bias, n0 + c0 + cc * 32, p.nout);
           __syncwarp();
           {
             // 128 bytes per row: lane -> (row = 4 i + lane / 8, piece = lane % 8)
+            const int piece = lane & 7;
+            const int col = n0 + c0 + piece * (16 / kElem);
+            const bool col_ok = col < p.nout;
+            const uint8_t* src = stage_out + (lane >> 3) * 128;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const int row = i * 4 + (lane >> 3), piece = lane & 7;
-              const uint32_t orow = __shfl_sync(0xffffffffu, sr[h], row);
-              const int col = n0 + c0 + piece * (16 / kElem);
-              const uint4 val = *reinterpret_cast<const uint4*>(stage_out + row * 128 + ((piece ^ (row & 7)) << 4));
+              const int row = i * 4 + (lane >> 3);
+              const uint32_t orow = __shfl_sync(0xffffffffu, sr[h], row);  // output row of staging row `row`
+              const uint4 val = *reinterpret_cast<const uint4*>(src + i * 512 + ((piece ^ (row & 7)) << 4));
               if constexpr (kFused) {
-                if (orow != kInvalid && col < p.nout) {
+                if (orow != kInvalid && col_ok) {
                   const size_t byte_off = (size_t(orow) * p.nout + col) * kElem;
                   *reinterpret_cast<uint4*>(p.out + byte_off) = fuse_piece<kDtype>(val, fe.act, fe.residual, fe.preact, byte_off);
                 }
               } else {
-                if (orow != kInvalid && col < p.nout)
-                  *reinterpret_cast<uint4*>(p.out + (size_t(orow) * p.nout + col) * kElem) = val;
+                if (orow != kInvalid && col_ok) *reinterpret_cast<uint4*>(p.out + (size_t(orow) * p.nout + col) * kElem) = val;
               }
             }
           }
@@ -616,26 +633,14 @@ static int pick_bn(int nout) {
 // registers), so a kernel launched beside them would otherwise wait for the first of them to finish.
 static std::atomic<int> g_cta_limit{0};
 
-static int sm_count() {
-  static int sms = []() {
-    int dev = 0, n = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n;
-  }();
-  return sms;
-}
-
 template <int kDtype, bool kFused>
 static int launch_igemm_variant(const CUtensorMap& tmap, const IgemmParams& p, const FusedEpilogue& fe, cudaStream_t s) {
   const size_t smem = 1024 + kCtrlBytes + size_t(p.stages) * (2 * kATileBytes + p.bn * 128) + kStoreStageBytes;
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(subm_igemm_kernel<kDtype, kFused>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) return cuda_status(e);
-    configured = smem;
-  }
+  static PerDeviceTable configured;  // the attribute belongs to (kernel instance, device)
+  const int rc = ensure_dynamic_smem(configured, subm_igemm_kernel<kDtype, kFused>, smem);
+  if (rc != FGB_OK) return rc;
   const int64_t work = int64_t(p.num_blocks) * p.n_tiles_n;
-  int ctas = sm_count();
+  int ctas = device_sm_count();
   const int limit = g_cta_limit.load(std::memory_order_relaxed);
   if (limit > 0 && limit < ctas) ctas = limit;
   const unsigned grid = static_cast<unsigned>(work < ctas ? work : ctas);

@@ -20,10 +20,12 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <mutex>
 #include <type_traits>
 
 #include "fgb_common.cuh"
+#include "fgb_device.cuh"
 #include "fgb_precision.cuh"
 #include "fgb_umma.cuh"
 
@@ -34,6 +36,7 @@ constexpr int kWgGatherWarp0 = 5;
 constexpr int kWgGatherThreads = 256;
 constexpr int kWgMaxStages = 8;
 constexpr int kWgRowsMax = 4;  // pair rows of a stage per gather thread: stages hold up to 128 pairs
+constexpr int kWgMaxBands = 64;
 
 struct WgradParams {
   const char* gout;  // [n, Co]
@@ -41,6 +44,10 @@ struct WgradParams {
   const uint32_t* vs_i;
   const uint32_t* vs_o;
   const uint32_t* seg;  // [V + 1]
+  const uint32_t* block_offsets;  // [V, nblk]: pairs of offset v in the 256-row map blocks before block k; null = one band
+  uint32_t nblk;        // 256-row map blocks of the output rows
+  uint32_t band_blocks; // map blocks per row band
+  int bands;            // row bands (1 .. kWgMaxBands)
   float* partial;       // [units, Co, Ci] slabs
   int Co, Ci, V;
   int target_units;  // the kernel cuts the pair lists into at most this many units (see wg_plan_unit_kb)
@@ -66,6 +73,9 @@ struct WgradSmem {
   uint32_t abort_flag;
   int unit_v, unit_j;  // the unit this CTA works on (offset, chunk index), -1 if none
   int unit_kb;         // k-blocks per unit, planned from the segment table
+  int total;           // k-blocks (stages) of this CTA over all bands
+  // this CTA's share of each row band: first pair, k-blocks, and the band's end in the pair list
+  uint32_t band_begin[kWgMaxBands], band_cnt[kWgMaxBands], band_end[kWgMaxBands];
 };
 static_assert(sizeof(WgradSmem) <= 1024, "control block too large");
 
@@ -130,6 +140,33 @@ __device__ __forceinline__ uint32_t wg_slab_of(const uint32_t* seg, int kb, int 
   return base + j;
 }
 
+// ------------------------------------------------------------------ row bands
+// The pair list of an offset is in ascending output-row order, and the input row of a pair lies near its output
+// row.  Cutting EVERY offset's list at the same output rows (bands of `band_blocks` 256-row map blocks) and letting
+// every CTA of an offset take its share of every band, band after band, makes all CTAs of the launch read the same
+// band of rows of both matrices at the same time: the band is fetched from HBM once and the other offsets find it
+// in L2.  (With each CTA walking one contiguous piece of one list, the 148 CTAs are spread over the whole row range
+// at any moment and every offset streams both matrices from HBM again.)
+//
+// Position in the pair list where band b of offset v starts; b == bands gives the end of the list.
+__host__ __device__ __forceinline__ uint32_t wg_band_pos(const uint32_t* seg, const uint32_t* block_offsets, uint32_t nblk,
+                                                         uint32_t band_blocks, int bands, int v, int b) {
+  if (b <= 0) return seg[v];
+  const uint64_t blk = uint64_t(b) * band_blocks;
+  if (b >= bands || blk >= nblk || block_offsets == nullptr) return seg[v + 1];
+  return seg[v] + block_offsets[size_t(v) * nblk + blk];
+}
+// Share of CTA `k` (of K for the offset) in a band of `nkb` k-blocks.  The K CTAs get nkb / K blocks each and the
+// remainder goes to nkb % K of them, dealt round-robin from where the previous bands stopped (`rot` = sum of the
+// earlier bands' remainders), so that over all bands the CTAs' totals differ by at most one block.
+// Returns the count; *first = index of the CTA's first block within the band.
+__host__ __device__ __forceinline__ uint32_t wg_band_share(uint32_t nkb, uint32_t K, uint32_t k, uint32_t rot, uint32_t* first) {
+  const uint32_t base = nkb / K, rem = nkb - base * K;
+  const uint32_t q = (k + K - rot % K) % K;  // position of this CTA in the band's dealing order
+  *first = q * base + (q < rem ? q : rem);
+  return base + (q < rem ? 1u : 0u);
+}
+
 template <int kElem, int kRows>  // kRows = pairs of a stage / 32 = pair rows per gather thread
 __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradParams p) {
   constexpr bool kTF32 = (kElem == 4);
@@ -157,11 +194,44 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
   bid /= p.co_groups;
   if (warp == 0) {
     const uint32_t ukb = wg_plan_unit_kb(p.seg, p.V, p.kb, static_cast<uint32_t>(p.target_units), lane);
+    int v = -1, j = -1;
     if (lane == 0) {
-      int v = -1, j = -1;
       const bool skip = p.status != nullptr && *reinterpret_cast<volatile const int32_t*>(p.status) != 0;
       if (skip || !wg_find_unit(p.seg, p.V, p.kb, static_cast<int>(ukb), p.order, bid, &v, &j)) v = j = -1;
       ctl->unit_v = v, ctl->unit_j = j, ctl->unit_kb = static_cast<int>(ukb);
+    }
+    v = __shfl_sync(0xffffffffu, v, 0), j = __shfl_sync(0xffffffffu, j, 0);
+    if (v >= 0) {
+      // this CTA's share of every row band (lane b looks at band b, 32 bands per round)
+      const uint32_t K = wg_chunks_of(p.seg, v, p.kb, static_cast<int>(ukb));
+      uint32_t rot = 0, total = 0;
+      for (int b0 = 0; b0 < p.bands; b0 += 32) {
+        const int b = b0 + lane;
+        uint32_t begin = 0, end = 0, nkb = 0;
+        if (b < p.bands) {
+          begin = wg_band_pos(p.seg, p.block_offsets, p.nblk, p.band_blocks, p.bands, v, b);
+          end = wg_band_pos(p.seg, p.block_offsets, p.nblk, p.band_blocks, p.bands, v, b + 1);
+          nkb = (end - begin + p.kb - 1) / p.kb;
+        }
+        // exclusive prefix of the remainders over the bands before this one
+        const uint32_t rem = nkb % K;
+        uint32_t inc = rem;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const uint32_t y = __shfl_up_sync(0xffffffffu, inc, d);
+          if (lane >= d) inc += y;
+        }
+        uint32_t first = 0;
+        const uint32_t cnt = wg_band_share(nkb, K, static_cast<uint32_t>(j), rot + inc - rem, &first);
+        if (b < p.bands) {
+          ctl->band_begin[b] = begin + first * p.kb;
+          ctl->band_cnt[b] = cnt;
+          ctl->band_end[b] = end;
+        }
+        total += __reduce_add_sync(0xffffffffu, cnt);
+        rot += __shfl_sync(0xffffffffu, inc, 31);
+      }
+      if (lane == 0) ctl->total = static_cast<int>(total);
     }
   }
   __syncthreads();
@@ -169,13 +239,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
   if (v < 0) return;  // grid is sized for the worst case; also the no-op path after a soft error
   const int co0 = co_group * p.mt * 128;
   const int ci0 = ci_tile * p.bn;
-
-  const uint32_t seg_begin = __ldg(&p.seg[v]);
-  const uint32_t seg_end = __ldg(&p.seg[v + 1]);
-  const uint32_t num_k = (seg_end - seg_begin + p.kb - 1) / p.kb;
-  const uint32_t k_begin = static_cast<uint32_t>(unit_j) * unit_kb;
-  const uint32_t k_end = min(num_k, k_begin + unit_kb);
-  const int total = static_cast<int>(k_end - k_begin);  // >= 1 by construction
+  const int total = ctl->total;  // may be 0 for a CTA of a very short offset: it writes a slab of zeros
   volatile uint32_t* abort_flag = &ctl->abort_flag;
 
   if (tid == 0) {
@@ -211,23 +275,33 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
       const int swz = kElem == 2 ? ((piece ^ (row & 7)) << 4) : (((((piece >> 1) ^ (row & 3)) << 1) | (piece & 1)) << 4);
       row_off[j] = row * 128 + swz;
     }
-    auto load_pairs = [&](uint32_t kblk, uint32_t (&io)[kRows], uint32_t (&ii)[kRows]) {
+    // walks the CTA's k-blocks band by band: (band, block within the CTA's share of the band)
+    int band = 0;
+    uint32_t blk = 0;
+    auto skip_empty = [&]() {
+      while (band < p.bands && blk >= ctl->band_cnt[band]) ++band, blk = 0;
+    };
+    auto load_pairs = [&](uint32_t (&io)[kRows], uint32_t (&ii)[kRows]) {  // pairs of block (band, blk), then advance
+      const uint32_t first = ctl->band_begin[band] + blk * p.kb, end = ctl->band_end[band];
 #pragma unroll
       for (int j = 0; j < kRows; ++j) {
-        const uint32_t pp = seg_begin + kblk * p.kb + g + 32 * j;
-        const bool ok = pp < seg_end;
+        const uint32_t pp = first + g + 32 * j;
+        const bool ok = pp < end;
         io[j] = ok ? __ldg(&p.vs_o[pp]) : kInvalid;
         ii[j] = ok ? __ldg(&p.vs_i[pp]) : kInvalid;
       }
+      ++blk;
+      skip_empty();
     };
     uint32_t io[kRows], ii[kRows], nio[kRows], nii[kRows];
-    load_pairs(k_begin, nio, nii);
+    skip_empty();
+    if (total > 0) load_pairs(nio, nii);
     int s = 0;
     uint32_t ph = 0;  // ring position and phase bit, advanced by hand (no division by the runtime stage count per stage)
     for (int it = 0; it < total; ++it) {
 #pragma unroll
       for (int j = 0; j < kRows; ++j) io[j] = nio[j], ii[j] = nii[j];
-      if (it + 1 < total) load_pairs(k_begin + it + 1, nio, nii);  // one stage ahead
+      if (it + 1 < total) load_pairs(nio, nii);  // one stage ahead
       const char* srca[kRows];
       const char* srcb[kRows];
 #pragma unroll
@@ -261,6 +335,8 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
       uint32_t ph = 0;
       for (int it = 0; it < total; ++it) {
         mbar_wait(&ctl->full[s], ph, abort_flag);
+        // both operands were written by cp.async (generic proxy), the MMA reads them through the async proxy
+        fence_proxy_async_smem();
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(stages + size_t(s) * stage_bytes);
         const uint32_t b_addr = a_addr + a_bytes;
@@ -276,7 +352,8 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
         umma_commit(&ctl->empty[s]);
         if (++s == S) s = 0, ph ^= 1;
       }
-      umma_commit(&ctl->acc_full);
+      if (total > 0) umma_commit(&ctl->acc_full);
+      else mbar_arrive(&ctl->acc_full);  // nothing was issued: the epilogue writes zeros
     }
   } else {
     // -------------------------------------------------------------- epilogue
@@ -294,8 +371,13 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
       float* obase = p.partial + (size_t(slab) * p.Co + co_base) * p.Ci;
       for (int c0 = 0; c0 < p.bn; c0 += 32) {
         uint32_t acc[32];
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + mt * p.bn + c0, acc);
-        tmem_ld_wait();
+        if (total > 0) {
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + mt * p.bn + c0, acc);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = 0u;
+        }
 #pragma unroll
         for (int g4 = 0; g4 < 8; ++g4)
           *reinterpret_cast<uint4*>(stage_out + lane * 128 + ((g4 ^ (lane & 7)) << 4)) =
@@ -467,8 +549,7 @@ static WgradPlan plan_wgrad(int Ci, int Co, int eb) {
 
 // CTAs of one (output-channel group, input-channel tile) that run together: one per SM
 static int wave_units(const WgradPlan& w) {
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = device_sm_count();
   const int per_wave = sms / (w.co_groups * w.ci_tiles);
   return per_wave > 0 ? per_wave : 1;
 }
@@ -483,7 +564,40 @@ static int target_units(const WgradPlan& w, int V, int splitk) {
   return static_cast<int>(t);
 }
 
+// Row bands of the pair-list walk (see wg_band_pos): bands of about 8 MB of rows of both matrices, so that the band the
+// CTAs are working on -- and the one they drift into -- stay in L2; never so many that the partial k-block at the end of
+// every (offset, band) piece adds up to more than ~2 % of the blocks; at most kWgMaxBands.  0 = automatic.
+static std::atomic<int> g_row_bands{0};
+
+static void plan_bands(int64_t n_out, int64_t n_in, int64_t n_pairs, int Ci, int Co, int V, int eb, int kb, bool have_offsets,
+                       int* bands, uint32_t* nblk, uint32_t* band_blocks) {
+  const int64_t blocks = ceil_div(n_out > 0 ? n_out : 1, kMapBlock);
+  int64_t b = 1;
+  if (have_offsets) {
+    const int forced = g_row_bands.load(std::memory_order_relaxed);
+    if (forced > 0) {
+      b = forced;
+    } else {
+      b = (n_out * Co + n_in * Ci) * eb / (int64_t(8) << 20);
+      const int64_t waste_cap = n_pairs / (int64_t(25) * kb * V);  // 0.5 * V * bands <= 2 % of n_pairs / kb
+      if (b > waste_cap) b = waste_cap;
+    }
+    if (b > kWgMaxBands) b = kWgMaxBands;
+    if (b > blocks) b = blocks;
+    if (b < 1) b = 1;
+  }
+  const int64_t per = ceil_div(blocks, b);
+  *bands = static_cast<int>(ceil_div(blocks, per));
+  *nblk = static_cast<uint32_t>(blocks);
+  *band_blocks = static_cast<uint32_t>(per);
+}
+
 }  // namespace fgb
+
+extern "C" int fgb_wgrad_set_row_bands(int bands) {
+  if (bands < 0 || bands > fgb::kWgMaxBands) return FGB_E_SIZE;
+  return fgb::g_row_bands.exchange(bands, std::memory_order_relaxed);
+}
 
 extern "C" int fgb_wgrad_default_splitk(int64_t n_pairs, int Ci, int Co, int V, int dtype) {
   using namespace fgb;
@@ -533,8 +647,9 @@ extern "C" int64_t fgb_sparse_conv_workspace_bytes(int pass, int64_t n_out, int6
 namespace fgb {
 // one wgrad pass over operands of element type `dtype` (never FGB_F32_IEEE): partial slabs, then the ordered sum
 static int wgrad_pass(const void* grad_out, const void* feats, const uint32_t* vs_i, const uint32_t* vs_o, const uint32_t* seg,
-                      void* grad_weight, float* grad_weight_f32, int64_t n_pairs, int Ci, int Co, int V, int dtype, int splitk,
-                      float* slabs, int accumulate, int32_t* status, cudaStream_t s) {
+                      const uint32_t* block_offsets, void* grad_weight, float* grad_weight_f32, int64_t n_out, int64_t n_in,
+                      int64_t n_pairs, int Ci, int Co, int V, int dtype, int splitk, float* slabs, int accumulate, int32_t* status,
+                      cudaStream_t s) {
   const int eb = elem_bytes(dtype);
   const WgradPlan w = plan_wgrad(Ci, Co, eb);
   WgradParams p;
@@ -543,6 +658,8 @@ static int wgrad_pass(const void* grad_out, const void* feats, const uint32_t* v
   p.vs_i = vs_i;
   p.vs_o = vs_o;
   p.seg = seg;
+  p.block_offsets = block_offsets;
+  plan_bands(n_out, n_in, n_pairs, Ci, Co, V, eb, w.kb, block_offsets != nullptr, &p.bands, &p.nblk, &p.band_blocks);
   p.partial = slabs;
   p.Co = Co, p.Ci = Ci, p.V = V;
   p.target_units = target_units(w, V, splitk);
@@ -557,8 +674,8 @@ static int wgrad_pass(const void* grad_out, const void* feats, const uint32_t* v
   const int64_t grid = max_units * w.co_groups * w.ci_tiles;
   if (grid > 0x7FFFFFFF) return FGB_E_SIZE;
   const auto launch = [&](auto kernel) -> cudaError_t {
-    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(w.smem));
-    if (e != cudaSuccess) return e;
+    static PerDeviceTable configured;  // one per kernel instance (the lambda is instantiated per kernel type)
+    if (ensure_dynamic_smem(configured, kernel, w.smem) != FGB_OK) return cudaErrorInvalidValue;
     kernel<<<static_cast<unsigned>(grid), kWgThreads, w.smem, s>>>(p);
     return cudaSuccess;
   };
@@ -585,17 +702,18 @@ static int wgrad_pass(const void* grad_out, const void* feats, const uint32_t* v
 }  // namespace fgb
 
 extern "C" int fgb_subm_conv_wgrad(const void* grad_out, const void* feats, const uint32_t* valid_signal_i,
-                                   const uint32_t* valid_signal_o, const uint32_t* valid_signal_seg, void* grad_weight,
-                                   float* grad_weight_f32, int64_t n, int64_t n_pairs, int Ci, int Co, int V, int dtype, int splitk,
-                                   void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
-  return fgb_sparse_conv_wgrad(grad_out, feats, valid_signal_i, valid_signal_o, valid_signal_seg, grad_weight, grad_weight_f32, n, n,
-                               n_pairs, Ci, Co, V, dtype, splitk, workspace, workspace_bytes, status, stream);
+                                   const uint32_t* valid_signal_o, const uint32_t* valid_signal_seg, const uint32_t* block_offsets,
+                                   void* grad_weight, float* grad_weight_f32, int64_t n, int64_t n_pairs, int Ci, int Co, int V,
+                                   int dtype, int splitk, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+  return fgb_sparse_conv_wgrad(grad_out, feats, valid_signal_i, valid_signal_o, valid_signal_seg, block_offsets, grad_weight,
+                               grad_weight_f32, n, n, n_pairs, Ci, Co, V, dtype, splitk, workspace, workspace_bytes, status, stream);
 }
 
 extern "C" int fgb_sparse_conv_wgrad(const void* grad_out, const void* feats, const uint32_t* valid_signal_i,
-                                     const uint32_t* valid_signal_o, const uint32_t* valid_signal_seg, void* grad_weight,
-                                     float* grad_weight_f32, int64_t n_out, int64_t n_in, int64_t n_pairs, int Ci, int Co, int V,
-                                     int dtype, int splitk, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+                                     const uint32_t* valid_signal_o, const uint32_t* valid_signal_seg, const uint32_t* block_offsets,
+                                     void* grad_weight, float* grad_weight_f32, int64_t n_out, int64_t n_in, int64_t n_pairs, int Ci,
+                                     int Co, int V, int dtype, int splitk, void* workspace, int64_t workspace_bytes, int32_t* status,
+                                     void* stream) {
   using namespace fgb;
   const int eb = elem_bytes(dtype);
   if (eb == 0) return FGB_E_DTYPE;
@@ -613,8 +731,8 @@ extern "C" int fgb_sparse_conv_wgrad(const void* grad_out, const void* feats, co
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* slabs = static_cast<float*>(workspace);
   if (dtype != FGB_F32_IEEE)
-    return wgrad_pass(grad_out, feats, valid_signal_i, valid_signal_o, valid_signal_seg, grad_weight, grad_weight_f32, n_pairs, Ci, Co, V,
-                      dtype, splitk, slabs, 0, status, s);
+    return wgrad_pass(grad_out, feats, valid_signal_i, valid_signal_o, valid_signal_seg, block_offsets, grad_weight, grad_weight_f32,
+                      n_out, n_in, n_pairs, Ci, Co, V, dtype, splitk, slabs, 0, status, s);
   // fp32-accurate: g_hi*x_hi + g_hi*x_lo + g_lo*x_hi, three passes adding into the fp32 output
   char* base = static_cast<char*>(workspace) + align256(int64_t(Ci) * V * Co * 4 * (int64_t(splitk) + 1));
   float* x_hi = reinterpret_cast<float*>(base);
@@ -629,8 +747,8 @@ extern "C" int fgb_sparse_conv_wgrad(const void* grad_out, const void* feats, co
   const float* ga[3] = {g_hi, g_hi, g_lo};
   const float* xa[3] = {x_hi, x_lo, x_hi};
   for (int pass = 0; pass < 3; ++pass) {
-    rc = wgrad_pass(ga[pass], xa[pass], valid_signal_i, valid_signal_o, valid_signal_seg, grad_weight, grad_weight_f32, n_pairs, Ci, Co,
-                    V, FGB_F32_TF32, splitk, slabs, pass > 0, status, s);
+    rc = wgrad_pass(ga[pass], xa[pass], valid_signal_i, valid_signal_o, valid_signal_seg, block_offsets, grad_weight, grad_weight_f32,
+                    n_out, n_in, n_pairs, Ci, Co, V, FGB_F32_TF32, splitk, slabs, pass > 0, status, s);
     if (rc != FGB_OK) return rc;
   }
   return FGB_OK;
@@ -757,4 +875,59 @@ extern "C" int fgb_cast_from_f32(const float* src, void* dst, int64_t count, int
       return FGB_E_DTYPE;
   }
   return launch_status();
+}
+
+// Host-side replay of the kernel's work split, for tests: which pairs each CTA of a wgrad launch would read.
+// seg and block_offsets are HOST arrays here.  For every unit u (offset-major, as the slabs are stored) and band b,
+// plan[(u * bands + b) * 3 + {0, 1, 2}] = first pair, k-blocks, end of the band in the pair list.  Returns the number
+// of units, or a negative code; *bands_out and *kb_out receive the band count and the pairs per k-block.
+extern "C" int fgb_wgrad_plan_host(const uint32_t* seg, const uint32_t* block_offsets, int64_t n_out, int64_t n_in, int Ci, int Co, int V,
+                                   int dtype, int splitk, uint32_t* plan, int64_t plan_capacity, int* bands_out, int* kb_out) {
+  using namespace fgb;
+  const int eb = elem_bytes(dtype == FGB_F32_IEEE ? FGB_F32_TF32 : dtype);
+  if (eb == 0) return FGB_E_DTYPE;
+  if (!seg || !plan || !bands_out || !kb_out) return FGB_E_NULL;
+  if (n_out < 0 || n_in < 0 || Ci <= 0 || Co <= 0 || V < 1 || V > 32 || splitk < 1 || splitk > 1024) return FGB_E_SIZE;
+  const WgradPlan w = plan_wgrad(Ci, Co, eb);
+  const uint32_t target = static_cast<uint32_t>(target_units(w, V, splitk));
+  const int64_t n_pairs = seg[V];
+  int bands = 1;
+  uint32_t nblk = 0, band_blocks = 0;
+  plan_bands(n_out, n_in, n_pairs, Ci, Co, V, eb, w.kb, block_offsets != nullptr, &bands, &nblk, &band_blocks);
+  // the kernel's bisection (wg_plan_unit_kb) with loops in place of warp reductions
+  uint32_t nk[32], hi = 1;
+  for (int v = 0; v < V; ++v) {
+    nk[v] = (seg[v + 1] - seg[v] + w.kb - 1) / w.kb;
+    if (nk[v] > hi) hi = nk[v];
+  }
+  uint32_t lo = 1;
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    uint32_t units = 0;
+    for (int v = 0; v < V; ++v) units += (nk[v] + mid - 1) / mid;
+    if (units <= target) hi = mid;
+    else lo = mid + 1;
+  }
+  const uint32_t unit_kb = lo;
+  int u = 0;
+  for (int v = 0; v < V; ++v) {
+    const uint32_t K = (nk[v] + unit_kb - 1) / unit_kb;
+    for (uint32_t k = 0; k < K; ++k, ++u) {
+      if (int64_t(u + 1) * bands * 3 > plan_capacity) return FGB_E_WORKSPACE;
+      uint32_t rot = 0;
+      for (int b = 0; b < bands; ++b) {
+        const uint32_t begin = wg_band_pos(seg, block_offsets, nblk, band_blocks, bands, v, b);
+        const uint32_t end = wg_band_pos(seg, block_offsets, nblk, band_blocks, bands, v, b + 1);
+        const uint32_t nkb = (end - begin + w.kb - 1) / w.kb;
+        uint32_t first = 0;
+        const uint32_t cnt = wg_band_share(nkb, K, k, rot, &first);
+        rot += nkb % K;
+        uint32_t* e = plan + (size_t(u) * bands + b) * 3;
+        e[0] = begin + first * w.kb, e[1] = cnt, e[2] = end;
+      }
+    }
+  }
+  *bands_out = bands;
+  *kb_out = w.kb;
+  return u;
 }

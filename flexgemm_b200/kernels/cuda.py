@@ -81,9 +81,57 @@ def check_status(device: torch.device) -> None:
     recorded a soft error."""
     word = status_word(device)
     code = int(word.item())
+    _status_pending.pop(_device_index(device), None)
     if code != 0:
         word.zero_()
         raise_for_status(code)
+
+
+def _device_index(device: torch.device) -> int:
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
+# device index -> (pinned host word, event recorded after the copy that fills it)
+_status_pending: Dict[int, tuple] = {}
+
+
+def poll_status(device: torch.device) -> None:
+    """Non-blocking look at the device status word, called by the conv wrappers
+    before they launch.
+
+    A kernel that hits a soft error (a bounded barrier wait that ran out, a full
+    hash table) records a code in the word and every later conv kernel on that
+    device returns at once while it is set, so the error must reach the caller:
+    this function queues a 4-byte copy of the word to pinned host memory and, on
+    a later call, once that copy has landed, looks at it.  A non-zero code clears
+    the word (so that the calls after the exception run normally) and raises
+    ``RuntimeError``.  Nothing here waits for the GPU; the error therefore
+    surfaces at the first conv call made after the device has reported it --
+    ``check_status`` is the synchronising variant."""
+    idx = _device_index(device)
+    entry = _status_pending.get(idx)
+    if entry is not None:
+        host, event = entry
+        if not event.query():
+            return  # the previous copy is still in flight: look again at the next call
+        code = int(host[0])
+        del _status_pending[idx]
+        if code != 0:
+            status_word(device).zero_()
+            raise_for_status(code)
+    else:
+        host = None
+    if host is None:
+        host = _status_host.get(idx)
+        if host is None:
+            host = _status_host[idx] = torch.zeros(1, dtype=torch.int32).pin_memory()
+    event = torch.cuda.Event()
+    host.copy_(status_word(device), non_blocking=True)
+    event.record(torch.cuda.current_stream(device))
+    _status_pending[idx] = (host, event)
+
+
+_status_host: Dict[int, torch.Tensor] = {}
 
 
 # --------------------------------------------------------------------------
@@ -325,6 +373,14 @@ def conv_tile_rows() -> int:
     return int(_cabi.lib().fgb_conv_tile_rows())
 
 
+def set_wgrad_row_bands(bands: int) -> int:
+    """Fix the number of row bands of the wgrad pair-list walk (0 = automatic); returns the previous setting."""
+    prev = _cabi.lib().fgb_wgrad_set_row_bands(int(bands))
+    if prev < 0:
+        _cabi.check(prev, "fgb_wgrad_set_row_bands")
+    return prev
+
+
 def set_conv_cta_limit(max_ctas: int) -> int:
     """Cap the CTAs (SMs) of the persistent fprop / dgrad kernels launched from now
     on (0 = no cap); returns the previous cap."""
@@ -338,11 +394,48 @@ def sm_count(device) -> int:
     return torch.cuda.get_device_properties(device).multi_processor_count
 
 
+def _channel_multiple(dtype: torch.dtype) -> int:
+    """Channel counts the kernels take directly: rows must be whole 16-byte pieces."""
+    return 16 // torch.empty(0, dtype=dtype).element_size()
+
+
+def _round_up(c: int, m: int) -> int:
+    return (c + m - 1) // m * m
+
+
+def _pad_last(t: Optional[torch.Tensor], width: int) -> Optional[torch.Tensor]:
+    """``t`` with its last dimension zero-padded to ``width`` (unchanged when it already has it)."""
+    if t is None or t.shape[-1] == width:
+        return t
+    out = t.new_zeros(*t.shape[:-1], width)
+    out[..., :t.shape[-1]] = t
+    return out
+
+
+def _pad_weight(weight_cvc: torch.Tensor, co_p: int, ci_p: int) -> torch.Tensor:
+    Co, V, Ci = weight_cvc.shape
+    if (Co, Ci) == (co_p, ci_p):
+        return weight_cvc
+    out = weight_cvc.new_zeros(co_p, V, ci_p)
+    out[:Co, :, :Ci] = weight_cvc
+    return out
+
+
 def conv_fprop(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks, order=None) -> torch.Tensor:
     """feats [N_in,Ci], weight_cvc [Co,V,Ci], neighbor_map [N_out,V] -> out [N_out,Co]
-    (N_in = N_out for a submanifold conv)."""
+    (N_in = N_out for a submanifold conv).  Channel counts that do not make the
+    rows whole 16-byte pieces (a first layer with Ci = 1, 3, 6 ...) are zero-padded
+    to the next multiple and the result is sliced back."""
     lib = _cabi.lib()
     dev = feats.device
+    m = _channel_multiple(feats.dtype)
+    if feats.shape[1] % m or weight_cvc.shape[0] % m:
+        Co = weight_cvc.shape[0]
+        ci_p, co_p = _round_up(feats.shape[1], m), _round_up(Co, m)
+        out = conv_fprop(_pad_last(feats, ci_p), _pad_weight(weight_cvc, co_p, ci_p), _pad_last(bias, co_p), neighbor_map, sorted_idx,
+                         masks, order)
+        return out[:, :Co].contiguous()
+    poll_status(dev)
     n_in, Ci = feats.shape
     n = neighbor_map.shape[0]
     Co, V, _ = weight_cvc.shape
@@ -376,6 +469,7 @@ def conv_fprop_fused(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks, o
         raise ValueError(f"Unsupported activation {activation!r}")
     lib = _cabi.lib()
     dev = feats.device
+    poll_status(dev)
     n, Ci = feats.shape
     assert neighbor_map.shape[0] == n, "the fused epilogue serves the submanifold conv (one output row per input row)"
     Co, V, _ = weight_cvc.shape
@@ -403,6 +497,13 @@ def conv_dgrad(grad_out, weight_cvc, neighbor_map, sorted_idx, masks, order=None
     it is the backward map [N_in, V] of a generic sparse conv (slot v)."""
     lib = _cabi.lib()
     dev = grad_out.device
+    m = _channel_multiple(grad_out.dtype)
+    if grad_out.shape[1] % m or weight_cvc.shape[2] % m:
+        Ci = weight_cvc.shape[2]
+        ci_p, co_p = _round_up(Ci, m), _round_up(grad_out.shape[1], m)
+        out = conv_dgrad(_pad_last(grad_out, co_p), _pad_weight(weight_cvc, co_p, ci_p), neighbor_map, sorted_idx, masks, order, mirror)
+        return out[:, :Ci].contiguous()
+    poll_status(dev)
     n_out, Co = grad_out.shape
     n = neighbor_map.shape[0]
     _, V, Ci = weight_cvc.shape
@@ -426,12 +527,21 @@ def conv_dgrad(grad_out, weight_cvc, neighbor_map, sorted_idx, masks, order=None
 
 
 def conv_wgrad(grad_out, feats, vs_i, vs_o, vs_seg, splitk: Optional[int] = None, want_f32: bool = False,
-               want_dtype: bool = True):
-    """-> (grad_weight [Co,V,Ci] in the feature dtype or None, fp32 copy or None)."""
+               want_dtype: bool = True, block_offsets: Optional[torch.Tensor] = None):
+    """-> (grad_weight [Co,V,Ci] in the feature dtype or None, fp32 copy or None).
+    ``block_offsets`` (the build's per-(offset, 256-row block) pair offsets) lets
+    the kernel walk all pair lists in row bands that the offsets share in L2."""
     lib = _cabi.lib()
     dev = feats.device
     n_in, Ci = feats.shape
     n_out, Co = grad_out.shape
+    m = _channel_multiple(feats.dtype)
+    if Ci % m or Co % m:
+        gw, gw32 = conv_wgrad(_pad_last(grad_out, _round_up(Co, m)), _pad_last(feats, _round_up(Ci, m)), vs_i, vs_o, vs_seg, splitk,
+                              want_f32, want_dtype, block_offsets)
+        return (gw[:Co, :, :Ci].contiguous() if gw is not None else None,
+                gw32[:Co, :, :Ci].contiguous() if gw32 is not None else None)
+    poll_status(dev)
     V = vs_seg.shape[0] - 1
     code = dtype_code(feats.dtype)
     if splitk is None:
@@ -444,12 +554,12 @@ def conv_wgrad(grad_out, feats, vs_i, vs_o, vs_seg, splitk: Optional[int] = None
                               "fgb_sparse_conv_workspace_bytes")
     ws = workspace(dev, "wgrad", nbytes)
     if n_in == n_out:
-        rc = lib.fgb_subm_conv_wgrad(_ptr(grad_out), _ptr(feats), _ptr(vs_i), _ptr(vs_o), vs_seg.data_ptr(), _ptr(gw), _ptr(gw32),
+        rc = lib.fgb_subm_conv_wgrad(_ptr(grad_out), _ptr(feats), _ptr(vs_i), _ptr(vs_o), vs_seg.data_ptr(), _ptr(block_offsets), _ptr(gw), _ptr(gw32),
                                      n_out, int(vs_i.shape[0]), Ci, Co, V, code, int(splitk), ws.data_ptr(), ws.numel() * 8,
                                      status_word(dev).data_ptr(), _stream(dev))
         _cabi.check(rc, "fgb_subm_conv_wgrad")
     else:
-        rc = lib.fgb_sparse_conv_wgrad(_ptr(grad_out), _ptr(feats), _ptr(vs_i), _ptr(vs_o), vs_seg.data_ptr(), _ptr(gw),
+        rc = lib.fgb_sparse_conv_wgrad(_ptr(grad_out), _ptr(feats), _ptr(vs_i), _ptr(vs_o), vs_seg.data_ptr(), _ptr(block_offsets), _ptr(gw),
                                        _ptr(gw32), n_out, n_in, int(vs_i.shape[0]), Ci, Co, V, code, int(splitk), ws.data_ptr(),
                                        ws.numel() * 8, status_word(dev).data_ptr(), _stream(dev))
         _cabi.check(rc, "fgb_sparse_conv_wgrad")

@@ -195,6 +195,7 @@ class SparseConv3dFunction(Function):
             cache["valid_signal_seg"] = seg
             cache["valid_signal_i"] = vs_i
             cache["valid_signal_o"] = vs_o
+            cache["pair_block_offsets"] = built["block_offsets"]   # lets wgrad walk the pair lists in shared row bands
             if any(s != 1 for s in stride) or is_out_coords_given:
                 cache._ensure_bwd_order()   # the cases in which the reference also sorts the backward map
         else:
@@ -293,7 +294,8 @@ class SparseConv3dFunction(Function):
                                                      mirror=False)
             if weight.requires_grad:
                 gw, _ = kernels.cuda.conv_wgrad(grad_output, feats, neighbor_cache["valid_signal_i"], neighbor_cache["valid_signal_o"],
-                                                neighbor_cache["valid_signal_seg"])
+                                                neighbor_cache["valid_signal_seg"],
+                                                block_offsets=getattr(neighbor_cache, "pair_block_offsets", None))
                 grad_weight = gw.reshape(Co, Kw, Kh, Kd, Ci)
             if join is not None:
                 join()

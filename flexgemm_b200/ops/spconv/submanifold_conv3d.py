@@ -116,6 +116,9 @@ class SubMConv3dFunction(Function):
             cache["valid_signal_seg"] = seg
             cache["valid_signal_i"] = vs_i
             cache["valid_signal_o"] = vs_o
+            # not part of the reference's cache: where each 256-row block starts in every offset's pair list, which
+            # lets wgrad walk all lists in row bands that share L2
+            cache["pair_block_offsets"] = built["block_offsets"]
         else:
             # inference cache: nothing needs the host, so nothing synchronises; an
             # overflowing table would show in this word, readable at any later time
@@ -207,7 +210,8 @@ class SubMConv3dFunction(Function):
                                                      neighbor_cache.tile_masks(tile), neighbor_cache.block_order(tile))
             if weight.requires_grad:
                 gw, _ = kernels.cuda.conv_wgrad(grad_output, feats, neighbor_cache["valid_signal_i"], neighbor_cache["valid_signal_o"],
-                                                neighbor_cache["valid_signal_seg"])
+                                                neighbor_cache["valid_signal_seg"],
+                                                block_offsets=getattr(neighbor_cache, "pair_block_offsets", None))
                 grad_weight = gw.reshape(Co, Kw, Kh, Kd, Ci)
             if join is not None:
                 join()

@@ -81,7 +81,7 @@ def _cuda_local_grads(grad_out, feats, cache, weight_cvc, has_bias):
     """fp32 weight / bias gradient of the local shard through the CUDA kernels."""
     from .kernels import cuda as K
     _, gw32 = K.conv_wgrad(grad_out, feats, cache["valid_signal_i"], cache["valid_signal_o"], cache["valid_signal_seg"],
-                           want_f32=True, want_dtype=False)
+                           want_f32=True, want_dtype=False, block_offsets=getattr(cache, "pair_block_offsets", None))
     gb32 = K.bias_grad(grad_out, want_f32=True, want_dtype=False)[1] if has_bias else None
     return gw32, gb32
 

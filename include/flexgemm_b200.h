@@ -53,6 +53,11 @@ extern "C" {
 const char* fgb_version(void);
 const char* fgb_error_string(int code);
 
+/* Host-only self-test of the per-device caches the launch code keeps (SM count,
+ * dynamic shared-memory limit per kernel and device); touches no GPU.  Returns 0
+ * or the number of the failed expectation.  (No counterpart in the reference.) */
+int fgb_selftest_device_tables(void);
+
 /* ------------------------------------------------------------------------
  * Hash table + neighbour map
  * --------------------------------------------------------------------- */
@@ -238,15 +243,38 @@ int fgb_wgrad_default_splitk(int64_t n_pairs, int Ci, int Co, int V, int dtype);
  * lists (valid_signal_seg[V]).  grad_weight (element type `dtype`) and/or
  * grad_weight_f32 may be null; the fp32 copy is what a multi-GPU caller hands
  * to its all-reduce.
+ * block_offsets (may be null): the [V, nblk] array written by
+ * fgb_subm_build_neighbor_map.  With it the lists of all offsets are cut at the
+ * same output rows into row bands, and every CTA walks its share of band after
+ * band, so that the whole launch reads one band of rows of grad_out and feats at
+ * a time and the 27 offsets share it in L2 instead of each streaming both
+ * matrices from HBM; without it every CTA walks one contiguous piece of one
+ * list.  The result does not depend on it beyond the order of fp32 additions.
  * Stands in for sparse_submanifold_conv_bwd_weight_masked_implicit_gemm_splitk
  * (…/sparse_submanifold_conv_bwd_masked_implicit_gemm_splitk.py:107-182, 274-317). */
 int fgb_subm_conv_wgrad(const void* grad_out, const void* feats,
                         const uint32_t* valid_signal_i, const uint32_t* valid_signal_o,
-                        const uint32_t* valid_signal_seg,
+                        const uint32_t* valid_signal_seg, const uint32_t* block_offsets,
                         void* grad_weight, float* grad_weight_f32,
                         int64_t n, int64_t n_pairs, int Ci, int Co, int V, int dtype, int splitk,
                         void* workspace, int64_t workspace_bytes,
                         int32_t* status, void* stream);
+
+/* Number of row bands fgb_*_conv_wgrad cuts the pair lists into when it is given
+ * block_offsets: 0 = chosen from the sizes (bands of about 8 MB of rows), 1 .. 64
+ * = fixed.  Returns the previous value.  Process-wide tuning knob; read at launch. */
+int fgb_wgrad_set_row_bands(int bands);
+
+/* Host-side replay of how a wgrad launch splits the pair lists among its CTAs, for
+ * tests (no GPU involved; seg and block_offsets are HOST arrays here, block_offsets
+ * may be null).  For unit u (offset-major) and band b,
+ * plan[(u * bands + b) * 3 + 0 / 1 / 2] = first pair / number of k-blocks / end of
+ * the band in the pair list; a k-block is *kb_out consecutive pairs, cut at the
+ * band's end.  Returns the number of units or a negative code.  (No counterpart in
+ * the reference.) */
+int fgb_wgrad_plan_host(const uint32_t* seg, const uint32_t* block_offsets, int64_t n_out, int64_t n_in,
+                        int Ci, int Co, int V, int dtype, int splitk,
+                        uint32_t* plan, int64_t plan_capacity, int* bands_out, int* kb_out);
 
 /* grad_bias[c] = sum_r grad_out[r, c] accumulated in fp32; writes grad_bias
  * (element type `dtype`) and/or grad_bias_f32, either may be null.
@@ -371,7 +399,7 @@ int fgb_sparse_conv_dgrad(const void* grad_out, const void* weight,
                           void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
 int fgb_sparse_conv_wgrad(const void* grad_out, const void* feats,
                           const uint32_t* valid_signal_i, const uint32_t* valid_signal_o,
-                          const uint32_t* valid_signal_seg,
+                          const uint32_t* valid_signal_seg, const uint32_t* block_offsets,
                           void* grad_weight, float* grad_weight_f32,
                           int64_t n_out, int64_t n_in, int64_t n_pairs, int Ci, int Co, int V, int dtype, int splitk,
                           void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);

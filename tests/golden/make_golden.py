@@ -67,7 +67,9 @@ def ref_map(spconv, coords, shape, ksize, dil):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FLEXGEMM_REFERENCE")
+    if not ref_root:
+        raise SystemExit("usage: %s <path to the FlexGEMM source tree>  (or set FLEXGEMM_REFERENCE)" % os.path.basename(__file__))
     spconv = load_reference(ref_root)
     fn = spconv.SubMConv3dFunction
     torch.flip = _flip_u32

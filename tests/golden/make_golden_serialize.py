@@ -15,7 +15,9 @@ ROOT = os.path.abspath(os.path.join(HERE, "..", ".."))
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FLEXGEMM_REFERENCE")
+    if not ref_root:
+        raise SystemExit("usage: %s <path to the FlexGEMM source tree>  (or set FLEXGEMM_REFERENCE)" % os.path.basename(__file__))
     exe = os.path.join(ROOT, "oracle", "_ref", "ref_serialize")
     os.makedirs(os.path.dirname(exe), exist_ok=True)
     subprocess.run(["nvcc", "-O1", "-I" + os.path.join(ref_root, "flex_gemm", "kernels", "cuda"), "-o", exe,

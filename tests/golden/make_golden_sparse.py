@@ -45,7 +45,9 @@ def u32(t):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FLEXGEMM_REFERENCE")
+    if not ref_root:
+        raise SystemExit("usage: %s <path to the FlexGEMM source tree>  (or set FLEXGEMM_REFERENCE)" % os.path.basename(__file__))
     spconv = load_reference(ref_root)
     fn = spconv.SparseConv3dFunction
     rng = np.random.default_rng(11)

@@ -37,6 +37,11 @@ def test_version_and_errors(lib):
         _cabi.check(1001, "x")
 
 
+def test_per_device_launch_caches(lib):
+    """SM count and shared-memory limits are remembered per device, not per process."""
+    assert lib.fgb_selftest_device_tables() == 0
+
+
 def test_size_queries(lib):
     assert lib.fgb_hash_table_bytes(1000, 32) == 8000
     assert lib.fgb_hash_table_bytes(1000, 64) == 12000
@@ -64,7 +69,8 @@ def test_argument_validation_without_launch(lib):
     assert lib.fgb_subm_conv_fprop(0, 0, 0, 0, 0, 0, 0, 0, 10, 64, 64, 27, _cabi.F16, 0, 0, 0, 0) == -1
     assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 60, 64, 27, _cabi.F16, 256, 256, 0, 0) == -4  # Ci % 8
     assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 64, 64, 27, 7, 256, 256, 0, 0) == -3
-    assert lib.fgb_subm_conv_wgrad(16, 16, 16, 16, 16, 16, 0, 10, 100, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -5  # workspace
+    assert lib.fgb_subm_conv_wgrad(16, 16, 16, 16, 16, 0, 16, 0, 10, 100, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -5  # workspace
+    assert lib.fgb_wgrad_set_row_bands(65) == -2 and lib.fgb_wgrad_set_row_bands(0) == 0
 
 
 def test_sparse_conv_entry_points_validate_without_launch(lib):
@@ -87,7 +93,7 @@ def test_sparse_conv_entry_points_validate_without_launch(lib):
     assert lib.fgb_sparse_conv_workspace_bytes(1, 1000, 500, 64, 32, 27, _cabi.F32_IEEE, 1) == \
         256 + 64 * 32 * 27 * 4 + 64 * 32 * 27 * 3 * 4 + 1000 * 3 * 32 * 4
     assert lib.fgb_sparse_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 20, 60, 64, 27, _cabi.F16, 256, 256, 0, 0) == -4  # Ci % 8
-    assert lib.fgb_sparse_conv_wgrad(16, 16, 16, 16, 16, 16, 0, 10, 20, 500, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -2  # pairs > n_out*V
+    assert lib.fgb_sparse_conv_wgrad(16, 16, 16, 16, 16, 0, 16, 0, 10, 20, 500, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -2  # pairs > n_out*V
 
 
 def test_fused_fprop_validates_without_launch(lib):

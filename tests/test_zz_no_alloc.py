@@ -62,6 +62,34 @@ def test_noalloc_bias_grad_matches_workspace_entry_twice(dtype, code):
         assert torch.equal(got, want) and torch.equal(got32, want32)
 
 
+@pytest.mark.parametrize("dtype,code", [(torch.float16, _cabi.F16), (torch.float32, _cabi.F32_TF32)])
+def test_noalloc_at_the_channel_limit_allocates_nothing(dtype, code):
+    """Co = 2048 with at least 592 rows uses the whole built-in buffer (16-bit rows
+    take the vector path of the partial-sum kernel, fp32 rows the one-thread-per-
+    column path), and the call itself must leave the amount of free device memory
+    unchanged: outputs are made first, then the driver's own figure is read on both
+    sides of the call."""
+    lib = _cabi.lib()
+    co = lib.fgb_noalloc_max_channels()
+    n = 1500
+    g = torch.randn(n, co, generator=torch.Generator().manual_seed(23)).to(dtype).to(DEV)
+    want, want32 = _reference_entry(g, code)
+    _noalloc_entry(g, code)                               # first call on this device may resolve the buffer's address
+    gb = torch.empty(co, dtype=dtype, device=DEV)
+    gb32 = torch.empty(co, dtype=torch.float32, device=DEV)
+    stream = torch.cuda.current_stream(DEV).cuda_stream
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(DEV)
+    rc = lib.fgb_subm_conv_bias_grad_noalloc(g.data_ptr(), gb.data_ptr(), gb32.data_ptr(), n, co, code, stream)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(DEV)
+    _cabi.check(rc, "fgb_subm_conv_bias_grad_noalloc")
+    assert free_after == free_before
+    assert torch.equal(gb, want) and torch.equal(gb32, want32)
+    exact = g.double().sum(0)
+    assert (gb32.double() - exact).abs().max().item() <= 1e-2 * exact.abs().max().item()
+
+
 def test_noalloc_rejects_sizes_beyond_the_builtin_buffer():
     lib = _cabi.lib()
     limit = lib.fgb_noalloc_max_channels()
