@@ -527,15 +527,21 @@ def conv_dgrad(grad_out, weight_cvc, neighbor_map, sorted_idx, masks, order=None
 
 
 def conv_wgrad(grad_out, feats, vs_i, vs_o, vs_seg, splitk: Optional[int] = None, want_f32: bool = False,
-               want_dtype: bool = True, block_offsets: Optional[torch.Tensor] = None):
+               want_dtype: bool = True, block_offsets: Optional[torch.Tensor] = None, out_f32: Optional[torch.Tensor] = None):
     """-> (grad_weight [Co,V,Ci] in the feature dtype or None, fp32 copy or None).
     ``block_offsets`` (the build's per-(offset, 256-row block) pair offsets) lets
-    the kernel walk all pair lists in row bands that the offsets share in L2."""
+    the kernel walk all pair lists in row bands that the offsets share in L2.
+    ``out_f32`` (fp32, Co*V*Ci elements, contiguous) receives the fp32 copy in
+    place -- e.g. a slice of the buffer a multi-GPU caller all-reduces."""
     lib = _cabi.lib()
     dev = feats.device
     n_in, Ci = feats.shape
     n_out, Co = grad_out.shape
     m = _channel_multiple(feats.dtype)
+    if (Ci % m or Co % m) and out_f32 is not None:
+        gw, gw32 = conv_wgrad(grad_out, feats, vs_i, vs_o, vs_seg, splitk, True, want_dtype, block_offsets)
+        out_f32.view(gw32.shape).copy_(gw32)
+        return gw, out_f32.view(gw32.shape)
     if Ci % m or Co % m:
         gw, gw32 = conv_wgrad(_pad_last(grad_out, _round_up(Co, m)), _pad_last(feats, _round_up(Ci, m)), vs_i, vs_o, vs_seg, splitk,
                               want_f32, want_dtype, block_offsets)
@@ -549,7 +555,11 @@ def conv_wgrad(grad_out, feats, vs_i, vs_o, vs_seg, splitk: Optional[int] = None
         if splitk < 1:
             _cabi.check(splitk, "fgb_wgrad_default_splitk")
     gw = torch.empty((Co, V, Ci), dtype=feats.dtype, device=dev) if want_dtype else None
-    gw32 = torch.empty((Co, V, Ci), dtype=torch.float32, device=dev) if want_f32 else None
+    if out_f32 is not None:
+        assert out_f32.dtype == torch.float32 and out_f32.numel() == Co * V * Ci and out_f32.is_contiguous()
+        gw32 = out_f32.view(Co, V, Ci)
+    else:
+        gw32 = torch.empty((Co, V, Ci), dtype=torch.float32, device=dev) if want_f32 else None
     nbytes = _cabi.check_size(lib.fgb_sparse_conv_workspace_bytes(2, n_out, n_in, Ci, Co, V, code, splitk),
                               "fgb_sparse_conv_workspace_bytes")
     ws = workspace(dev, "wgrad", nbytes)
@@ -567,13 +577,18 @@ def conv_wgrad(grad_out, feats, vs_i, vs_o, vs_seg, splitk: Optional[int] = None
     return gw, gw32
 
 
-def bias_grad(grad_out, want_f32: bool = False, want_dtype: bool = True):
+def bias_grad(grad_out, want_f32: bool = False, want_dtype: bool = True, out_f32: Optional[torch.Tensor] = None):
+    """-> (grad_bias [Co] in the feature dtype or None, fp32 copy or None); ``out_f32`` receives the fp32 copy in place."""
     lib = _cabi.lib()
     dev = grad_out.device
     n, Co = grad_out.shape
     code = dtype_code(grad_out.dtype)
     gb = torch.empty(Co, dtype=grad_out.dtype, device=dev) if want_dtype else None
-    gb32 = torch.empty(Co, dtype=torch.float32, device=dev) if want_f32 else None
+    if out_f32 is not None:
+        assert out_f32.dtype == torch.float32 and out_f32.shape == (Co,) and out_f32.is_contiguous()
+        gb32 = out_f32
+    else:
+        gb32 = torch.empty(Co, dtype=torch.float32, device=dev) if want_f32 else None
     nbytes = _cabi.check_size(lib.fgb_bias_grad_workspace_bytes(Co), "fgb_bias_grad_workspace_bytes")
     ws = workspace(dev, "bias", nbytes)
     rc = lib.fgb_subm_conv_bias_grad(_ptr(grad_out), _ptr(gb), _ptr(gb32), n, Co, code, ws.data_ptr(), ws.numel() * 8, _stream(dev))
@@ -585,7 +600,7 @@ def bias_grad(grad_out, want_f32: bool = False, want_dtype: bool = True):
 _side_streams: Dict[int, "torch.cuda.Stream"] = {}
 
 
-def bias_grad_overlapped(grad_out, want_f32: bool = False, want_dtype: bool = True):
+def bias_grad_overlapped(grad_out, want_f32: bool = False, want_dtype: bool = True, out_f32: Optional[torch.Tensor] = None):
     """Starts the bias gradient on a side stream so that it runs in the shadow of
     the persistent conv kernels (which hold one CTA per SM but leave room for the
     small reduction CTAs), and returns ``(grad_bias, grad_bias_f32, join)``: call
@@ -599,8 +614,10 @@ def bias_grad_overlapped(grad_out, want_f32: bool = False, want_dtype: bool = Tr
         side = _side_streams[idx] = torch.cuda.Stream(device=dev)
     side.wait_stream(cur)                  # grad_out is ready once the launching stream gets here
     with torch.cuda.stream(side):
-        gb, gb32 = bias_grad(grad_out, want_f32=want_f32, want_dtype=want_dtype)
+        gb, gb32 = bias_grad(grad_out, want_f32=want_f32, want_dtype=want_dtype, out_f32=out_f32)
     grad_out.record_stream(side)
+    if out_f32 is not None:
+        out_f32.record_stream(side)
 
     def join():
         cur.wait_stream(side)

@@ -77,15 +77,6 @@ def local_shard(coords: torch.Tensor, feats: Optional[torch.Tensor], shape, rank
 ALLREDUCE_SMS = int(os.environ.get("FGB_ALLREDUCE_SMS", "0"))
 
 
-def _cuda_local_grads(grad_out, feats, cache, weight_cvc, has_bias):
-    """fp32 weight / bias gradient of the local shard through the CUDA kernels."""
-    from .kernels import cuda as K
-    _, gw32 = K.conv_wgrad(grad_out, feats, cache["valid_signal_i"], cache["valid_signal_o"], cache["valid_signal_seg"],
-                           want_f32=True, want_dtype=False, block_offsets=getattr(cache, "pair_block_offsets", None))
-    gb32 = K.bias_grad(grad_out, want_f32=True, want_dtype=False)[1] if has_bias else None
-    return gw32, gb32
-
-
 def allreduce_param_grads(gw32: torch.Tensor, gb32: Optional[torch.Tensor], group=None, async_op: bool = False):
     """Sum the fp32 weight (and bias) gradient over the ranks with a single
     all-reduce of one flat buffer; returns views of the reduced buffer (and,
@@ -116,14 +107,23 @@ def sharded_backward(grad_out: torch.Tensor, feats: torch.Tensor, cache, weight:
     grad_in = None
     if local_grads is None:
         from .kernels import cuda as K
-        gb32, join = None, None
+        # One fp32 buffer [Co*V*Ci (+ Co)] is what travels: the split-K reduction and the bias reduction write their
+        # fp32 results straight into it, NCCL sums it in place, and one cast kernel turns all of it into the weight dtype.
+        nw = Co * V * Ci
+        flat = torch.empty(nw + (Co if bias is not None else 0), dtype=torch.float32, device=grad_out.device)
+        gw32 = flat[:nw].view(Co, V, Ci)
+        gb32 = flat[nw:] if bias is not None else None
+        join = None
         if bias is not None:  # small reduction: runs beside the conv kernels on a side stream
-            _, gb32, join = K.bias_grad_overlapped(grad_out, want_f32=True, want_dtype=False)
+            _, _, join = K.bias_grad_overlapped(grad_out, want_f32=True, want_dtype=False, out_f32=gb32)
         # parameter gradients first, so that their all-reduce travels while the input gradient is computed
-        gw32, _ = _cuda_local_grads(grad_out, feats, cache, w, False)
+        K.conv_wgrad(grad_out, feats, cache["valid_signal_i"], cache["valid_signal_o"], cache["valid_signal_seg"], want_f32=True,
+                     want_dtype=False, block_offsets=getattr(cache, "pair_block_offsets", None), out_f32=flat[:nw])
         if join is not None:
             join()
-        gw32, gb32, work = allreduce_param_grads(gw32, gb32, group, async_op=True)
+        work = None
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=True)
         if want_input_grad:
             tile = K.conv_tile_rows()
             # the dgrad CTAs fill their SMs: leave the all-reduce a few, or it would only start when dgrad ends
@@ -137,6 +137,13 @@ def sharded_backward(grad_out: torch.Tensor, feats: torch.Tensor, cache, weight:
                     K.set_conv_cta_limit(prev)
         if work is not None:
             work.wait()
+        if weight.dtype != torch.float32:
+            cast = K.cast_from_f32(flat, weight.dtype)   # weight and bias gradient in one launch
+            gw = cast[:nw].view(Co, V, Ci)
+            gb = cast[nw:] if bias is not None else None
+        else:
+            gw, gb = gw32, gb32
+        return grad_in, gw.reshape(Co, Kw, Kh, Kd, Ci), gb
     else:
         grad_in, gw32, gb32 = local_grads(grad_out, feats, cache, w, bias is not None)
         gw32, gb32 = allreduce_param_grads(gw32, gb32, group)
