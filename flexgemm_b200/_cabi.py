@@ -45,6 +45,11 @@ _PROTOTYPES = {
     "fgb_cast_from_f32": (c_int, [_P, _P, c_int64, c_int, _P]),
     "fgb_hash_insert_3d_idx_as_val": (c_int, [_P, c_int64, c_int, c_int, c_int, _P, c_int64, c_int, _P, _P]),
     "fgb_hash_lookup_3d": (c_int, [_P, c_int64, c_int, c_int, c_int, _P, c_int64, c_int, _P, _P]),
+    "fgb_hashmap_insert": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, c_int64, _P, _P]),
+    "fgb_hashmap_lookup": (c_int, [_P, _P, c_int64, c_int, c_int, _P, c_int64, _P, _P]),
+    "fgb_hashmap_insert_3d": (c_int, [_P, _P, c_int64, c_int, c_int, _P, _P, c_int64, c_int, c_int, c_int, _P, _P]),
+    "fgb_hashmap_insert_3d_idx_as_val": (c_int, [_P, _P, c_int64, c_int, c_int, _P, c_int64, c_int, c_int, c_int, _P, _P]),
+    "fgb_hashmap_lookup_3d": (c_int, [_P, _P, c_int64, c_int, c_int, _P, c_int64, c_int, c_int, c_int, _P, _P]),
     "fgb_grid_sample_neighbor_map": (c_int, [_P, c_int64, c_int64, c_int, c_int, c_int, _P, c_int64, c_int, c_int, _P, _P, _P]),
     "fgb_indice_weighted_sum_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int, c_int, _P]),
     "fgb_indice_weighted_sum_bwd": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, _P]),

@@ -640,8 +640,8 @@ def cast_from_f32(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 # --------------------------------------------------------------------------
 # generic table use and grid sample
 # --------------------------------------------------------------------------
-def hashmap_insert_3d_idx_as_val(table: torch.Tensor, key_bits: int, slots: int, coords: torch.Tensor, W: int, H: int, D: int) -> torch.Tensor:
-    """Clears ``table`` and inserts ``coords[i] -> i``; returns this call's device status word."""
+def table_insert_3d_idx_as_val(table: torch.Tensor, key_bits: int, slots: int, coords: torch.Tensor, W: int, H: int, D: int) -> torch.Tensor:
+    """The library's packed table: clears ``table`` and inserts ``coords[i] -> i``; returns this call's device status word."""
     _require_cuda(coords, "coords")
     dev = coords.device
     status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -652,13 +652,113 @@ def hashmap_insert_3d_idx_as_val(table: torch.Tensor, key_bits: int, slots: int,
     return status
 
 
-def hashmap_lookup_3d(table: torch.Tensor, key_bits: int, slots: int, query_coords: torch.Tensor, W: int, H: int, D: int) -> torch.Tensor:
-    """uint32 [M]: row stored for each (b, x, y, z) query row, 0xffffffff where absent."""
+def table_lookup_3d(table: torch.Tensor, key_bits: int, slots: int, query_coords: torch.Tensor, W: int, H: int, D: int) -> torch.Tensor:
+    """The library's packed table: uint32 [M], row stored for each (b, x, y, z) query row, 0xffffffff where absent."""
     dev = query_coords.device
     out = torch.empty(query_coords.shape[0], dtype=torch.uint32, device=dev)
     rc = _cabi.lib().fgb_hash_lookup_3d(_ptr(query_coords), query_coords.shape[0], int(W), int(H), int(D), table.data_ptr(), int(slots),
                                         int(key_bits), _ptr(out), _stream(dev))
     _cabi.check(rc, "fgb_hash_lookup_3d")
+    _count(1)
+    return out
+
+
+# The generic hash map in the reference's own layout and call shapes
+# (flex_gemm/kernels/cuda/hash/hash.cu; bound in ext.cpp:12-16): a key tensor
+# (uint32 / uint64, empty = all ones) and a value tensor (uint32 / uint64).
+_BITS = {torch.uint32: 32, torch.uint64: 64}
+
+
+def _hashmap_args(hashmap_keys: torch.Tensor, hashmap_values: torch.Tensor):
+    _require_cuda(hashmap_keys, "hashmap_keys")
+    if hashmap_keys.dtype not in _BITS or hashmap_values.dtype not in _BITS:
+        raise RuntimeError("Unsupported data type")       # the reference's TORCH_CHECK message
+    if hashmap_keys.shape != hashmap_values.shape or hashmap_keys.dim() != 1:
+        raise RuntimeError("hashmap_keys and hashmap_values must be 1-D tensors of the same length")
+    return hashmap_keys.shape[0], _BITS[hashmap_keys.dtype], _BITS[hashmap_values.dtype]
+
+
+def _hashmap_status(dev, status: torch.Tensor) -> None:
+    raise_for_status(int(status.item()))
+
+
+def hashmap_insert(hashmap_keys: torch.Tensor, hashmap_values: torch.Tensor, keys: torch.Tensor, values: torch.Tensor) -> None:
+    """Insert ``keys[i] -> values[i]`` (hash.cu:60-92).  Synchronises to report a full table."""
+    slots, kb, vb = _hashmap_args(hashmap_keys, hashmap_values)
+    if keys.dtype != hashmap_keys.dtype:
+        raise RuntimeError(f"Keys must be {str(hashmap_keys.dtype).split('.')[-1]}")
+    if values.dtype != hashmap_values.dtype:
+        raise RuntimeError(f"Values must be {str(hashmap_values.dtype).split('.')[-1]}")
+    dev = hashmap_keys.device
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    keys, values = keys.contiguous(), values.contiguous()
+    rc = _cabi.lib().fgb_hashmap_insert(hashmap_keys.data_ptr(), hashmap_values.data_ptr(), slots, kb, vb, _ptr(keys), _ptr(values),
+                                        keys.shape[0], status.data_ptr(), _stream(dev))
+    _cabi.check(rc, "fgb_hashmap_insert")
+    _count(1)
+    _hashmap_status(dev, status)
+
+
+def hashmap_lookup(hashmap_keys: torch.Tensor, hashmap_values: torch.Tensor, keys: torch.Tensor) -> torch.Tensor:
+    """Values of ``keys`` (all ones where absent), in the value dtype (hash.cu:139-175)."""
+    slots, kb, vb = _hashmap_args(hashmap_keys, hashmap_values)
+    if keys.dtype != hashmap_keys.dtype:
+        raise RuntimeError(f"Keys must be {str(hashmap_keys.dtype).split('.')[-1]}")
+    dev = hashmap_keys.device
+    keys = keys.contiguous()
+    out = torch.empty(keys.shape[0], dtype=hashmap_values.dtype, device=dev)
+    rc = _cabi.lib().fgb_hashmap_lookup(hashmap_keys.data_ptr(), hashmap_values.data_ptr(), slots, kb, vb, _ptr(keys), keys.shape[0],
+                                        _ptr(out), _stream(dev))
+    _cabi.check(rc, "fgb_hashmap_lookup")
+    _count(1)
+    return out
+
+
+def hashmap_insert_3d(hashmap_keys: torch.Tensor, hashmap_values: torch.Tensor, coords: torch.Tensor, values: torch.Tensor,
+                      W: int, H: int, D: int) -> None:
+    """Insert ``coords[i] (b, x, y, z) -> values[i]`` under the flat index (hash.cu:237-270)."""
+    slots, kb, vb = _hashmap_args(hashmap_keys, hashmap_values)
+    if coords.dtype != torch.int32:
+        raise RuntimeError("Coords must be int32")
+    if values.dtype != hashmap_values.dtype:
+        raise RuntimeError(f"Values must be {str(hashmap_values.dtype).split('.')[-1]}")
+    dev = hashmap_keys.device
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    coords, values = coords.contiguous(), values.contiguous()
+    rc = _cabi.lib().fgb_hashmap_insert_3d(hashmap_keys.data_ptr(), hashmap_values.data_ptr(), slots, kb, vb, _ptr(coords), _ptr(values),
+                                           coords.shape[0], int(W), int(H), int(D), status.data_ptr(), _stream(dev))
+    _cabi.check(rc, "fgb_hashmap_insert_3d")
+    _count(1)
+    _hashmap_status(dev, status)
+
+
+def hashmap_insert_3d_idx_as_val(hashmap_keys: torch.Tensor, hashmap_values: torch.Tensor, coords: torch.Tensor,
+                                 W: int, H: int, D: int) -> None:
+    """Insert ``coords[i] -> i`` (hash.cu:425-449)."""
+    slots, kb, vb = _hashmap_args(hashmap_keys, hashmap_values)
+    if coords.dtype != torch.int32:
+        raise RuntimeError("Coords must be int32")
+    dev = hashmap_keys.device
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    coords = coords.contiguous()
+    rc = _cabi.lib().fgb_hashmap_insert_3d_idx_as_val(hashmap_keys.data_ptr(), hashmap_values.data_ptr(), slots, kb, vb, _ptr(coords),
+                                                      coords.shape[0], int(W), int(H), int(D), status.data_ptr(), _stream(dev))
+    _cabi.check(rc, "fgb_hashmap_insert_3d_idx_as_val")
+    _count(1)
+    _hashmap_status(dev, status)
+
+
+def hashmap_lookup_3d(hashmap_keys: torch.Tensor, hashmap_values: torch.Tensor, coords: torch.Tensor, W: int, H: int, D: int) -> torch.Tensor:
+    """Values stored for the (b, x, y, z) rows of ``coords`` (all ones where absent or outside the grid; hash.cu:336-365)."""
+    slots, kb, vb = _hashmap_args(hashmap_keys, hashmap_values)
+    if coords.dtype != torch.int32:
+        raise RuntimeError("Coords must be int32")
+    dev = hashmap_keys.device
+    coords = coords.contiguous()
+    out = torch.empty(coords.shape[0], dtype=hashmap_values.dtype, device=dev)
+    rc = _cabi.lib().fgb_hashmap_lookup_3d(hashmap_keys.data_ptr(), hashmap_values.data_ptr(), slots, kb, vb, _ptr(coords), coords.shape[0],
+                                           int(W), int(H), int(D), _ptr(out), _stream(dev))
+    _cabi.check(rc, "fgb_hashmap_lookup_3d")
     _count(1)
     return out
 

@@ -25,8 +25,8 @@ def _table_for(coords: torch.Tensor, shape):
     C, W, H, D = [int(s) for s in shape[-4:]]
     n = coords.shape[0]
     slots = max(int(grid_sample.HASHMAP_RATIO * n), n, 1)
-    table, key_bits = utils.init_hashmap(shape, slots, coords.device)
-    status = kernels.cuda.hashmap_insert_3d_idx_as_val(table, key_bits, slots, coords.int().contiguous(), W, H, D)
+    table, key_bits = utils.init_table(shape, slots, coords.device)
+    status = kernels.cuda.table_insert_3d_idx_as_val(table, key_bits, slots, coords.int().contiguous(), W, H, D)
     return table, key_bits, slots, status, (W, H, D)
 
 

@@ -173,7 +173,7 @@ class SparseConv3dFunction(Function):
         assert V <= 32, "Currently, the max kernel volume is 32 because kernel mask is encoded as uint32"
         m = coords.shape[0]
         slots = max(int(spconv.HASHMAP_RATIO * m), m, 1)
-        table, key_bits = utils.init_hashmap(shape, slots, coords.device)
+        table, key_bits = utils.init_table(shape, slots, coords.device)
         built = kernels.cuda.sparse_build_neighbor_map(coords, out_coords, shape, kernel_size, stride, padding, dilation, table,
                                                        key_bits, slots, needs_grad)
         if spconv.ALGORITHM == Algorithm.EXPLICIT_GEMM:

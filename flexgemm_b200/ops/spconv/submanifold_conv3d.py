@@ -94,7 +94,7 @@ class SubMConv3dFunction(Function):
         assert all(int(k) % 2 == 1 for k in kernel_size), "Kernel extents must be odd"
         n = coords.shape[0]
         slots = max(int(spconv.HASHMAP_RATIO * n), n, 1)
-        table, key_bits = utils.init_hashmap(shape, slots, coords.device)
+        table, key_bits = utils.init_table(shape, slots, coords.device)
         built = kernels.cuda.subm_build_neighbor_map(coords, shape, kernel_size, dilation, table, key_bits, slots)
         if spconv.ALGORITHM == Algorithm.EXPLICIT_GEMM:
             kernels.cuda.raise_for_status(int(built["meta"][-1].item()))

@@ -411,8 +411,10 @@ int64_t fgb_sparse_conv_workspace_bytes(int pass, int64_t n_out, int64_t n_in, i
  * grid_sample.cu, kernels/cuda/hash/hash.cu, kernels/triton/grid_sample/).
  * --------------------------------------------------------------------- */
 
-/* Clears the table and inserts coords[i] -> i.  Stands in for
- * hashmap_insert_3d_idx_as_val (hash/hash.cu:369-449).  slots >= n. */
+/* The library's own packed table (one 64-bit word per slot for 32-bit keys; the
+ * layout the neighbour-map and grid-sample kernels probe): clears it and inserts
+ * coords[i] -> i.  Plays the part of hashmap_insert_3d_idx_as_val
+ * (hash/hash.cu:369-449) inside grid_sample_3d.  slots >= n. */
 int fgb_hash_insert_3d_idx_as_val(const int32_t* coords, int64_t n, int W, int H, int D,
                                   void* table, int64_t slots, int key_bits, int32_t* status, void* stream);
 
@@ -421,6 +423,35 @@ int fgb_hash_insert_3d_idx_as_val(const int32_t* coords, int64_t n, int W, int H
  * for hashmap_lookup_3d (hash/hash.cu:296-365). */
 int fgb_hash_lookup_3d(const int32_t* query_coords, int64_t m, int W, int H, int D,
                        void* table, int64_t slots, int key_bits, uint32_t* out_rows, void* stream);
+
+/* The generic hash map with caller-chosen values, in the reference's layout:
+ * hashmap_keys (uint32 or uint64 [slots], empty = all ones, initialised by the
+ * caller as init_hashmap does, flex_gemm/ops/utils.py:4-19) and hashmap_vals
+ * (uint32 or uint64 [slots]); key_bits / val_bits are 32 or 64.  A lookup
+ * returns all ones (of the value type) for an absent key.  Which slot a key
+ * occupies is not part of the contract.  Inserting duplicate keys in one call
+ * keeps one of their values.  A full table records FGB_S_TABLE_FULL in *status
+ * (may be null).
+ *   fgb_hashmap_insert         keys [m] -> values [m]        (hash/hash.cu:13-92)
+ *   fgb_hashmap_lookup         values of keys [m]             (hash/hash.cu:94-175)
+ *   fgb_hashmap_insert_3d      key = flat (b, x, y, z) index of coords [m,4],
+ *                              truncated to the key type       (hash/hash.cu:177-270)
+ *   fgb_hashmap_lookup_3d      the same keying; coordinates outside
+ *                              [0,W)x[0,H)x[0,D) are absent    (hash/hash.cu:272-365)
+ *   fgb_hashmap_insert_3d_idx_as_val   value = row number      (hash/hash.cu:369-449)
+ * coords must be 16-byte aligned. */
+int fgb_hashmap_insert(void* hashmap_keys, void* hashmap_vals, int64_t slots, int key_bits, int val_bits,
+                       const void* keys, const void* values, int64_t m, int32_t* status, void* stream);
+int fgb_hashmap_lookup(const void* hashmap_keys, const void* hashmap_vals, int64_t slots, int key_bits, int val_bits,
+                       const void* keys, int64_t m, void* out_values, void* stream);
+int fgb_hashmap_insert_3d(void* hashmap_keys, void* hashmap_vals, int64_t slots, int key_bits, int val_bits,
+                          const int32_t* coords, const void* values, int64_t m, int W, int H, int D,
+                          int32_t* status, void* stream);
+int fgb_hashmap_insert_3d_idx_as_val(void* hashmap_keys, void* hashmap_vals, int64_t slots, int key_bits, int val_bits,
+                                     const int32_t* coords, int64_t m, int W, int H, int D,
+                                     int32_t* status, void* stream);
+int fgb_hashmap_lookup_3d(const void* hashmap_keys, const void* hashmap_vals, int64_t slots, int key_bits, int val_bits,
+                          const int32_t* coords, int64_t m, int W, int H, int D, void* out_values, void* stream);
 
 /* Neighbour map of B*L float query points (x, y, z) in voxel units, batch b =
  * point / L, against a table built by fgb_hash_insert_3d_idx_as_val.

@@ -33,7 +33,7 @@ def build_table(coords_np, shape):
     coords = torch.from_numpy(np.ascontiguousarray(coords_np)).to(DEV)
     slots = max(2 * coords.shape[0], 1)
     table, key_bits = utils.init_hashmap(shape, slots, DEV)
-    status = K.hashmap_insert_3d_idx_as_val(table, key_bits, slots, coords, *[int(v) for v in shape[-3:]])
+    status = K.table_insert_3d_idx_as_val(table, key_bits, slots, coords, *[int(v) for v in shape[-3:]])
     assert int(status.item()) == 0
     return table, key_bits, slots
 
@@ -46,7 +46,7 @@ def test_table_lookup_and_neighbor_maps(name):
     table, key_bits, slots = build_table(coords, shape)
     # plain lookups: every stored voxel, its +x neighbour, and points outside the grid
     probe = np.concatenate([coords, coords + np.array([0, 1, 0, 0], dtype=np.int32), np.array([[0, -1, 0, 0], [0, 0, H, 0]], dtype=np.int32)])
-    got = u32(K.hashmap_lookup_3d(table, key_bits, slots, torch.from_numpy(np.ascontiguousarray(probe)).to(DEV), W, H, D))
+    got = u32(K.table_lookup_3d(table, key_bits, slots, torch.from_numpy(np.ascontiguousarray(probe)).to(DEV), W, H, D))
     want = orc._rows_of(coords, shape, probe.astype(np.int64))
     assert np.array_equal(got, np.where(want < 0, 0xFFFFFFFF, want).astype(np.uint32))
     qd = torch.from_numpy(q).to(DEV)
