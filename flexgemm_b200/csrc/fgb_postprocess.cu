@@ -1,34 +1,9 @@
 // Post-processing of the neighbour map for the masked implicit GEMM:
-// sorted row order, wgrad pair lists, per-tile offset masks and their list form.
-#include <cub/device/device_radix_sort.cuh>
-
+// wgrad pair lists, per-tile offset masks and their list form (the sorted row
+// order is in fgb_sort.cu).
 #include "fgb_common.cuh"
 
 namespace fgb {
-
-// ------------------------------------------------------------------ sorted_idx
-__global__ void iota_i64_kernel(int64_t* out, int64_t n) {
-  const int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
-  if (i < n) out[i] = i;
-}
-
-struct SortPlan {
-  size_t keys_out_off, vals_in_off, temp_off, temp_bytes, total;
-};
-
-static int sort_plan(int64_t n, SortPlan* p) {
-  auto align = [](size_t x) { return (x + 255) & ~size_t(255); };
-  p->keys_out_off = 0;
-  p->vals_in_off = align(size_t(n) * sizeof(int32_t));
-  p->temp_off = p->vals_in_off + align(size_t(n) * sizeof(int64_t));
-  p->temp_bytes = 0;
-  cudaError_t e = cub::DeviceRadixSort::SortPairs(nullptr, p->temp_bytes, static_cast<const int32_t*>(nullptr),
-                                                  static_cast<int32_t*>(nullptr), static_cast<const int64_t*>(nullptr),
-                                                  static_cast<int64_t*>(nullptr), n, 0, 32, nullptr);
-  if (e != cudaSuccess) return cuda_status(e);
-  p->total = p->temp_off + align(p->temp_bytes);
-  return FGB_OK;
-}
 
 // ------------------------------------------------------------------ pair lists
 // One CTA per 256 voxels (the blocking of the lookup kernel, whose per-block
@@ -143,40 +118,6 @@ __global__ void __launch_bounds__(1024)
 }
 
 }  // namespace fgb
-
-extern "C" int64_t fgb_pp_sorted_idx_workspace_bytes(int64_t n) {
-  if (n < 0 || n >= (int64_t(1) << 31)) return FGB_E_SIZE;
-  fgb::SortPlan p;
-  int rc = fgb::sort_plan(n, &p);
-  return rc == FGB_OK ? static_cast<int64_t>(p.total) : -int64_t(rc < 0 ? -rc : rc);
-}
-
-extern "C" int fgb_pp_sorted_idx(const int32_t* binary_code, int64_t n, int key_bits, int64_t* sorted_idx, void* workspace,
-                                 int64_t workspace_bytes, void* stream) {
-  using namespace fgb;
-  if (n < 0 || n >= (int64_t(1) << 31)) return FGB_E_SIZE;
-  if (key_bits < 1 || key_bits > 32) return FGB_E_SIZE;
-  if (n == 0) return FGB_OK;
-  if (!binary_code || !sorted_idx || !workspace) return FGB_E_NULL;
-  if (reinterpret_cast<uintptr_t>(workspace) & 255) return FGB_E_ALIGN;
-  SortPlan p;
-  int rc = sort_plan(n, &p);
-  if (rc != FGB_OK) return rc;
-  if (workspace_bytes < static_cast<int64_t>(p.total)) return FGB_E_WORKSPACE;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  char* ws = static_cast<char*>(workspace);
-  auto* keys_out = reinterpret_cast<int32_t*>(ws + p.keys_out_off);
-  auto* vals_in = reinterpret_cast<int64_t*>(ws + p.vals_in_off);
-  iota_i64_kernel<<<static_cast<unsigned>(ceil_div(n, 256)), 256, 0, s>>>(vals_in, n);
-  size_t temp = p.temp_bytes;
-  // Codes with fewer than 32 significant bits are non-negative, so sorting the
-  // low key_bits bits orders them as signed integers; with 32 bits the signed
-  // key type does.
-  cudaError_t e = cub::DeviceRadixSort::SortPairs(ws + p.temp_off, temp, binary_code, keys_out, vals_in, sorted_idx, n, 0,
-                                                  key_bits, s);
-  if (e != cudaSuccess) return cuda_status(e);
-  return launch_status();
-}
 
 extern "C" int fgb_pp_valid_signal(const uint32_t* neighbor_map, const int32_t* gray_code, int64_t n, int V,
                                    const uint32_t* block_offsets, const uint32_t* valid_signal_seg, uint32_t* valid_signal_i,

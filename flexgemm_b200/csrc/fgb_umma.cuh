@@ -80,7 +80,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // ------------------------------------------------------------------ proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   // generic-proxy writes to shared memory -> visible to the async proxy (tcgen05.mma, TMA)
+#ifndef FGB_AB_NO_PROXY_FENCE  // measurement builds only: what the fence costs
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
 }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }

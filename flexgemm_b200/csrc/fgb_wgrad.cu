@@ -645,6 +645,17 @@ extern "C" int64_t fgb_sparse_conv_workspace_bytes(int pass, int64_t n_out, int6
 }
 
 namespace fgb {
+// One launcher per kernel instance: the dynamic shared-memory limit is a property of (kernel, device), and all
+// instances share one function-pointer type, so the table must hang on the template arguments, not on the type.
+template <int kElem, int kRows>
+static int launch_wgrad(int64_t grid, size_t smem, const WgradParams& p, cudaStream_t s) {
+  static PerDeviceTable configured;
+  const int rc = ensure_dynamic_smem(configured, subm_wgrad_kernel<kElem, kRows>, smem);
+  if (rc != FGB_OK) return rc;
+  subm_wgrad_kernel<kElem, kRows><<<static_cast<unsigned>(grid), kWgThreads, smem, s>>>(p);
+  return launch_status();
+}
+
 // one wgrad pass over operands of element type `dtype` (never FGB_F32_IEEE): partial slabs, then the ordered sum
 static int wgrad_pass(const void* grad_out, const void* feats, const uint32_t* vs_i, const uint32_t* vs_o, const uint32_t* seg,
                       const uint32_t* block_offsets, void* grad_weight, float* grad_weight_f32, int64_t n_out, int64_t n_in,
@@ -673,18 +684,10 @@ static int wgrad_pass(const void* grad_out, const void* feats, const uint32_t* v
   p.status = status;
   const int64_t grid = max_units * w.co_groups * w.ci_tiles;
   if (grid > 0x7FFFFFFF) return FGB_E_SIZE;
-  const auto launch = [&](auto kernel) -> cudaError_t {
-    static PerDeviceTable configured;  // one per kernel instance (the lambda is instantiated per kernel type)
-    if (ensure_dynamic_smem(configured, kernel, w.smem) != FGB_OK) return cudaErrorInvalidValue;
-    kernel<<<static_cast<unsigned>(grid), kWgThreads, w.smem, s>>>(p);
-    return cudaSuccess;
-  };
-  cudaError_t e;
   const int rows = w.kb / 32;
-  if (eb == 2) e = rows == 4 ? launch(subm_wgrad_kernel<2, 4>) : rows == 2 ? launch(subm_wgrad_kernel<2, 2>) : launch(subm_wgrad_kernel<2, 1>);
-  else e = rows == 4 ? launch(subm_wgrad_kernel<4, 4>) : rows == 2 ? launch(subm_wgrad_kernel<4, 2>) : launch(subm_wgrad_kernel<4, 1>);
-  if (e != cudaSuccess) return cuda_status(e);
-  int rc = launch_status();
+  int rc;
+  if (eb == 2) rc = rows == 4 ? launch_wgrad<2, 4>(grid, w.smem, p, s) : rows == 2 ? launch_wgrad<2, 2>(grid, w.smem, p, s) : launch_wgrad<2, 1>(grid, w.smem, p, s);
+  else rc = rows == 4 ? launch_wgrad<4, 4>(grid, w.smem, p, s) : rows == 2 ? launch_wgrad<4, 2>(grid, w.smem, p, s) : launch_wgrad<4, 1>(grid, w.smem, p, s);
   if (rc != FGB_OK) return rc;
   const dim3 rgrid(static_cast<unsigned>(ceil_div(int64_t(Co) * Ci, 1024)), static_cast<unsigned>(V));
   switch (dtype) {

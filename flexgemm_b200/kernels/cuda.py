@@ -42,9 +42,8 @@ def _stream(device) -> int:
 _scratch: Dict[tuple, torch.Tensor] = {}
 _status: Dict[int, torch.Tensor] = {}
 
-# Number of this library's own kernels launched so far (CUB's radix-sort kernels
-# inside fgb_pp_sorted_idx are not counted).  Each wrapper adds the fixed number
-# of kernels its C entry point launches.
+# Number of this library's own kernels launched so far.  Each wrapper adds the
+# number of kernels its C entry point launches.
 launch_count = 0
 
 
@@ -297,7 +296,7 @@ def raise_for_status(code: int) -> None:
 
 
 def sorted_idx_from_binary(binary_code: torch.Tensor, key_bits: int) -> torch.Tensor:
-    """int64 stable argsort of the binary code (radix sort over ``key_bits`` bits)."""
+    """int64 stable argsort of the binary code (the library's own radix sort over ``key_bits`` bits)."""
     lib = _cabi.lib()
     dev = binary_code.device
     n = binary_code.shape[0]
@@ -306,9 +305,10 @@ def sorted_idx_from_binary(binary_code: torch.Tensor, key_bits: int) -> torch.Te
         return out
     nbytes = _cabi.check_size(lib.fgb_pp_sorted_idx_workspace_bytes(n), "fgb_pp_sorted_idx_workspace_bytes")
     ws = workspace(dev, "sort", nbytes)
-    rc = lib.fgb_pp_sorted_idx(binary_code.data_ptr(), n, int(key_bits), out.data_ptr(), ws.data_ptr(), ws.numel() * 8, _stream(dev))
+    rc = lib.fgb_pp_sorted_idx(binary_code.data_ptr(), n, int(key_bits), out.data_ptr(), ws.data_ptr(), ws.numel() * 8,
+                               status_word(dev).data_ptr(), _stream(dev))
     _cabi.check(rc, "fgb_pp_sorted_idx")
-    _count(1)
+    _count(1 + (int(key_bits) + 8) // 9)   # digit histogram + one kernel per 9-bit digit
     return out
 
 

@@ -113,12 +113,17 @@ int fgb_subm_build_neighbor_map(const int32_t* coords, int64_t n,
 /* Workspace bytes for fgb_pp_sorted_idx. */
 int64_t fgb_pp_sorted_idx_workspace_bytes(int64_t n);
 
-/* sorted_idx (int64 [n]) = a stable argsort of binary_code (signed int32,
- * only bits [0, key_bits) differ).  Stands in for torch::argsort(binary_code)
- * in migemm_neighmap_pp.cu:79, 221. */
+/* sorted_idx (int64 [n]) = the stable argsort of binary_code (signed int32,
+ * only bits [0, key_bits) differ): a radix sort with 9-bit digits, one kernel
+ * per digit (three for a 3x3x3 stencil), the tiles of a pass chained by a
+ * decoupled look-back.  n < 2^30.  A look-back that stays unanswered (it never
+ * should) records FGB_S_WAIT_TIMEOUT in *status (may be null) instead of
+ * spinning.  Stands in for torch::argsort(binary_code) in
+ * migemm_neighmap_pp.cu:79, 221 (an unstable sort there; any order of equal
+ * codes is a valid result, this one is the stable one and hence deterministic). */
 int fgb_pp_sorted_idx(const int32_t* binary_code, int64_t n, int key_bits,
                       int64_t* sorted_idx, void* workspace, int64_t workspace_bytes,
-                      void* stream);
+                      int32_t* status, void* stream);
 
 /* Pair lists for wgrad: grouped by offset v, ascending output row inside a
  * group: valid_signal_o[p] = row, valid_signal_i[p] = neighbor_map[row, v].

@@ -32,7 +32,7 @@ def build_table(coords_np, shape):
     from flexgemm_b200.ops import utils
     coords = torch.from_numpy(np.ascontiguousarray(coords_np)).to(DEV)
     slots = max(2 * coords.shape[0], 1)
-    table, key_bits = utils.init_hashmap(shape, slots, DEV)
+    table, key_bits = utils.init_table(shape, slots, DEV)
     status = K.table_insert_3d_idx_as_val(table, key_bits, slots, coords, *[int(v) for v in shape[-3:]])
     assert int(status.item()) == 0
     return table, key_bits, slots
