@@ -21,7 +21,7 @@ _PROTOTYPES = {
     "fgb_selftest_device_tables": (c_int, []),
     "fgb_hash_table_bytes": (c_int64, [c_int64, c_int]),
     "fgb_map_num_blocks": (c_int64, [c_int64]),
-    "fgb_subm_build_neighbor_map": (c_int, [_P, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+    "fgb_subm_build_neighbor_map": (c_int, [_P, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                             _P, c_int64, c_int, _P, _P, _P, _P, _P, _P, _P]),
     "fgb_pp_sorted_idx_workspace_bytes": (c_int64, [c_int64]),
     "fgb_pp_sorted_idx": (c_int, [_P, c_int64, c_int, _P, _P, c_int64, _P, _P]),

@@ -17,13 +17,16 @@
 // counts that a small scan turns into the offsets of the wgrad pair lists.
 //
 // Sorted input (the common case: coordinates in lexicographic (b, x, y, z)
-// order, which is ascending flat-index order) needs no table at all for the
-// 3x3x3, dilation-1 stencil: a row's position in the input IS its rank among
-// the keys, and the neighbours of 256 consecutive voxels lie in nine short
-// windows of the same array (one per (dx, dy); the three dz neighbours are
-// adjacent keys).  A check kernel decides on the device which path runs -- the
-// kernels of the other path return at once -- so no host round trip is added;
-// both paths produce the same map.
+// order, which is ascending flat-index order) needs no hash table at all: a
+// row's position in the input IS its rank among the keys, and the voxels of one
+// (b, x, y) column are consecutive rows.  One kernel checks the order and, while
+// it has neighbouring rows in hand, writes the first and one-past-last row of
+// every column into a direct-address table (8 bytes per column, kept in the
+// memory the caller provided for the hash table); the lookup kernel then finds a
+// neighbour by reading the column entry of (x + dx, y + dy) and searching the
+// few rows of that column for z + dz.  The decision is taken on the device --
+// the kernels of the other path return at once -- so no host round trip is
+// added; both paths produce the same map.
 #include <algorithm>
 #include <type_traits>
 
@@ -181,17 +184,35 @@ __global__ void seg_prefix_kernel(uint32_t* seg, int V) {
 }
 
 // ------------------------------------------------------------------ sorted-input path
-constexpr int kCombos = 9;          // (dx, dy) pairs of the 3x3x3 stencil
-constexpr int kLocalSlots = 1024;   // slots of a CTA's own shared-memory table over its 256 voxels (load factor 1/4)
-
-// *unsorted = 1 when some key is not greater than its predecessor (the word must be 0 on entry)
+// Column table entry: (first row, one past the last row) of the voxels of one (b, x, y) column; first == kInvalid for
+// an empty column.
+//
+// *unsorted = 1 when some key is not greater than its predecessor or a coordinate lies outside the grid / batch (the
+// word must be 0 on entry); otherwise every non-empty column's entry is written (the table must be filled with
+// 0xff bytes on entry).
 template <int kKeyBits>
-__global__ void __launch_bounds__(256) sorted_check_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, uint32_t* unsorted) {
+__global__ void __launch_bounds__(256) column_index_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, uint64_t columns,
+                                                          uint2* __restrict__ col_table, uint32_t* unsorted) {
   const uint32_t i = blockIdx.x * 256u + threadIdx.x;
   bool bad = false;
-  if (i > 0 && i < n) {
-    const int4 a = __ldg(&coords[i - 1]), b = __ldg(&coords[i]);
-    bad = g.template key<kKeyBits>(a.x, a.y, a.z, a.w) >= g.template key<kKeyBits>(b.x, b.y, b.z, b.w);
+  if (i < n) {
+    const int4 b = __ldg(&coords[i]);
+    const bool inside = b.x >= 0 && b.y >= 0 && b.y < g.W && b.z >= 0 && b.z < g.H && b.w >= 0 && b.w < g.D;
+    const uint64_t col = (static_cast<uint64_t>(static_cast<uint32_t>(b.x)) * g.W + static_cast<uint32_t>(b.y)) * g.H + static_cast<uint32_t>(b.z);
+    bad = !inside || col >= columns;
+    uint64_t col_prev = ~uint64_t(0);
+    if (i > 0) {
+      const int4 a = __ldg(&coords[i - 1]);
+      bad = bad || g.template key<kKeyBits>(a.x, a.y, a.z, a.w) >= g.template key<kKeyBits>(b.x, b.y, b.z, b.w);
+      col_prev = (static_cast<uint64_t>(static_cast<uint32_t>(a.x)) * g.W + static_cast<uint32_t>(a.y)) * g.H + static_cast<uint32_t>(a.z);
+    }
+    if (!bad) {
+      if (col != col_prev) {
+        col_table[col].x = i;
+        if (i > 0 && col_prev < columns) col_table[col_prev].y = i;
+      }
+      if (i == n - 1) col_table[col].y = n;
+    }
   }
   // one store per warp at most, and none once the word is set (with shuffled input every thread would store otherwise)
   if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0 && *reinterpret_cast<volatile uint32_t*>(unsorted) == 0u) *unsorted = 1u;
@@ -203,172 +224,94 @@ __global__ void __launch_bounds__(256) table_clear_kernel(uint32_t* __restrict__
   for (size_t i = blockIdx.x * size_t(256) + threadIdx.x; i < count; i += size_t(gridDim.x) * 256) words[i] = 0xFFFFFFFFu;
 }
 
-template <int kKeyBits>
-__device__ __forceinline__ long long key_at(const int4* __restrict__ coords, uint32_t i, const Grid3& g) {
-  const int4 c = __ldg(&coords[i]);
-  return static_cast<long long>(g.template key<kKeyBits>(c.x, c.y, c.z, c.w));
-}
-
-template <typename K>
-__device__ __forceinline__ uint32_t local_home(K key) {
-  uint32_t k32 = static_cast<uint32_t>(key);
-  if constexpr (sizeof(K) == 8) k32 ^= static_cast<uint32_t>(static_cast<unsigned long long>(key) >> 32) * 0x85EBCA6Bu;
-  return (k32 * 0x9E3779B1u) >> 22;  // top 10 bits: kLocalSlots = 1024
-}
-static_assert(kLocalSlots == 1024 && kLocalSlots == 4 * kMapBlock, "local_home() returns 10 bits; the table is cleared with one 16-byte store per thread");
-
-// One CTA per 256 voxels (the blocking of the hash lookup, so the side products
-// are the same).  With the rows in key order a row's position is its rank, so no
-// global table is needed: the voxels that can be neighbours of the CTA's voxels
-// at (dx, dy, *) have keys between key_first + delta - 1 and key_last + delta + 1,
-// a contiguous run of rows whose ends two binary searches find.  The CTA keeps a
-// small shared-memory table over its OWN 256 keys, streams the nine runs once
-// (coalesced) and lets every streamed row look for the up to three voxels it is a
-// neighbour of (itself minus (dx, dy, dz), dz = -1, 0, 1) -- a hit writes the
-// streamed row's number into that voxel's map row.  All probes are independent
-// shared-memory reads; nothing depends on the length of a run.
+// One CTA per 256 voxels (the blocking of the hash lookup, so the side products are the same).  Work items are
+// (voxel, (kx, ky)) pairs, dealt to the threads round-robin: an item reads the entry of the neighbouring column and
+// walks the column's rows (ascending z) once for the Kd targets z + (kz - Kd/2) * Dd, which ascend with kz.  Hits go
+// into the CTA's map tile in shared memory, which leaves as 16-byte stores.
 template <int kKeyBits>
 __global__ void __launch_bounds__(kMapBlock)
-    subm_sorted_lookup_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, uint32_t* __restrict__ nbr,
-                              int32_t* __restrict__ gray_out, int32_t* __restrict__ binary_out, uint32_t* __restrict__ block_counts,
-                              uint32_t nblk, const uint32_t* __restrict__ unsorted) {
-  using K = typename std::conditional<kKeyBits == 32, uint32_t, unsigned long long>::type;
+    subm_column_lookup_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, Stencil st, const uint2* __restrict__ col_table,
+                              uint32_t* __restrict__ nbr, int32_t* __restrict__ gray_out, int32_t* __restrict__ binary_out,
+                              uint32_t* __restrict__ block_counts, uint32_t nblk, const uint32_t* __restrict__ unsorted) {
   if (*unsorted != 0u) return;  // the hash kernels build the map
-  __shared__ __align__(16) uint32_t s_nbr[kMapBlock * 27];
-  __shared__ __align__(16) uint32_t s_slot[kLocalSlots];  // local voxel index, kInvalid = empty
-  __shared__ K s_key[kMapBlock];
-  __shared__ uint32_t s_lo[kCombos], s_hi[kCombos];
+  extern __shared__ __align__(16) uint32_t s_nbr[];  // [kMapBlock * V]
+  __shared__ int4 s_coord[kMapBlock];
   __shared__ uint32_t s_count[32];
   const uint32_t n0 = blockIdx.x * kMapBlock;
   const uint32_t nv = min(static_cast<uint32_t>(kMapBlock), n - n0);
   const int t = threadIdx.x, lane = t & 31;
+  const int V = st.V;
   {
     const uint4 inv = make_uint4(kInvalid, kInvalid, kInvalid, kInvalid);
-    reinterpret_cast<uint4*>(s_slot)[t] = inv;  // kLocalSlots / 4 == kMapBlock
-#pragma unroll
-    for (int i = t; i < kMapBlock * 27 / 4; i += kMapBlock) reinterpret_cast<uint4*>(s_nbr)[i] = inv;
+    for (int i = t; i < kMapBlock * V / 4; i += kMapBlock) reinterpret_cast<uint4*>(s_nbr)[i] = inv;  // kMapBlock * V is a multiple of 4
   }
   if (t < 32) s_count[t] = 0;
-  K key = 0;
-  if (t < nv) {
-    const int4 cc = __ldg(&coords[n0 + t]);
-    key = g.template key<kKeyBits>(cc.x, cc.y, cc.z, cc.w);
-    s_key[t] = key;
-  }
+  if (t < nv) s_coord[t] = __ldg(&coords[n0 + t]);
   __syncthreads();
 
-  const long long HD = static_cast<long long>(g.H) * g.D;
-  if (t < nv) {  // keys are distinct (strictly increasing), so every insert ends on an empty slot
-    uint32_t slot = local_home<K>(key);
-    while (atomicCAS(&s_slot[slot], kInvalid, static_cast<uint32_t>(t)) != kInvalid) slot = (slot + 1) & (kLocalSlots - 1);
-  }
-  {
-    // Run bounds, one group of eight lanes per bound (18 of the CTA's 32 groups): group 2c finds the first row with
-    // key >= key_first + delta - 1, group 2c + 1 the first row with key > key_last + delta + 1.  Each step the eight
-    // lanes test eight pivots that cut the range into nine parts, so a bound costs about log9(n) dependent loads
-    // instead of log2(n).
-    const int grp = t >> 3, gl = t & 7;
-    if (grp < 2 * kCombos) {
-      const unsigned gmask = 0xFFu << (lane & 24);
-      const int c = grp >> 1;
-      const bool upper = grp & 1;
-      const long long delta = (c / 3 - 1) * HD + (c % 3 - 1) * static_cast<long long>(g.D);
-      const long long target = static_cast<long long>(upper ? s_key[nv - 1] : s_key[0]) + delta + (upper ? 1 : -1);
-      // invariant: rows < lo go left of the bound, rows >= hi do not
-      uint32_t lo = 0, hi = n;
-      while (hi - lo > 8u) {
-        // pivot k of 1..8 sits at lo + floor(span * k / 9) = lo + step * k + floor(rem * k / 9); rem * k <= 72, where
-        // (x * 57) >> 9 equals x / 9
-        const uint32_t span = hi - lo, step = span / 9u, rem = span - step * 9u;
-        auto pivot_at = [&](uint32_t k) { return lo + step * k + ((rem * k * 57u) >> 9); };
-        const uint32_t pivot = pivot_at(gl + 1);  // lo < pivot < hi, increasing in gl
-        const long long km = key_at<kKeyBits>(coords, pivot, g);
-        const bool left = upper ? km <= target : km < target;
-        const unsigned votes = (__ballot_sync(gmask, left) >> (lane & 24)) & 0xFFu;  // monotone: a prefix of ones
-        const int cnt = __popc(votes);
-        const uint32_t p_prev = pivot_at(cnt);      // last pivot that went left (cnt > 0)
-        const uint32_t p_next = pivot_at(cnt + 1);  // first pivot that did not (cnt < 8)
-        if (cnt < 8) hi = p_next;
-        if (cnt > 0) lo = p_prev + 1;
-      }
-      {
-        const uint32_t r = lo + gl;
-        bool left = false;
-        if (r < hi) {
-          const long long km = key_at<kKeyBits>(coords, r, g);
-          left = upper ? km <= target : km < target;
-        }
-        const unsigned votes = (__ballot_sync(gmask, left) >> (lane & 24)) & 0xFFu;
-        lo += __popc(votes);
-      }
-      if (gl == 0) {
-        if (upper) s_hi[c] = lo;
-        else s_lo[c] = lo;
+  const int combos = st.Kw * st.Kh;
+  const uint32_t items = nv * combos;
+  for (uint32_t item = t; item < items; item += kMapBlock) {
+    const uint32_t lv = item / combos;
+    const int c = static_cast<int>(item - lv * combos);
+    const int kx = c / st.Kh, ky = c - kx * st.Kh;
+    const int4 me = s_coord[lv];
+    const int x = me.y + (kx - st.Kw / 2) * st.Dw, y = me.z + (ky - st.Kh / 2) * st.Dh;
+    if (x < 0 || x >= g.W || y < 0 || y >= g.H) continue;
+    uint32_t* out = s_nbr + lv * V + c * st.Kd;
+    const bool own_column = kx == st.Kw / 2 && ky == st.Kh / 2;
+    const uint64_t col = (static_cast<uint64_t>(static_cast<uint32_t>(me.x)) * g.W + static_cast<uint32_t>(x)) * g.H + static_cast<uint32_t>(y);
+    const uint2 e = __ldg(&col_table[col]);
+    if (e.x == kInvalid) continue;
+    // first row of the column whose z is not below the smallest target
+    const int z_first = me.w - (st.Kd / 2) * st.Dd;
+    uint32_t lo = e.x, hi = e.y;
+    const uint32_t back = static_cast<uint32_t>((st.Kd / 2) * st.Dd);  // z_first = z - back
+    if (own_column && back <= 8u) {
+      // this voxel's own column: z strictly increases along its rows, so z - back cannot lie more than `back` rows before it
+      const uint32_t self = n0 + lv;
+      lo = self - e.x > back ? self - back : e.x;
+    } else {
+      while (hi - lo > 4u) {  // short columns (a surface crosses a column a few times) are walked from their start
+        const uint32_t mid = lo + ((hi - lo) >> 1);
+        if (__ldg(&coords[mid].w) < z_first) lo = mid + 1;
+        else hi = mid;
       }
     }
-  }
-  __syncthreads();
-
-  // the nine runs as one flat list, so that every thread gets the same share whatever the runs' lengths
-  uint32_t off[kCombos + 1];
-  off[0] = 0;
-#pragma unroll
-  for (int c = 0; c < kCombos; ++c) off[c + 1] = off[c] + (s_hi[c] > s_lo[c] ? s_hi[c] - s_lo[c] : 0u);
-#pragma unroll 2
-  for (uint32_t f = t; f < off[kCombos]; f += kMapBlock) {
-    // which run f falls into: first dx (runs 0-2, 3-5, 6-8), then dy
-    const int gx = (f >= off[3]) + (f >= off[6]);
-    const uint32_t o1 = gx == 0 ? off[1] : gx == 1 ? off[4] : off[7], o2 = gx == 0 ? off[2] : gx == 1 ? off[5] : off[8];
-    const int gy = (f >= o1) + (f >= o2);
-    const uint32_t base = gy == 0 ? (gx == 0 ? 0u : gx == 1 ? off[3] : off[6]) : gy == 1 ? o1 : o2;
-    const int c = gx * 3 + gy;
-    const uint32_t row = s_lo[c] + (f - base);
-    const int4 e = __ldg(&coords[row]);
-    const int dx = gx - 1, dy = gy - 1;
-    const int xs = e.y - dx, ys = e.z - dy;  // the voxels this row is a (dx, dy, dz) neighbour of: (b, xs, ys, z - dz)
-    if (xs < 0 || xs >= g.W || ys < 0 || ys >= g.H) continue;
-    const K row0 = g.template key<kKeyBits>(e.x, xs, ys, 0);
-#pragma unroll
-    for (int dz = -1; dz <= 1; ++dz) {
-      const int zs = e.w - dz;
-      if (zs < 0 || zs >= g.D) continue;
-      const K want = row0 + static_cast<K>(zs);
-      uint32_t slot = local_home<K>(want);
-      for (int probe = 0; probe < kLocalSlots; ++probe) {
-        const uint32_t i = s_slot[slot];
-        if (i == kInvalid) break;
-        if (s_key[i] == want) {
-          s_nbr[i * 27 + c * 3 + (dz + 1)] = row;
-          break;
-        }
-        slot = (slot + 1) & (kLocalSlots - 1);
+    uint32_t row = lo;
+    int zr = row < e.y ? __ldg(&coords[row].w) : 0x7FFFFFFF;
+    for (int kz = 0; kz < st.Kd; ++kz) {
+      const int z = z_first + kz * st.Dd;
+      if (z < 0 || z >= g.D) continue;
+      while (zr < z) {
+        ++row;
+        zr = row < e.y ? __ldg(&coords[row].w) : 0x7FFFFFFF;
       }
+      if (zr == z) out[kz] = row;
     }
   }
   __syncthreads();
 
   uint32_t gray = 0;
   if (t < nv) {
-#pragma unroll
-    for (int k = 0; k < 27; ++k) {
-      if (s_nbr[t * 27 + k] != kInvalid) gray |= 1u << k;
+    for (int k = 0; k < V; ++k) {
+      if (s_nbr[t * V + k] != kInvalid) gray |= 1u << k;
     }
   }
   // per-offset valid counts of the CTA (for the pair-list offsets): lane v of each warp keeps the warp's count of offset v
   {
     uint32_t mine = 0;
-#pragma unroll
-    for (int v = 0; v < 27; ++v) {
+    for (int v = 0; v < V; ++v) {
       const uint32_t b = __ballot_sync(0xffffffffu, (gray >> v) & 1u);
       if (lane == v) mine = static_cast<uint32_t>(__popc(b));
     }
-    if (lane < 27 && mine != 0u) atomicAdd(&s_count[lane], mine);
+    if (lane < V && mine != 0u) atomicAdd(&s_count[lane], mine);
   }
   __syncthreads();
   {
-    // the CTA's map rows leave as 16-byte pieces (a block starts 256 * 108 bytes after the previous one)
-    uint32_t* out = nbr + static_cast<size_t>(n0) * 27;
-    const uint32_t words = nv * 27;
+    // the CTA's map rows leave as 16-byte pieces (a block starts 256 * V * 4 bytes after the previous one)
+    uint32_t* out = nbr + static_cast<size_t>(n0) * V;
+    const uint32_t words = nv * V;
     const uint32_t vecs = (reinterpret_cast<uintptr_t>(out) & 15) == 0 ? words >> 2 : 0u;  // a map that is only 4-byte aligned goes word by word
     for (uint32_t i = t; i < vecs; i += kMapBlock) reinterpret_cast<uint4*>(out)[i] = reinterpret_cast<const uint4*>(s_nbr)[i];
     for (uint32_t i = vecs * 4 + t; i < words; i += kMapBlock) out[i] = s_nbr[i];
@@ -383,34 +326,38 @@ __global__ void __launch_bounds__(kMapBlock)
     gray_out[n0 + t] = static_cast<int32_t>(gray);
     binary_out[n0 + t] = static_cast<int32_t>(binary);
   }
-  if (t < 27) block_counts[static_cast<size_t>(t) * nblk + blockIdx.x] = s_count[t];
+  if (t < V) block_counts[static_cast<size_t>(t) * nblk + blockIdx.x] = s_count[t];
 }
 
 template <int kKeyBits>
-static int build_impl(const int32_t* coords, uint32_t n, Grid3 g, Stencil st, void* table, uint32_t slots, uint32_t* nbr,
+static int build_impl(const int32_t* coords, uint32_t n, int B, Grid3 g, Stencil st, void* table, uint32_t slots, uint32_t* nbr,
                       int32_t* gray, int32_t* binary, uint32_t* block_counts, uint32_t* seg, int32_t* status, cudaStream_t s) {
   const uint32_t nblk = static_cast<uint32_t>(ceil_div(n, kMapBlock));
   const int4* c4 = reinterpret_cast<const int4*>(coords);
-  const size_t table_words = static_cast<size_t>(fgb_hash_table_bytes(slots, kKeyBits)) / 4;
+  const size_t table_bytes = static_cast<size_t>(fgb_hash_table_bytes(slots, kKeyBits));
+  const size_t table_words = table_bytes / 4;
   const unsigned clear_grid = static_cast<unsigned>(std::min<size_t>(ceil_div(static_cast<int64_t>(table_words), 256 * 8), 148 * 16));
-  // The sorted-input path serves the 3x3x3, dilation-1 stencil with keys that fit a signed 64-bit range; seg[0]
-  // (rewritten by the scan at the end) carries the device-side decision between the two paths.
-  const bool try_sorted = st.Kw == 3 && st.Kh == 3 && st.Kd == 3 && st.Dw == 1 && st.Dh == 1 && st.Dd == 1 &&
-                          (kKeyBits == 32 || static_cast<double>(g.W) * g.H * g.D < 1e15);
+  // The sorted-input path needs one 8-byte entry per (b, x, y) column and keeps them in the caller's table memory; the
+  // map tile of a CTA must fit shared memory.  seg[0] (rewritten by the scan at the end) carries the device-side
+  // decision between the two paths.
+  const uint64_t columns = static_cast<uint64_t>(B > 0 ? B : 0) * g.W * g.H;
+  const bool try_sorted = columns > 0 && columns * sizeof(uint2) <= table_bytes;
   uint32_t* unsorted = try_sorted ? seg : nullptr;
   if (try_sorted) {
     cudaError_t e = cudaMemsetAsync(seg, 0, sizeof(uint32_t), s);
     if (e != cudaSuccess) return cuda_status(e);
-    sorted_check_kernel<kKeyBits><<<static_cast<unsigned>(ceil_div(n, 256)), 256, 0, s>>>(c4, n, g, unsorted);
+    e = cudaMemsetAsync(table, 0xFF, columns * sizeof(uint2), s);
+    if (e != cudaSuccess) return cuda_status(e);
+    column_index_kernel<kKeyBits><<<static_cast<unsigned>(ceil_div(n, 256)), 256, 0, s>>>(c4, n, g, columns, static_cast<uint2*>(table), unsorted);
   }
   table_clear_kernel<<<clear_grid > 0 ? clear_grid : 1, 256, 0, s>>>(static_cast<uint32_t*>(table), table_words, unsorted);
   hash_insert_kernel<kKeyBits><<<nblk, kMapBlock, 0, s>>>(c4, n, g, table, slots, status, unsorted);
   subm_lookup_kernel<kKeyBits, false><<<nblk, kMapBlock, 0, s>>>(c4, n, g, st, table, slots, nbr, nullptr, gray, binary, block_counts,
                                                                 nblk, unsorted);
   if (try_sorted) {
-    cudaError_t e = cudaFuncSetAttribute(subm_sorted_lookup_kernel<kKeyBits>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    if (e != cudaSuccess) return cuda_status(e);
-    subm_sorted_lookup_kernel<kKeyBits><<<nblk, kMapBlock, 0, s>>>(c4, n, g, nbr, gray, binary, block_counts, nblk, unsorted);
+    const size_t smem = size_t(kMapBlock) * st.V * sizeof(uint32_t);
+    subm_column_lookup_kernel<kKeyBits><<<nblk, kMapBlock, smem, s>>>(c4, n, g, st, static_cast<const uint2*>(table), nbr, gray, binary,
+                                                                     block_counts, nblk, unsorted);
   }
   block_scan_kernel<<<st.V, 1024, 0, s>>>(block_counts, nblk, seg);
   seg_prefix_kernel<<<1, 32, 0, s>>>(seg, st.V);
@@ -476,13 +423,13 @@ extern "C" int64_t fgb_hash_table_bytes(int64_t slots, int key_bits) {
 
 extern "C" int64_t fgb_map_num_blocks(int64_t n) { return n < 0 ? FGB_E_SIZE : fgb::ceil_div(n, fgb::kMapBlock); }
 
-extern "C" int fgb_subm_build_neighbor_map(const int32_t* coords, int64_t n, int W, int H, int D, int Kw, int Kh, int Kd, int Dw,
+extern "C" int fgb_subm_build_neighbor_map(const int32_t* coords, int64_t n, int B, int W, int H, int D, int Kw, int Kh, int Kd, int Dw,
                                            int Dh, int Dd, void* table, int64_t slots, int key_bits, uint32_t* neighbor_map,
                                            int32_t* gray_code, int32_t* binary_code, uint32_t* block_counts,
                                            uint32_t* valid_signal_seg, int32_t* status, void* stream) {
   using namespace fgb;
   if (n < 0 || n >= (int64_t(1) << 32) - 1) return FGB_E_SIZE;
-  if (W <= 0 || H <= 0 || D <= 0) return FGB_E_SIZE;
+  if (B < 0 || W <= 0 || H <= 0 || D <= 0) return FGB_E_SIZE;
   if (Kw <= 0 || Kh <= 0 || Kd <= 0 || !(Kw & 1) || !(Kh & 1) || !(Kd & 1)) return FGB_E_SIZE;
   if (Dw <= 0 || Dh <= 0 || Dd <= 0) return FGB_E_SIZE;
   const int64_t V = int64_t(Kw) * Kh * Kd;
@@ -498,9 +445,9 @@ extern "C" int fgb_subm_build_neighbor_map(const int32_t* coords, int64_t n, int
   const Grid3 g{W, H, D};
   const Stencil st{Kw, Kh, Kd, Dw, Dh, Dd, static_cast<int>(V)};
   if (key_bits == 32)
-    return build_impl<32>(coords, static_cast<uint32_t>(n), g, st, table, static_cast<uint32_t>(slots), neighbor_map, gray_code,
+    return build_impl<32>(coords, static_cast<uint32_t>(n), B, g, st, table, static_cast<uint32_t>(slots), neighbor_map, gray_code,
                           binary_code, block_counts, valid_signal_seg, status, s);
-  return build_impl<64>(coords, static_cast<uint32_t>(n), g, st, table, static_cast<uint32_t>(slots), neighbor_map, gray_code,
+  return build_impl<64>(coords, static_cast<uint32_t>(n), B, g, st, table, static_cast<uint32_t>(slots), neighbor_map, gray_code,
                         binary_code, block_counts, valid_signal_seg, status, s);
 }
 

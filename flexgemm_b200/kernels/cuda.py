@@ -146,7 +146,7 @@ def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table:
     lib = _cabi.lib()
     dev = coords.device
     n = coords.shape[0]
-    _, _, W, H, D = [int(s) for s in shape]
+    B, _, W, H, D = [int(s) for s in shape]
     V = int(ksize[0]) * int(ksize[1]) * int(ksize[2])
     nblk = _cabi.check_size(lib.fgb_map_num_blocks(n), "fgb_map_num_blocks")
     meta = torch.zeros(V + 2, dtype=torch.uint32, device=dev)
@@ -159,15 +159,15 @@ def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table:
         "meta": meta,
     }
     rc = lib.fgb_subm_build_neighbor_map(
-        _ptr(coords), n, W, H, D, int(ksize[0]), int(ksize[1]), int(ksize[2]),
+        _ptr(coords), n, B, W, H, D, int(ksize[0]), int(ksize[1]), int(ksize[2]),
         int(dilation[0]), int(dilation[1]), int(dilation[2]),
         table.data_ptr(), int(slots), int(key_bits),
         _ptr(out["neighbor_map"]), _ptr(out["gray_code"]), _ptr(out["binary_code"]),
         out["block_offsets"].data_ptr(), meta.data_ptr(),
         meta.data_ptr() + 4 * (V + 1), _stream(dev))
     _cabi.check(rc, "fgb_subm_build_neighbor_map")
-    # table clear, insert, hash lookup, block scan, prefix (+ order check and sorted-input lookup for the 3x3x3 stencil)
-    _count(7 if (tuple(int(k) for k in ksize), tuple(int(d) for d in dilation)) == ((3, 3, 3), (1, 1, 1)) else 5)
+    # order check + column index, table clear, insert, hash lookup, column lookup, block scan, prefix
+    _count(7)
     return out
 
 

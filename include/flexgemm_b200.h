@@ -90,14 +90,18 @@ int64_t fgb_map_num_blocks(int64_t n);
  * bytes; its content on entry is ignored.  slots >= n.  V <= 32.
  *
  * Rows that arrive in ascending flat-index order -- lexicographic (b, x, y, z),
- * without duplicates -- need no table for the 3x3x3, dilation-1 stencil (a
- * row's position is its rank among the keys): a check kernel decides on the
- * device, without a host round trip, whether the map is built from the sorted
- * input itself (each block of rows streams the runs of rows that can hold its
- * neighbours) or by the hash table; the table memory is then left untouched.
- * The map is the same either way. */
+ * without duplicates, batch indices below B -- need no hash table (a row's
+ * position is its rank among the keys, and a (b, x, y) column is a run of
+ * consecutive rows): a kernel checks the order on the device, without a host
+ * round trip, and records where every column starts and ends in a direct-address
+ * table of B*W*H entries of 8 bytes kept in `table`; the lookup then reads the
+ * neighbouring column's entry and searches its few rows.  This path is taken
+ * when B*W*H*8 <= fgb_hash_table_bytes(slots, key_bits); otherwise, and for
+ * unsorted rows, the hash table is built and probed.  The map is the same either
+ * way.  B = number of samples (coords[:,0] < B); B = 0 disables the table-free
+ * path. */
 int fgb_subm_build_neighbor_map(const int32_t* coords, int64_t n,
-                                int W, int H, int D,
+                                int B, int W, int H, int D,
                                 int Kw, int Kh, int Kd,
                                 int Dw, int Dh, int Dd,
                                 void* table, int64_t slots, int key_bits,

@@ -60,11 +60,11 @@ def test_size_queries(lib):
 
 def test_argument_validation_without_launch(lib):
     # all of these return before touching the device
-    assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 2, 3, 3, 1, 1, 1, 0, 20, 32, 0, 0, 0, 0, 0, 0, 0) == -2  # even kernel
-    assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 3, 3, 5, 1, 1, 1, 0, 20, 32, 0, 0, 0, 0, 0, 0, 0) == -2  # V > 32
-    assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 5, 32, 0, 0, 0, 0, 0, 0, 0) == -2   # slots < n
-    assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 20, 48, 0, 0, 0, 0, 0, 0, 0) == -3  # key width
-    assert lib.fgb_subm_build_neighbor_map(0, 10, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 20, 32, 0, 0, 0, 0, 0, 0, 0) == -1  # null seg
+    assert lib.fgb_subm_build_neighbor_map(0, 10, 1, 4, 4, 4, 2, 3, 3, 1, 1, 1, 0, 20, 32, 0, 0, 0, 0, 0, 0, 0) == -2  # even kernel
+    assert lib.fgb_subm_build_neighbor_map(0, 10, 1, 4, 4, 4, 3, 3, 5, 1, 1, 1, 0, 20, 32, 0, 0, 0, 0, 0, 0, 0) == -2  # V > 32
+    assert lib.fgb_subm_build_neighbor_map(0, 10, 1, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 5, 32, 0, 0, 0, 0, 0, 0, 0) == -2   # slots < n
+    assert lib.fgb_subm_build_neighbor_map(0, 10, 1, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 20, 48, 0, 0, 0, 0, 0, 0, 0) == -3  # key width
+    assert lib.fgb_subm_build_neighbor_map(0, 10, 1, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 20, 32, 0, 0, 0, 0, 0, 0, 0) == -1  # null seg
     assert lib.fgb_pp_tile_masks(0, 0, 10, 100, 0, 0) == -2   # not a power of two
     assert lib.fgb_subm_conv_fprop(0, 0, 0, 0, 0, 0, 0, 0, 10, 64, 64, 27, _cabi.F16, 0, 0, 0, 0) == -1
     assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 60, 64, 27, _cabi.F16, 256, 256, 0, 0) == -4  # Ci % 8
