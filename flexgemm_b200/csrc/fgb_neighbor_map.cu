@@ -194,6 +194,9 @@ template <int kKeyBits>
 __global__ void __launch_bounds__(256) column_index_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, uint64_t columns,
                                                           uint2* __restrict__ col_table, uint32_t* unsorted) {
   const uint32_t i = blockIdx.x * 256u + threadIdx.x;
+  // an earlier CTA found the rows out of order: the table will not be used.  (Lane 0's reading decides for the warp:
+  // the word may change between the lanes' loads, and the vote below needs the whole warp.)
+  if (__shfl_sync(0xffffffffu, *reinterpret_cast<volatile uint32_t*>(unsorted), 0) != 0u) return;
   bool bad = false;
   if (i < n) {
     const int4 b = __ldg(&coords[i]);
@@ -249,45 +252,98 @@ __global__ void __launch_bounds__(kMapBlock)
   if (t < nv) s_coord[t] = __ldg(&coords[n0 + t]);
   __syncthreads();
 
+  // An item costs two dependent round trips to L2 -- the column entry, then the z of the column's rows -- so the
+  // loop takes kBatch items at a time and issues the loads of all of them together: first the kBatch column entries,
+  // then the first four rows' z of each column (a surface crosses a column a few times; longer columns are bisected
+  // down to a window first, and walked past the fourth row with further loads).
+  constexpr int kBatch = 3;
+  constexpr int kNoZ = 0x7FFFFFFF;
   const int combos = st.Kw * st.Kh;
   const uint32_t items = nv * combos;
-  for (uint32_t item = t; item < items; item += kMapBlock) {
-    const uint32_t lv = item / combos;
-    const int c = static_cast<int>(item - lv * combos);
-    const int kx = c / st.Kh, ky = c - kx * st.Kh;
-    const int4 me = s_coord[lv];
-    const int x = me.y + (kx - st.Kw / 2) * st.Dw, y = me.z + (ky - st.Kh / 2) * st.Dh;
-    if (x < 0 || x >= g.W || y < 0 || y >= g.H) continue;
-    uint32_t* out = s_nbr + lv * V + c * st.Kd;
-    const bool own_column = kx == st.Kw / 2 && ky == st.Kh / 2;
-    const uint64_t col = (static_cast<uint64_t>(static_cast<uint32_t>(me.x)) * g.W + static_cast<uint32_t>(x)) * g.H + static_cast<uint32_t>(y);
-    const uint2 e = __ldg(&col_table[col]);
-    if (e.x == kInvalid) continue;
-    // first row of the column whose z is not below the smallest target
-    const int z_first = me.w - (st.Kd / 2) * st.Dd;
-    uint32_t lo = e.x, hi = e.y;
-    const uint32_t back = static_cast<uint32_t>((st.Kd / 2) * st.Dd);  // z_first = z - back
-    if (own_column && back <= 8u) {
-      // this voxel's own column: z strictly increases along its rows, so z - back cannot lie more than `back` rows before it
-      const uint32_t self = n0 + lv;
-      lo = self - e.x > back ? self - back : e.x;
-    } else {
-      while (hi - lo > 4u) {  // short columns (a surface crosses a column a few times) are walked from their start
-        const uint32_t mid = lo + ((hi - lo) >> 1);
-        if (__ldg(&coords[mid].w) < z_first) lo = mid + 1;
-        else hi = mid;
+  const uint32_t back = static_cast<uint32_t>((st.Kd / 2) * st.Dd);  // smallest target z = own z - back
+  for (uint32_t item0 = t; item0 < items; item0 += kBatch * kMapBlock) {
+    uint32_t lv[kBatch], lo[kBatch], end[kBatch];
+    int cc[kBatch], zme[kBatch];
+    uint2 ent[kBatch];
+    // column entries
+#pragma unroll
+    for (int q = 0; q < kBatch; ++q) {
+      const uint32_t item = item0 + q * kMapBlock;
+      ent[q] = make_uint2(kInvalid, 0u);
+      lv[q] = 0, cc[q] = 0, zme[q] = 0;
+      if (item < items) {
+        lv[q] = item / combos;
+        cc[q] = static_cast<int>(item - lv[q] * combos);
+        const int kx = cc[q] / st.Kh, ky = cc[q] - kx * st.Kh;
+        const int4 me = s_coord[lv[q]];
+        zme[q] = me.w;
+        const int x = me.y + (kx - st.Kw / 2) * st.Dw, y = me.z + (ky - st.Kh / 2) * st.Dh;
+        if (x >= 0 && x < g.W && y >= 0 && y < g.H) {
+          const uint64_t col = (static_cast<uint64_t>(static_cast<uint32_t>(me.x)) * g.W + static_cast<uint32_t>(x)) * g.H + static_cast<uint32_t>(y);
+          ent[q] = __ldg(&col_table[col]);
+        }
       }
     }
-    uint32_t row = lo;
-    int zr = row < e.y ? __ldg(&coords[row].w) : 0x7FFFFFFF;
-    for (int kz = 0; kz < st.Kd; ++kz) {
-      const int z = z_first + kz * st.Dd;
-      if (z < 0 || z >= g.D) continue;
-      while (zr < z) {
-        ++row;
-        zr = row < e.y ? __ldg(&coords[row].w) : 0x7FFFFFFF;
+    // window start in each column
+#pragma unroll
+    for (int q = 0; q < kBatch; ++q) {
+      lo[q] = ent[q].x, end[q] = ent[q].y;
+      if (ent[q].x == kInvalid) {
+        end[q] = 0u, lo[q] = 0u;  // empty window
+        continue;
       }
-      if (zr == z) out[kz] = row;
+      const int kx = cc[q] / st.Kh, ky = cc[q] - kx * st.Kh;
+      const bool own_column = kx == st.Kw / 2 && ky == st.Kh / 2;
+      if (own_column && back <= 8u) {
+        // the voxel's own column: z strictly increases along its rows, so z - back lies at most `back` rows before it
+        const uint32_t self = n0 + lv[q];
+        lo[q] = self - ent[q].x > back ? self - back : ent[q].x;
+      } else if (end[q] - lo[q] > 4u) {
+        const int z_first = zme[q] - static_cast<int>(back);
+        uint32_t hi = end[q];
+        while (hi - lo[q] > 4u) {
+          const uint32_t mid = lo[q] + ((hi - lo[q]) >> 1);
+          if (__ldg(&coords[mid].w) < z_first) lo[q] = mid + 1;
+          else hi = mid;
+        }
+      }
+    }
+    // z of the first four rows of every window
+    int zr[kBatch][4];
+#pragma unroll
+    for (int q = 0; q < kBatch; ++q) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) zr[q][k] = lo[q] + k < end[q] ? __ldg(&coords[lo[q] + k].w) : kNoZ;
+    }
+    // match the Kd targets (ascending) against the window
+#pragma unroll
+    for (int q = 0; q < kBatch; ++q) {
+      if (lo[q] >= end[q]) continue;
+      uint32_t* out = s_nbr + lv[q] * V + cc[q] * st.Kd;
+      uint32_t row = lo[q] + 4;            // next row to load once the four preloaded ones are used up
+      int zrow = kNoZ;                     // its z (loaded on demand)
+      bool beyond = false;                 // the walk has moved past the preloaded rows
+      for (int kz = 0; kz < st.Kd; ++kz) {
+        const int z = zme[q] - static_cast<int>(back) + kz * st.Dd;
+        if (z < 0 || z >= g.D) continue;
+        if (!beyond) {
+          if (zr[q][0] == z) out[kz] = lo[q];
+          else if (zr[q][1] == z) out[kz] = lo[q] + 1;
+          else if (zr[q][2] == z) out[kz] = lo[q] + 2;
+          else if (zr[q][3] == z) out[kz] = lo[q] + 3;
+          else if (zr[q][3] < z) {         // (kNoZ is never below a target) the target lies further along the column
+            beyond = true;
+            zrow = row < end[q] ? __ldg(&coords[row].w) : kNoZ;
+          }
+        }
+        if (beyond) {
+          while (zrow < z) {
+            ++row;
+            zrow = row < end[q] ? __ldg(&coords[row].w) : kNoZ;
+          }
+          if (zrow == z) out[kz] = row;
+        }
+      }
     }
   }
   __syncthreads();

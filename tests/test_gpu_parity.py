@@ -456,3 +456,20 @@ def test_sharded_backward_on_the_kernels_matches_the_sum_over_shards(K):
         total_w += gw.double().cpu()
         total_b += gb.double().cpu()
     assert rel_err(total_w, ref_gw) <= 1e-2 and rel_err(total_b, ref_gb) <= 1e-2
+
+
+@pytest.mark.parametrize("ksize,dil", [((3, 3, 3), (1, 1, 1)), ((3, 3, 3), (2, 1, 3)), ((1, 1, 5), (1, 1, 1)), ((5, 1, 5), (1, 1, 2)),
+                                       ((3, 1, 3), (1, 2, 9))])
+def test_sorted_input_with_long_columns(ksize, dil, K):
+    """Rows in key order whose (b, x, y) columns are long (a dense slab: up to 48 voxels per
+    column, searched by bisection) next to short and empty ones, for stencils of several
+    extents and dilations -- the table-free path serves every odd stencil."""
+    rng = np.random.default_rng(21)
+    W, H, D = 12, 10, 48
+    dense = np.stack(np.meshgrid(np.arange(3, 9), np.arange(2, 8), np.arange(D), indexing="ij"), -1).reshape(-1, 3)
+    sparse = np.stack(np.meshgrid(np.arange(W), np.arange(H), np.arange(D), indexing="ij"), -1).reshape(-1, 3)
+    sparse = sparse[rng.random(sparse.shape[0]) < 0.07]
+    pts = np.unique(np.concatenate([dense, sparse]), axis=0)            # lexicographic (x, y, z)
+    coords = np.concatenate([np.concatenate([np.full((pts.shape[0], 1), b), pts], axis=1) for b in range(2)]).astype(np.int32)
+    shape = (2, 0, W, H, D)
+    check_cache(build_cache(coords, shape, ksize, dil), orc.neighbor_cache(coords, shape, ksize, dil), ksize[0] * ksize[1] * ksize[2])
