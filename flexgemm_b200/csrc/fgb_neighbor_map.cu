@@ -194,9 +194,6 @@ template <int kKeyBits>
 __global__ void __launch_bounds__(256) column_index_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, uint64_t columns,
                                                           uint2* __restrict__ col_table, uint32_t* unsorted) {
   const uint32_t i = blockIdx.x * 256u + threadIdx.x;
-  // an earlier CTA found the rows out of order: the table will not be used.  (Lane 0's reading decides for the warp:
-  // the word may change between the lanes' loads, and the vote below needs the whole warp.)
-  if (__shfl_sync(0xffffffffu, *reinterpret_cast<volatile uint32_t*>(unsorted), 0) != 0u) return;
   bool bad = false;
   if (i < n) {
     const int4 b = __ldg(&coords[i]);
@@ -231,119 +228,76 @@ __global__ void __launch_bounds__(256) table_clear_kernel(uint32_t* __restrict__
 // (voxel, (kx, ky)) pairs, dealt to the threads round-robin: an item reads the entry of the neighbouring column and
 // walks the column's rows (ascending z) once for the Kd targets z + (kz - Kd/2) * Dd, which ascend with kz.  Hits go
 // into the CTA's map tile in shared memory, which leaves as 16-byte stores.
-template <int kKeyBits>
+//
+// The kernel is bound by instruction issue, not by memory, so the common stencil (3x3x3, dilation 1: kUnit) gets an
+// instance whose extents are compile-time constants (divisions by 9 and 3 become multiplies, the target loop unrolls),
+// and column indices are 32-bit (the table has fewer than 2^32 entries by construction).
+template <int kKeyBits, bool kUnit>
 __global__ void __launch_bounds__(kMapBlock)
     subm_column_lookup_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, Stencil st, const uint2* __restrict__ col_table,
                               uint32_t* __restrict__ nbr, int32_t* __restrict__ gray_out, int32_t* __restrict__ binary_out,
                               uint32_t* __restrict__ block_counts, uint32_t nblk, const uint32_t* __restrict__ unsorted) {
   if (*unsorted != 0u) return;  // the hash kernels build the map
   extern __shared__ __align__(16) uint32_t s_nbr[];  // [kMapBlock * V]
-  __shared__ int4 s_coord[kMapBlock];
+  __shared__ int4 s_coord[kMapBlock];                // (column index, x, y, z)
   __shared__ uint32_t s_count[32];
+  const int Kw = kUnit ? 3 : st.Kw, Kh = kUnit ? 3 : st.Kh, Kd = kUnit ? 3 : st.Kd;
+  const int Dw = kUnit ? 1 : st.Dw, Dh = kUnit ? 1 : st.Dh, Dd = kUnit ? 1 : st.Dd;
+  const int V = kUnit ? 27 : st.V;
   const uint32_t n0 = blockIdx.x * kMapBlock;
   const uint32_t nv = min(static_cast<uint32_t>(kMapBlock), n - n0);
   const int t = threadIdx.x, lane = t & 31;
-  const int V = st.V;
   {
     const uint4 inv = make_uint4(kInvalid, kInvalid, kInvalid, kInvalid);
     for (int i = t; i < kMapBlock * V / 4; i += kMapBlock) reinterpret_cast<uint4*>(s_nbr)[i] = inv;  // kMapBlock * V is a multiple of 4
   }
   if (t < 32) s_count[t] = 0;
-  if (t < nv) s_coord[t] = __ldg(&coords[n0 + t]);
+  if (t < nv) {
+    const int4 c = __ldg(&coords[n0 + t]);
+    const uint32_t col = (static_cast<uint32_t>(c.x) * static_cast<uint32_t>(g.W) + static_cast<uint32_t>(c.y)) * static_cast<uint32_t>(g.H) +
+                         static_cast<uint32_t>(c.z);
+    s_coord[t] = make_int4(static_cast<int>(col), c.y, c.z, c.w);
+  }
   __syncthreads();
 
-  // An item costs two dependent round trips to L2 -- the column entry, then the z of the column's rows -- so the
-  // loop takes kBatch items at a time and issues the loads of all of them together: first the kBatch column entries,
-  // then the first four rows' z of each column (a surface crosses a column a few times; longer columns are bisected
-  // down to a window first, and walked past the fourth row with further loads).
-  constexpr int kBatch = 3;
-  constexpr int kNoZ = 0x7FFFFFFF;
-  const int combos = st.Kw * st.Kh;
+  const int combos = Kw * Kh;
+  const int back = (Kd / 2) * Dd;  // smallest target z = own z - back
   const uint32_t items = nv * combos;
-  const uint32_t back = static_cast<uint32_t>((st.Kd / 2) * st.Dd);  // smallest target z = own z - back
-  for (uint32_t item0 = t; item0 < items; item0 += kBatch * kMapBlock) {
-    uint32_t lv[kBatch], lo[kBatch], end[kBatch];
-    int cc[kBatch], zme[kBatch];
-    uint2 ent[kBatch];
-    // column entries
-#pragma unroll
-    for (int q = 0; q < kBatch; ++q) {
-      const uint32_t item = item0 + q * kMapBlock;
-      ent[q] = make_uint2(kInvalid, 0u);
-      lv[q] = 0, cc[q] = 0, zme[q] = 0;
-      if (item < items) {
-        lv[q] = item / combos;
-        cc[q] = static_cast<int>(item - lv[q] * combos);
-        const int kx = cc[q] / st.Kh, ky = cc[q] - kx * st.Kh;
-        const int4 me = s_coord[lv[q]];
-        zme[q] = me.w;
-        const int x = me.y + (kx - st.Kw / 2) * st.Dw, y = me.z + (ky - st.Kh / 2) * st.Dh;
-        if (x >= 0 && x < g.W && y >= 0 && y < g.H) {
-          const uint64_t col = (static_cast<uint64_t>(static_cast<uint32_t>(me.x)) * g.W + static_cast<uint32_t>(x)) * g.H + static_cast<uint32_t>(y);
-          ent[q] = __ldg(&col_table[col]);
-        }
+  for (uint32_t item = t; item < items; item += kMapBlock) {
+    const uint32_t lv = item / combos;
+    const int c = static_cast<int>(item - lv * combos);
+    const int kx = c / Kh, ky = c - kx * Kh;
+    const int dx = (kx - Kw / 2) * Dw, dy = (ky - Kh / 2) * Dh;
+    const int4 me = s_coord[lv];
+    const int x = me.y + dx, y = me.z + dy;
+    if (x < 0 || x >= g.W || y < 0 || y >= g.H) continue;
+    const uint2 e = __ldg(&col_table[static_cast<uint32_t>(me.x) + static_cast<uint32_t>(dx * g.H + dy)]);
+    if (e.x == kInvalid) continue;
+    uint32_t* out = s_nbr + lv * V + c * Kd;
+    const int z_first = me.w - back;
+    uint32_t lo = e.x;
+    if (dx == 0 && dy == 0 && back <= 8) {
+      // the voxel's own column: z strictly increases along its rows, so z - back lies at most `back` rows before it
+      const uint32_t self = n0 + lv;
+      lo = self - e.x > static_cast<uint32_t>(back) ? self - back : e.x;
+    } else if (e.y - e.x > 4u) {  // short columns (a surface crosses a column a few times) are walked from their start
+      uint32_t hi = e.y;
+      while (hi - lo > 4u) {
+        const uint32_t mid = lo + ((hi - lo) >> 1);
+        if (__ldg(&coords[mid].w) < z_first) lo = mid + 1;
+        else hi = mid;
       }
     }
-    // window start in each column
+    uint32_t row = lo;
+    int zr = __ldg(&coords[row].w);  // lo < e.y: a non-empty column, and bisection keeps lo below its end or at a row that exists
 #pragma unroll
-    for (int q = 0; q < kBatch; ++q) {
-      lo[q] = ent[q].x, end[q] = ent[q].y;
-      if (ent[q].x == kInvalid) {
-        end[q] = 0u, lo[q] = 0u;  // empty window
-        continue;
+    for (int kz = 0; kz < Kd; ++kz) {  // three iterations, unrolled, in the kUnit instance
+      const int z = z_first + kz * Dd;
+      while (zr < z) {
+        ++row;
+        zr = row < e.y ? __ldg(&coords[row].w) : 0x7FFFFFFF;
       }
-      const int kx = cc[q] / st.Kh, ky = cc[q] - kx * st.Kh;
-      const bool own_column = kx == st.Kw / 2 && ky == st.Kh / 2;
-      if (own_column && back <= 8u) {
-        // the voxel's own column: z strictly increases along its rows, so z - back lies at most `back` rows before it
-        const uint32_t self = n0 + lv[q];
-        lo[q] = self - ent[q].x > back ? self - back : ent[q].x;
-      } else if (end[q] - lo[q] > 4u) {
-        const int z_first = zme[q] - static_cast<int>(back);
-        uint32_t hi = end[q];
-        while (hi - lo[q] > 4u) {
-          const uint32_t mid = lo[q] + ((hi - lo[q]) >> 1);
-          if (__ldg(&coords[mid].w) < z_first) lo[q] = mid + 1;
-          else hi = mid;
-        }
-      }
-    }
-    // z of the first four rows of every window
-    int zr[kBatch][4];
-#pragma unroll
-    for (int q = 0; q < kBatch; ++q) {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) zr[q][k] = lo[q] + k < end[q] ? __ldg(&coords[lo[q] + k].w) : kNoZ;
-    }
-    // match the Kd targets (ascending) against the window
-#pragma unroll
-    for (int q = 0; q < kBatch; ++q) {
-      if (lo[q] >= end[q]) continue;
-      uint32_t* out = s_nbr + lv[q] * V + cc[q] * st.Kd;
-      uint32_t row = lo[q] + 4;            // next row to load once the four preloaded ones are used up
-      int zrow = kNoZ;                     // its z (loaded on demand)
-      bool beyond = false;                 // the walk has moved past the preloaded rows
-      for (int kz = 0; kz < st.Kd; ++kz) {
-        const int z = zme[q] - static_cast<int>(back) + kz * st.Dd;
-        if (z < 0 || z >= g.D) continue;
-        if (!beyond) {
-          if (zr[q][0] == z) out[kz] = lo[q];
-          else if (zr[q][1] == z) out[kz] = lo[q] + 1;
-          else if (zr[q][2] == z) out[kz] = lo[q] + 2;
-          else if (zr[q][3] == z) out[kz] = lo[q] + 3;
-          else if (zr[q][3] < z) {         // (kNoZ is never below a target) the target lies further along the column
-            beyond = true;
-            zrow = row < end[q] ? __ldg(&coords[row].w) : kNoZ;
-          }
-        }
-        if (beyond) {
-          while (zrow < z) {
-            ++row;
-            zrow = row < end[q] ? __ldg(&coords[row].w) : kNoZ;
-          }
-          if (zrow == z) out[kz] = row;
-        }
-      }
+      if (zr == z && z >= 0 && z < g.D) out[kz] = row;
     }
   }
   __syncthreads();
@@ -412,8 +366,13 @@ static int build_impl(const int32_t* coords, uint32_t n, int B, Grid3 g, Stencil
                                                                 nblk, unsorted);
   if (try_sorted) {
     const size_t smem = size_t(kMapBlock) * st.V * sizeof(uint32_t);
-    subm_column_lookup_kernel<kKeyBits><<<nblk, kMapBlock, smem, s>>>(c4, n, g, st, static_cast<const uint2*>(table), nbr, gray, binary,
-                                                                     block_counts, nblk, unsorted);
+    const bool unit = st.Kw == 3 && st.Kh == 3 && st.Kd == 3 && st.Dw == 1 && st.Dh == 1 && st.Dd == 1;
+    if (unit)
+      subm_column_lookup_kernel<kKeyBits, true><<<nblk, kMapBlock, smem, s>>>(c4, n, g, st, static_cast<const uint2*>(table), nbr, gray, binary,
+                                                                             block_counts, nblk, unsorted);
+    else
+      subm_column_lookup_kernel<kKeyBits, false><<<nblk, kMapBlock, smem, s>>>(c4, n, g, st, static_cast<const uint2*>(table), nbr, gray,
+                                                                              binary, block_counts, nblk, unsorted);
   }
   block_scan_kernel<<<st.V, 1024, 0, s>>>(block_counts, nblk, seg);
   seg_prefix_kernel<<<1, 32, 0, s>>>(seg, st.V);
