@@ -35,6 +35,12 @@ inline int elem_bytes(int dtype) {
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// fprop / dgrad of a small input (fewer work items than SMs) split every item's offsets into shares that run as
+// separate items into fp32 slabs (fgb_igemm.cu): the number of shares for n output rows x nout channels on the current
+// device, and the bytes of the slabs (0 when the launch is not split).  The workspace sizes are built from these.
+int igemm_splits(int64_t n, int nout, int V);
+int64_t igemm_partial_bytes(int64_t n, int nout, int V);
+
 #ifdef __CUDACC__
 // Murmur3 finalisers: the hash of every table in the library
 __device__ __forceinline__ uint32_t fmix32(uint32_t k) {

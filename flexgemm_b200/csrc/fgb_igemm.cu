@@ -77,6 +77,8 @@ struct IgemmParams {
   int V;
   int bn;                    // output channels per work item (32, 64, 128, 256)
   int n_tiles_n;
+  int splits;                // split-K: shares of a block's offsets that run as separate work items (1 = off)
+  int items_per_block;       // n_tiles_n * splits
   int row_bytes;             // kc * element size
   int num_kb;                // 128-byte slices per row
   int flip;                  // weight slot = flip ? V-1-v : v
@@ -101,7 +103,7 @@ struct IgemmSmem {
   uint64_t acc_empty[2];
   uint64_t sched_full[kSchedRing];   // work entry published
   uint64_t sched_empty[kSchedRing];  // work entry read by every role
-  uint32_t sched_entry[kSchedRing];  // block * n_tiles_n + column tile, or kInvalid = no more work
+  uint32_t sched_entry[kSchedRing];  // block * items_per_block + (column tile * splits + split), or kInvalid = no more work
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -195,11 +197,20 @@ __device__ __forceinline__ uint4 fuse_piece(uint4 val, int act, const char* resi
   return o;
 }
 
-template <int kDtype, bool kFused>
+// kMode: kPlain -- the epilogue adds the bias and writes `out` in the operand type; kFusedEp -- the same plus
+// activation / residual / pre-activation copy; kSplitK -- the work item covers only a share of the block's offsets and
+// the epilogue writes the raw fp32 accumulators into its split's slab of a partial buffer (summed by a second kernel).
+enum { kPlain = 0, kFusedEp = 1, kSplitK = 2 };
+
+template <int kDtype, int kMode>
 __global__ void __launch_bounds__(kIgemmThreads, 1)
     subm_igemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const IgemmParams p, const FusedEpilogue fe) {
   constexpr bool kTF32 = (kDtype == FGB_F32_TF32);
+  constexpr bool kFused = kMode == kFusedEp;
+  constexpr bool kSplit = kMode == kSplitK;
   constexpr int kElem = (kDtype == FGB_F16 || kDtype == FGB_BF16) ? 2 : 4;
+  constexpr int kOutDtype = kSplit ? FGB_F32_TF32 : kDtype;  // element type the epilogue writes
+  constexpr int kElemOut = kSplit ? 4 : kElem;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // dynamic shared memory is only guaranteed 16-byte aligned: align by hand
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -256,14 +267,14 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
   auto publish_work = [&](uint32_t k, uint32_t& pub_block, uint32_t& pub_ntile) {  // one thread
     const uint32_t slot = k % kSchedRing;
     mbar_wait(&ctl->sched_empty[slot], ((k / kSchedRing) & 1) ^ 1, abort_flag);
-    if (pub_block != kInvalid && ++pub_ntile >= static_cast<uint32_t>(p.n_tiles_n)) pub_ntile = 0;
+    if (pub_block != kInvalid && ++pub_ntile >= static_cast<uint32_t>(p.items_per_block)) pub_ntile = 0;
     if (pub_block == kInvalid || pub_ntile == 0) {
       const uint32_t t = atomicAdd(p.ticket, 1u);
       pub_block = t < p.num_blocks ? (p.block_order != nullptr ? __ldg(&p.block_order[t]) : t) : none;
       pub_ntile = 0;
       if (pub_block == kInvalid) pub_ntile = 0xFFFFFFFFu;  // stays "no more work"
     }
-    ctl->sched_entry[slot] = (pub_block == none || *abort_flag) ? none : pub_block * p.n_tiles_n + pub_ntile;
+    ctl->sched_entry[slot] = (pub_block == none || *abort_flag) ? none : pub_block * p.items_per_block + pub_ntile;
     mbar_arrive(&ctl->sched_full[slot]);
   };
   // k-th work item of this CTA; every reader (a whole warp, or a single lane when
@@ -275,14 +286,29 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     if (!one_lane) __syncwarp();
     if (one_lane || lane == 0) mbar_arrive(&ctl->sched_empty[slot]);
     if (e == kInvalid) return false;
-    mblk = p.n_tiles_n == 1 ? e : e / p.n_tiles_n;  // once per work item
-    ntile = e - mblk * p.n_tiles_n;
+    mblk = p.items_per_block == 1 ? e : e / p.items_per_block;  // once per work item
+    ntile = e - mblk * p.items_per_block;  // column tile * splits + split
     return true;
   };
-  auto masks_of = [&](uint32_t mblk, uint32_t& m0, uint32_t& m1) {
+  // column tile and split of a work item's sub-index
+  auto tile_of = [&](uint32_t sub) -> uint32_t { return kSplit ? sub / static_cast<uint32_t>(p.splits) : sub; };
+  auto split_of = [&](uint32_t sub) -> uint32_t { return kSplit ? sub % static_cast<uint32_t>(p.splits) : 0u; };
+  // Offset masks of the two halves of a work item.  With split-K the item keeps only its share of the block's
+  // offsets: the set bits of the union mask, in ascending order, are dealt to the splits in equal runs (a split beyond
+  // the number of offsets gets none and writes zeros).  Every role derives the same masks from the same words.
+  auto masks_of = [&](uint32_t mblk, uint32_t sub, uint32_t& m0, uint32_t& m1) {
     const uint32_t t0 = mblk * 2;
     m0 = __ldg(&p.tile_masks[t0]);
     m1 = t0 + 1 < p.num_tiles ? __ldg(&p.tile_masks[t0 + 1]) : 0u;
+    if constexpr (kSplit) {
+      const uint32_t un = m0 | m1, count = __popc(un), sp = split_of(sub), S = static_cast<uint32_t>(p.splits);
+      const uint32_t first = sp * count / S, last = (sp + 1) * count / S;
+      uint32_t keep = 0, rank = 0;
+      for (uint32_t u = un; u != 0u; u &= u - 1u, ++rank) {
+        if (rank >= first && rank < last) keep |= u & (0u - u);
+      }
+      m0 &= keep, m1 &= keep;
+    }
   };
 
   if (warp >= kGatherWarp0 && warp < kEpilogueWarp1) {
@@ -321,7 +347,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     if (publisher) publish_work(0, pub_block, pub_ntile);
     bool has_work = work_of(0, mblk, ntile, false);
     if (has_work) {
-      masks_of(mblk, m0, m1);
+      masks_of(mblk, ntile, m0, m1);
       load_rows(mblk, rows);
       if (m0 | m1) load_idx(rows, __ffs(m0 | m1) - 1, m0, m1, nidx);
     }
@@ -335,7 +361,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
         if (publisher) publish_work(pass + 1, pub_block, pub_ntile);
         has_next = work_of(pass + 1, mblk_n, ntile_n, false);
         if (has_next) {
-          masks_of(mblk_n, nm0, nm1);
+          masks_of(mblk_n, ntile_n, nm0, nm1);
           load_rows(mblk_n, nrows);
         }
         claimed = true;
@@ -387,9 +413,9 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
       uint32_t s = 0, ph = 0;
       uint32_t mblk = 0, ntile = 0;
       for (uint32_t pass = 0; work_of(pass, mblk, ntile, true); ++pass) {
-        const int n0 = static_cast<int>(ntile) * p.bn;
+        const int n0 = static_cast<int>(tile_of(ntile)) * p.bn;
         uint32_t m0, m1;
-        masks_of(mblk, m0, m1);
+        masks_of(mblk, ntile, m0, m1);
         uint32_t un = m0 | m1;
         while (un) {
           const int v = __ffs(un) - 1;
@@ -412,7 +438,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
       uint32_t mblk = 0, ntile = 0;
       for (; work_of(item, mblk, ntile, true); ++item) {
         uint32_t m0, m1;
-        masks_of(mblk, m0, m1);
+        masks_of(mblk, ntile, m0, m1);
         const uint32_t acc_tmem = tmem_base + set * 2 * p.bn;
         // the epilogue must have drained this accumulator pair
         mbar_wait(&ctl->acc_empty[set], set_ph ^ 1, abort_flag);
@@ -464,15 +490,17 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     const int quarter = warp & 3;
     const int group = warp >= kEpilogueWarp1 ? 1 : 0;
     uint8_t* stage_out = smem + kCtrlBytes + size_t(S) * stage_bytes + (group * 4 + quarter) * 4096;
-    constexpr int kColsPerPass = 4096 / 32 / kElem;  // 64 columns of 16-bit, 32 columns of fp32: 128 bytes per row
+    constexpr int kColsPerPass = 4096 / 32 / kElemOut;  // 64 columns of 16-bit, 32 columns of fp32: 128 bytes per row
     constexpr int kChunksPerPass = kColsPerPass / 32 > 0 ? kColsPerPass / 32 : 1;
     uint32_t item = 0;
     uint32_t set = 0, set_ph = 0;
     uint32_t mblk = 0, ntile = 0;
     for (; work_of(item, mblk, ntile, false); ++item) {
-      const int n0 = static_cast<int>(ntile) * p.bn;
+      const int n0 = static_cast<int>(tile_of(ntile)) * p.bn;
       uint32_t m0, m1;
-      masks_of(mblk, m0, m1);
+      masks_of(mblk, ntile, m0, m1);
+      // split-K: this item's slab [n, nout] of fp32 partial sums
+      char* const out_base = kSplit ? p.out + size_t(split_of(ntile)) * p.n * p.nout * 4 : p.out;
       uint32_t sr[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -499,12 +527,12 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
           }
 #pragma unroll
           for (int cc = 0; cc < kChunksPerPass; ++cc)
-            stage_row_chunk<kDtype>(stage_out, lane, cc, acc[cc], p.bias, n0 + c0 + cc * 32, p.nout);
+            stage_row_chunk<kOutDtype>(stage_out, lane, cc, acc[cc], kSplit ? nullptr : p.bias, n0 + c0 + cc * 32, p.nout);
           __syncwarp();
           {
             // 128 bytes per row: lane -> (row = 4 i + lane / 8, piece = lane % 8)
             const int piece = lane & 7;
-            const int col = n0 + c0 + piece * (16 / kElem);
+            const int col = n0 + c0 + piece * (16 / kElemOut);
             const bool col_ok = col < p.nout;
             const uint8_t* src = stage_out + (lane >> 3) * 128;
 #pragma unroll
@@ -514,11 +542,11 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
               const uint4 val = *reinterpret_cast<const uint4*>(src + i * 512 + ((piece ^ (row & 7)) << 4));
               if constexpr (kFused) {
                 if (orow != kInvalid && col_ok) {
-                  const size_t byte_off = (size_t(orow) * p.nout + col) * kElem;
-                  *reinterpret_cast<uint4*>(p.out + byte_off) = fuse_piece<kDtype>(val, fe.act, fe.residual, fe.preact, byte_off);
+                  const size_t byte_off = (size_t(orow) * p.nout + col) * kElemOut;
+                  *reinterpret_cast<uint4*>(out_base + byte_off) = fuse_piece<kDtype>(val, fe.act, fe.residual, fe.preact, byte_off);
                 }
               } else {
-                if (orow != kInvalid && col_ok) *reinterpret_cast<uint4*>(p.out + (size_t(orow) * p.nout + col) * kElem) = val;
+                if (orow != kInvalid && col_ok) *reinterpret_cast<uint4*>(out_base + (size_t(orow) * p.nout + col) * kElemOut) = val;
               }
             }
           }
@@ -633,32 +661,81 @@ static int pick_bn(int nout) {
 // registers), so a kernel launched beside them would otherwise wait for the first of them to finish.
 static std::atomic<int> g_cta_limit{0};
 
-template <int kDtype, bool kFused>
+template <int kDtype, int kMode>
 static int launch_igemm_variant(const CUtensorMap& tmap, const IgemmParams& p, const FusedEpilogue& fe, cudaStream_t s) {
   const size_t smem = 1024 + kCtrlBytes + size_t(p.stages) * (2 * kATileBytes + p.bn * 128) + kStoreStageBytes;
   static PerDeviceTable configured;  // the attribute belongs to (kernel instance, device)
-  const int rc = ensure_dynamic_smem(configured, subm_igemm_kernel<kDtype, kFused>, smem);
+  const int rc = ensure_dynamic_smem(configured, subm_igemm_kernel<kDtype, kMode>, smem);
   if (rc != FGB_OK) return rc;
-  const int64_t work = int64_t(p.num_blocks) * p.n_tiles_n;
+  const int64_t work = int64_t(p.num_blocks) * p.items_per_block;
   int ctas = device_sm_count();
   const int limit = g_cta_limit.load(std::memory_order_relaxed);
   if (limit > 0 && limit < ctas) ctas = limit;
   const unsigned grid = static_cast<unsigned>(work < ctas ? work : ctas);
-  subm_igemm_kernel<kDtype, kFused><<<grid, kIgemmThreads, smem, s>>>(tmap, p, fe);
+  subm_igemm_kernel<kDtype, kMode><<<grid, kIgemmThreads, smem, s>>>(tmap, p, fe);
   return launch_status();
 }
 
 // the plain kernel carries no trace of the fused epilogue (its register allocation is the tuned one)
 template <int kDtype>
 static int launch_igemm(const CUtensorMap& tmap, const IgemmParams& p, const FusedEpilogue& fe, cudaStream_t s) {
-  if (fe.act != FGB_ACT_NONE || fe.residual != nullptr || fe.preact != nullptr) return launch_igemm_variant<kDtype, true>(tmap, p, fe, s);
-  return launch_igemm_variant<kDtype, false>(tmap, p, fe, s);
+  if (p.splits > 1) return launch_igemm_variant<kDtype, kSplitK>(tmap, p, fe, s);
+  if (fe.act != FGB_ACT_NONE || fe.residual != nullptr || fe.preact != nullptr) return launch_igemm_variant<kDtype, kFusedEp>(tmap, p, fe, s);
+  return launch_igemm_variant<kDtype, kPlain>(tmap, p, fe, s);
+}
+
+// ------------------------------------------------------------------ split-K for small inputs
+// A launch with fewer work items (row blocks x column tiles) than SMs leaves most of the device idle: each item walks
+// up to V offsets x kc/64 slices on its own.  Then every item is cut into `splits` shares of its offsets, the shares
+// run as separate work items into fp32 slabs, and a second kernel adds the slabs in a fixed order, adds the bias and
+// converts.  (The reference splits the same way when tiles * SPLITK < number of SMs:
+// sparse_submanifold_conv_fwd_masked_implicit_gemm_splitk.py:109-121.)
+static std::atomic<int> g_force_splits{0};  // 0 = by the rule below, 1 = never split, k = k shares (capped at V)
+
+int igemm_splits(int64_t n, int nout, int V) {
+  if (n <= 0) return 1;
+  const int forced = g_force_splits.load(std::memory_order_relaxed);
+  if (forced > 0) return forced < V ? forced : V;
+  const int64_t items = ceil_div(n, kBlockM) * ceil_div(nout, pick_bn(nout));
+  const int64_t sms = device_sm_count();
+  if (items * 2 > sms) return 1;
+  int64_t sp = sms / items;
+  if (sp > V) sp = V;
+  return static_cast<int>(sp < 1 ? 1 : sp);
+}
+int64_t igemm_partial_bytes(int64_t n, int nout, int V) {
+  const int sp = igemm_splits(n, nout, V);
+  return sp > 1 ? align256(int64_t(sp) * n * nout * 4) : 0;
+}
+
+// out[r, c] = sum_s partial[s, r, c] (+ bias[c]) in split order, converted to T
+template <typename T>
+__global__ void __launch_bounds__(256) splitk_rows_reduce_kernel(const float* __restrict__ partial, int splits, int64_t elems, int nout,
+                                                                 const T* __restrict__ bias, T* __restrict__ out) {
+  const int64_t e = (blockIdx.x * int64_t(256) + threadIdx.x) * 4;
+  if (e >= elems) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int sp = 0; sp < splits; ++sp) {
+    const float4 t = __ldg(reinterpret_cast<const float4*>(partial + size_t(sp) * elems + e));
+    acc.x += t.x, acc.y += t.y, acc.z += t.z, acc.w += t.w;
+  }
+  float v[4] = {acc.x, acc.y, acc.z, acc.w};
+  const int c = static_cast<int>(e % nout);  // nout is a multiple of 4: the four values share a row
+  T o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    // same roundings as the unsplit epilogue: 16-bit types round the sum, then add the bias in the type
+    if constexpr (std::is_same<T, float>::value) o[i] = v[i] + (bias ? bias[c + i] : 0.f);
+    else o[i] = bias ? static_cast<T>(static_cast<T>(v[i]) + bias[c + i]) : static_cast<T>(v[i]);
+  }
+  if constexpr (std::is_same<T, float>::value) *reinterpret_cast<float4*>(out + e) = make_float4(o[0], o[1], o[2], o[3]);
+  else *reinterpret_cast<uint2*>(out + e) = *reinterpret_cast<const uint2*>(o);
 }
 
 // x [n, kc] gathered through nbr; w [nout, V, kc]; out [n, nout]
 int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nbr, const int64_t* sorted_idx,
               const uint32_t* tile_masks, const uint32_t* block_order, uint32_t* ticket, void* out, int64_t n, int kc, int nout, int V, int dtype, int flip, int32_t* status,
-              cudaStream_t s, int act = FGB_ACT_NONE, const void* residual = nullptr, void* preact = nullptr) {
+              cudaStream_t s, float* partial = nullptr, int act = FGB_ACT_NONE, const void* residual = nullptr, void* preact = nullptr) {
   const int eb = elem_bytes(dtype);
   if (eb == 0 || dtype == FGB_F32_IEEE) return FGB_E_DTYPE;  // callers expand fp32-accurate mode to TF32 operands
   if (n < 0 || n >= (int64_t(1) << 32) - 1 || kc <= 0 || nout <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
@@ -688,6 +765,11 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   p.V = V;
   p.bn = pick_bn(nout);
   p.n_tiles_n = static_cast<int>(ceil_div(nout, p.bn));
+  // split-K when the caller gave room for the partial sums and the plain epilogue is asked for
+  const bool fused = act != FGB_ACT_NONE || residual != nullptr || preact != nullptr;
+  p.splits = (partial != nullptr && !fused) ? igemm_splits(n, nout, V) : 1;
+  p.items_per_block = p.n_tiles_n * p.splits;
+  if (p.splits > 1) p.out = reinterpret_cast<char*>(partial);
   p.row_bytes = kc * eb;
   p.num_kb = static_cast<int>(ceil_div(p.row_bytes, 128));
   p.flip = flip;
@@ -708,12 +790,29 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   if (rc != FGB_OK) return rc;
   switch (dtype) {
     case FGB_F16:
-      return launch_igemm<FGB_F16>(tmap, p, fe, s);
+      rc = launch_igemm<FGB_F16>(tmap, p, fe, s);
+      break;
     case FGB_BF16:
-      return launch_igemm<FGB_BF16>(tmap, p, fe, s);
+      rc = launch_igemm<FGB_BF16>(tmap, p, fe, s);
+      break;
     default:
-      return launch_igemm<FGB_F32_TF32>(tmap, p, fe, s);
+      rc = launch_igemm<FGB_F32_TF32>(tmap, p, fe, s);
   }
+  if (rc != FGB_OK || p.splits == 1) return rc;
+  const int64_t elems = n * nout;
+  const unsigned grid = static_cast<unsigned>(ceil_div(elems, 1024));
+  switch (dtype) {
+    case FGB_F16:
+      splitk_rows_reduce_kernel<__half><<<grid, 256, 0, s>>>(partial, p.splits, elems, nout, static_cast<const __half*>(bias), static_cast<__half*>(out));
+      break;
+    case FGB_BF16:
+      splitk_rows_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(partial, p.splits, elems, nout, static_cast<const __nv_bfloat16*>(bias),
+                                                                    static_cast<__nv_bfloat16*>(out));
+      break;
+    default:
+      splitk_rows_reduce_kernel<float><<<grid, 256, 0, s>>>(partial, p.splits, elems, nout, static_cast<const float*>(bias), static_cast<float*>(out));
+  }
+  return launch_status();
 }
 
 }  // namespace fgb
@@ -723,6 +822,11 @@ extern "C" int fgb_conv_tile_rows(void) { return fgb::kTileM; }
 extern "C" int fgb_conv_set_cta_limit(int max_ctas) {
   if (max_ctas < 0) return FGB_E_SIZE;
   return fgb::g_cta_limit.exchange(max_ctas, std::memory_order_relaxed);
+}
+
+extern "C" int fgb_conv_set_splitk(int splits) {
+  if (splits < 0 || splits > 32) return FGB_E_SIZE;
+  return fgb::g_force_splits.exchange(splits, std::memory_order_relaxed);
 }
 
 extern "C" int fgb_conv_block_schedule(const uint32_t* tile_masks, int64_t num_tiles, uint32_t* block_order, void* stream) {
@@ -754,22 +858,27 @@ static int fprop_impl(const void* feats, const void* weight, const void* bias, c
   if (workspace_bytes < kWsHeader) return FGB_E_WORKSPACE;
   uint32_t* ticket = static_cast<uint32_t*>(workspace);
   char* scratch = static_cast<char*>(workspace) + kWsHeader;
-  if (dtype != FGB_F32_IEEE)
-    return run_igemm(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, ticket, out, n, Ci, Co, V, dtype, 0, status, s, act,
-                     residual, preact);
+  const bool fused = act != FGB_ACT_NONE || residual != nullptr || preact != nullptr;  // the fused epilogue is never split
+  const int64_t part_bytes = fused ? 0 : igemm_partial_bytes(n, Co, V);
+  if (dtype != FGB_F32_IEEE) {
+    if (workspace_bytes < kWsHeader + part_bytes) return FGB_E_WORKSPACE;
+    return run_igemm(feats, weight, bias, neighbor_map, sorted_idx, tile_masks, block_order, ticket, out, n, Ci, Co, V, dtype, 0, status, s,
+                     part_bytes ? reinterpret_cast<float*>(scratch) : nullptr, act, residual, preact);
+  }
   // fp32-accurate: one TF32 run over the tripled channel dimension
   if (!feats || !weight) return FGB_E_NULL;
   const int64_t x_bytes = align256(n_src * 3 * Ci * 4), w_bytes = align256(int64_t(Co) * V * 3 * Ci * 4);
-  if (workspace_bytes < kWsHeader + x_bytes + w_bytes) return FGB_E_WORKSPACE;
+  if (workspace_bytes < kWsHeader + x_bytes + w_bytes + part_bytes) return FGB_E_WORKSPACE;
   float* x3 = reinterpret_cast<float*>(scratch);
   float* w3 = reinterpret_cast<float*>(scratch + x_bytes);
+  float* part = part_bytes ? reinterpret_cast<float*>(scratch + x_bytes + w_bytes) : nullptr;
   int rc = FGB_OK;
   if (n_src > 0) rc = launch_split3(static_cast<const float*>(feats), x3, n_src, Ci, kSplitActivations, s);
   if (rc != FGB_OK) return rc;
   rc = launch_split3(static_cast<const float*>(weight), w3, int64_t(Co) * V, Ci, kSplitWeights, s);
   if (rc != FGB_OK) return rc;
-  return run_igemm(x3, w3, bias, neighbor_map, sorted_idx, tile_masks, block_order, ticket, out, n, 3 * Ci, Co, V, FGB_F32_TF32, 0, status, s, act,
-                   residual, preact);
+  return run_igemm(x3, w3, bias, neighbor_map, sorted_idx, tile_masks, block_order, ticket, out, n, 3 * Ci, Co, V, FGB_F32_TF32, 0, status, s,
+                   part, act, residual, preact);
 }
 
 }  // namespace fgb
@@ -817,7 +926,9 @@ static int dgrad_impl(const void* grad_out, const void* weight, const uint32_t* 
   const bool ieee = dtype == FGB_F32_IEEE;
   const int64_t w3_bytes = ieee ? align256(int64_t(Ci) * V * 3 * Co * 4) : 0;
   const int64_t g3_bytes = ieee ? align256(n_src * 3 * Co * 4) : 0;
-  if (workspace_bytes < kWsHeader + wt_bytes + w3_bytes + g3_bytes) return FGB_E_WORKSPACE;
+  const int64_t part_bytes = igemm_partial_bytes(n, Ci, V);
+  if (workspace_bytes < kWsHeader + wt_bytes + w3_bytes + g3_bytes + part_bytes) return FGB_E_WORKSPACE;
+  float* part = part_bytes ? reinterpret_cast<float*>(static_cast<char*>(workspace) + kWsHeader + wt_bytes + w3_bytes + g3_bytes) : nullptr;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint32_t* ticket = static_cast<uint32_t*>(workspace);
   char* wt = static_cast<char*>(workspace) + kWsHeader;
@@ -830,7 +941,7 @@ static int dgrad_impl(const void* grad_out, const void* weight, const uint32_t* 
   if (rc != FGB_OK) return rc;
   if (!ieee)
     return run_igemm(grad_out, wt, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, ticket, grad_feats, n, Co, Ci, V, dtype,
-                     mirror, status, s);
+                     mirror, status, s, part);
   if (!grad_out) return FGB_E_NULL;
   float* w3 = reinterpret_cast<float*>(wt + wt_bytes);
   float* g3 = reinterpret_cast<float*>(wt + wt_bytes + w3_bytes);
@@ -839,7 +950,7 @@ static int dgrad_impl(const void* grad_out, const void* weight, const uint32_t* 
   if (n_src > 0) rc = launch_split3(static_cast<const float*>(grad_out), g3, n_src, Co, kSplitActivations, s);
   if (rc != FGB_OK) return rc;
   return run_igemm(g3, w3, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, ticket, grad_feats, n, 3 * Co, Ci, V, FGB_F32_TF32,
-                   mirror, status, s);
+                   mirror, status, s, part);
 }
 
 }  // namespace fgb

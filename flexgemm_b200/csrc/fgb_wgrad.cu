@@ -632,10 +632,11 @@ extern "C" int64_t fgb_sparse_conv_workspace_bytes(int pass, int64_t n_out, int6
   const int64_t w_elems = int64_t(Ci) * V * Co;
   const bool ieee = dtype == FGB_F32_IEEE;
   switch (pass) {
-    case 0:  // header with the ticket counter (+ fp32-accurate mode: tripled activations and weights)
-      return 256 + (ieee ? align256(n_in * 3 * Ci * 4) + align256(w_elems * 3 * 4) : 0);
-    case 1:  // header, re-laid-out weight (+ its tripled copy and the tripled grad_out)
-      return 256 + align256(w_elems * eb) + (ieee ? align256(w_elems * 3 * 4) + align256(n_out * 3 * Co * 4) : 0);
+    case 0:  // header with the ticket counter (+ fp32-accurate mode: tripled activations and weights; + split-K slabs of a small launch)
+      return 256 + (ieee ? align256(n_in * 3 * Ci * 4) + align256(w_elems * 3 * 4) : 0) + igemm_partial_bytes(n_out, Co, V);
+    case 1:  // header, re-laid-out weight (+ its tripled copy and the tripled grad_out; + split-K slabs)
+      return 256 + align256(w_elems * eb) + (ieee ? align256(w_elems * 3 * 4) + align256(n_out * 3 * Co * 4) : 0) +
+             igemm_partial_bytes(n_in, Ci, V);
     case 2:  // slabs [Co, Ci] for up to (splitk + 1) * V units (+ hi/lo copies of both operands)
       if (splitk < 1 || splitk > 1024) return FGB_E_SIZE;
       return align256(w_elems * 4 * (int64_t(splitk) + 1)) + (ieee ? 2 * align256(n_in * Ci * 4) + 2 * align256(n_out * Co * 4) : 0);

@@ -381,6 +381,14 @@ def set_wgrad_row_bands(bands: int) -> int:
     return prev
 
 
+def set_conv_splitk(splits: int) -> int:
+    """Split-K of fprop / dgrad: 0 = automatic (small launches only), 1 = off, k = k shares; returns the previous setting."""
+    prev = _cabi.lib().fgb_conv_set_splitk(int(splits))
+    if prev < 0:
+        _cabi.check(prev, "fgb_conv_set_splitk")
+    return prev
+
+
 def set_conv_cta_limit(max_ctas: int) -> int:
     """Cap the CTAs (SMs) of the persistent fprop / dgrad kernels launched from now
     on (0 = no cap); returns the previous cap."""
@@ -453,7 +461,7 @@ def conv_fprop(feats, weight_cvc, bias, neighbor_map, sorted_idx, masks, order=N
                                        _ptr(masks), _ptr(order), _ptr(out), n, n_in, Ci, Co, V, code, ws.data_ptr(),
                                        ws.numel() * 8, status_word(dev).data_ptr(), _stream(dev))
         _cabi.check(rc, "fgb_sparse_conv_fprop")
-    _count(1)
+    _count(1)   # (+ the slab reduction of a split launch, not counted)
     return out
 
 

@@ -173,6 +173,18 @@ int fgb_conv_tile_rows(void);
  * Process-wide; read when a kernel is launched. */
 int fgb_conv_set_cta_limit(int max_ctas);
 
+/* Split-K of fprop / dgrad.  A launch with fewer work items (256-row blocks x
+ * column tiles) than half the SMs cuts every item into shares of its offsets that
+ * run as separate items into fp32 slabs in the workspace; a second kernel adds
+ * the slabs in a fixed order, adds the bias and converts (deterministic).  This
+ * setting overrides the rule: 0 = automatic (as many shares as SMs per item, at
+ * most V), 1 = never split, k = k shares.  Returns the previous value.
+ * Process-wide; read when workspace sizes are computed and when a kernel is
+ * launched, so change it between calls, not between the size query and the call.
+ * Stands in for the SPLITK heuristic of the reference's kernels
+ * (sparse_submanifold_conv_fwd_masked_implicit_gemm_splitk.py:109-121). */
+int fgb_conv_set_splitk(int splits);
+
 /* block_order (uint32 [ceil(num_tiles / 2)]) = the 256-row blocks (pairs of
  * consecutive 128-row tiles) in descending order of work, computed from the tile
  * masks.  The persistent conv kernels deal blocks to the SMs from this list so
@@ -191,8 +203,9 @@ int fgb_conv_block_schedule(const uint32_t* tile_masks, int64_t num_tiles,
  * (flex_gemm/kernels/triton/spconv/
  *  sparse_submanifold_conv_fwd_masked_implicit_gemm_splitk.py:21-172).
  * `workspace`: fgb_conv_workspace_bytes(0, ...) bytes, 256-byte aligned (it holds
- * the work counter of the persistent kernel, and the split operands for
- * FGB_F32_IEEE). */
+ * the work counter of the persistent kernel, the split operands for
+ * FGB_F32_IEEE, and the fp32 slabs of a split-K launch, see
+ * fgb_conv_set_splitk). */
 int fgb_subm_conv_fprop(const void* feats, const void* weight, const void* bias,
                         const uint32_t* neighbor_map, const int64_t* sorted_idx,
                         const uint32_t* tile_masks, const uint32_t* block_order,

@@ -50,9 +50,13 @@ def test_size_queries(lib):
     assert lib.fgb_map_num_blocks(0) == 0
     assert lib.fgb_map_num_blocks(257) == 2
     assert lib.fgb_conv_tile_rows() == 128
-    assert lib.fgb_conv_workspace_bytes(0, 1000, 64, 64, 27, _cabi.F16, 1) == 256
-    assert lib.fgb_conv_workspace_bytes(0, 1000, 64, 64, 27, _cabi.F32_IEEE, 1) == 256 + 1000 * 3 * 64 * 4 + 64 * 64 * 27 * 3 * 4
-    assert lib.fgb_conv_workspace_bytes(1, 1000, 64, 32, 27, _cabi.F16, 1) == 256 + 64 * 32 * 27 * 2
+    n = 100000   # enough row blocks for every SM: no split-K slabs in the fprop / dgrad workspaces
+    assert lib.fgb_conv_workspace_bytes(0, n, 64, 64, 27, _cabi.F16, 1) == 256
+    assert lib.fgb_conv_workspace_bytes(0, n, 64, 64, 27, _cabi.F32_IEEE, 1) == 256 + n * 3 * 64 * 4 + 64 * 64 * 27 * 3 * 4
+    assert lib.fgb_conv_workspace_bytes(1, n, 64, 32, 27, _cabi.F16, 1) == 256 + 64 * 32 * 27 * 2
+    # a launch with fewer work items than SMs is split over the offsets: room for the fp32 slabs [splits, n, Co]
+    small = lib.fgb_conv_workspace_bytes(0, 1000, 64, 64, 27, _cabi.F16, 1) - 256
+    assert small > 0 and small % (1000 * 64 * 4) == 0 and 2 <= small // (1000 * 64 * 4) <= 27
     assert lib.fgb_conv_workspace_bytes(2, 1000, 64, 32, 27, _cabi.F16, 4) == 64 * 32 * 27 * 4 * 5
     assert lib.fgb_conv_workspace_bytes(2, 1000, 64, 32, 27, 9, 4) < 0
     assert lib.fgb_bias_grad_workspace_bytes(256) > 0
@@ -67,8 +71,9 @@ def test_argument_validation_without_launch(lib):
     assert lib.fgb_subm_build_neighbor_map(0, 10, 1, 4, 4, 4, 3, 3, 3, 1, 1, 1, 0, 20, 32, 0, 0, 0, 0, 0, 0, 0) == -1  # null seg
     assert lib.fgb_pp_tile_masks(0, 0, 10, 100, 0, 0) == -2   # not a power of two
     assert lib.fgb_subm_conv_fprop(0, 0, 0, 0, 0, 0, 0, 0, 10, 64, 64, 27, _cabi.F16, 0, 0, 0, 0) == -1
-    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 60, 64, 27, _cabi.F16, 256, 256, 0, 0) == -4  # Ci % 8
-    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 64, 64, 27, 7, 256, 256, 0, 0) == -3
+    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 100000, 60, 64, 27, _cabi.F16, 256, 256, 0, 0) == -4  # Ci % 8
+    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 100000, 64, 64, 27, 7, 256, 256, 0, 0) == -3
+    assert lib.fgb_subm_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 64, 64, 27, _cabi.F16, 256, 256, 0, 0) == -5  # small launch: no room for the split-K slabs
     assert lib.fgb_subm_conv_wgrad(16, 16, 16, 16, 16, 0, 16, 0, 10, 100, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -5  # workspace
     assert lib.fgb_wgrad_set_row_bands(65) == -2 and lib.fgb_wgrad_set_row_bands(0) == 0
 
@@ -89,10 +94,11 @@ def test_sparse_conv_entry_points_validate_without_launch(lib):
     assert lib.fgb_sparse_build_neighbor_map(16, 10, 16, 5, 8, 8, 8, *g, 16, 5, 32, 16, 0, 16, 16, 16, 16, 0, 0) == -2   # slots < n_in
     assert lib.fgb_sparse_build_neighbor_map(16, 10, 16, 5, 8, 8, 8, *g, 16, 20, 32, 16, 0, 16, 16, 16, 0, 0, 0) == -1   # null seg
     assert lib.fgb_pp_gray_code(0, 10, 40, 0, 0, 0) == -2
-    assert lib.fgb_sparse_conv_workspace_bytes(0, 1000, 500, 64, 64, 27, _cabi.F32_IEEE, 1) == 256 + 500 * 3 * 64 * 4 + 64 * 64 * 27 * 3 * 4
-    assert lib.fgb_sparse_conv_workspace_bytes(1, 1000, 500, 64, 32, 27, _cabi.F32_IEEE, 1) == \
-        256 + 64 * 32 * 27 * 4 + 64 * 32 * 27 * 3 * 4 + 1000 * 3 * 32 * 4
-    assert lib.fgb_sparse_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, 10, 20, 60, 64, 27, _cabi.F16, 256, 256, 0, 0) == -4  # Ci % 8
+    no, ni = 100000, 50000   # enough rows on both sides that neither fprop nor dgrad is split
+    assert lib.fgb_sparse_conv_workspace_bytes(0, no, ni, 64, 64, 27, _cabi.F32_IEEE, 1) == 256 + ni * 3 * 64 * 4 + 64 * 64 * 27 * 3 * 4
+    assert lib.fgb_sparse_conv_workspace_bytes(1, no, ni, 64, 32, 27, _cabi.F32_IEEE, 1) == \
+        256 + 64 * 32 * 27 * 4 + 64 * 32 * 27 * 3 * 4 + no * 3 * 32 * 4
+    assert lib.fgb_sparse_conv_fprop(16, 16, 0, 16, 16, 16, 0, 16, no, ni, 60, 64, 27, _cabi.F16, 256, 256, 0, 0) == -4  # Ci % 8
     assert lib.fgb_sparse_conv_wgrad(16, 16, 16, 16, 16, 0, 16, 0, 10, 20, 500, 64, 64, 27, _cabi.F16, 2, 256, 10, 0, 0) == -2  # pairs > n_out*V
 
 

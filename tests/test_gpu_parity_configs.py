@@ -294,3 +294,62 @@ def test_wgrad_row_bands_vs_oracle(res, c, bands):
     ref = ref_gw.reshape(c, 27, c)
     assert rel_err(gw, ref) <= 1e-2 and rel_err(gw32, ref) <= 1e-2
     assert rel_err(gw32, plain32.double().cpu()) <= 1e-5
+
+
+@pytest.mark.parametrize("res,batch,c,dtype", [(8, 1, 1024, "float16"), (16, 1, 256, "bfloat16"), (8, 2, 64, "float32"), (12, 1, 512, "float16")])
+def test_splitk_of_small_launches_vs_oracle(res, batch, c, dtype):
+    """Tiny inputs (a handful of row blocks): fprop and dgrad split every block's offsets
+    into shares that run as separate work items.  Checked against the oracle with the
+    automatic rule, with a forced odd share count and with splitting off, and the three
+    must agree with each other to rounding."""
+    from flexgemm_b200.kernels import cuda as K
+    from flexgemm_b200.ops import spconv
+    scales = (1.0,) * batch
+    coords, feats, weight, bias, shape = orc.make_problem(res, c, c, dtype, seed=res + c, batch=batch, scales=scales)
+    g = torch.Generator().manual_seed(3)
+    gout = torch.randn(coords.shape[0], c, generator=g).to(feats.dtype)
+    nbr = orc.neighbor_map(coords.numpy(), shape)
+    ref_out = orc.conv_forward(feats.double(), nbr, weight.double(), bias.double())
+    ref_gin, _, _ = orc.conv_backward(gout.double(), feats.double(), nbr, weight.double())
+    results = []
+    for setting in (0, 5, 1):
+        prev = K.set_conv_splitk(setting)
+        try:
+            f = feats.to(DEV).requires_grad_(True)
+            out, _ = spconv.sparse_submanifold_conv3d(f, coords.to(DEV), torch.Size(shape), weight.to(DEV), bias.to(DEV))
+            out.backward(gout.to(DEV))
+            torch.cuda.synchronize()
+            K.check_status(DEV)
+        finally:
+            K.set_conv_splitk(prev)
+        assert rel_err(out, ref_out) <= 1e-2, (setting, rel_err(out, ref_out))
+        assert rel_err(f.grad, ref_gin) <= 1e-2, (setting, rel_err(f.grad, ref_gin))
+        results.append((out.detach().float().cpu(), f.grad.float().cpu()))
+    for o, gi in results[:2]:
+        assert rel_err(o, results[2][0]) <= 4e-3 and rel_err(gi, results[2][1]) <= 4e-3
+
+
+def test_reference_first_forward_case_res8_c1024_batch256():
+    """The first case of the reference's forward test (its own shell rule, RES=8, 256 samples, C=1024, fp16)."""
+    from flexgemm_b200.kernels import cuda as K
+    from flexgemm_b200.ops import spconv
+    res, c, batch = 8, 1024, 256
+    base = orc.reference_sphere_coords(res)
+    coords_np = np.concatenate([np.concatenate([np.full((base.shape[0], 1), b, np.int32), base[:, 1:]], axis=1) for b in range(batch)])
+    coords_np = np.ascontiguousarray(coords_np.astype(np.int32))
+    n = coords_np.shape[0]
+    shape = torch.Size((batch, c, res, res, res))
+    g = torch.Generator().manual_seed(8)
+    feats = torch.randn(n, c, generator=g).half()
+    weight = (torch.randn(c, 3, 3, 3, c, generator=g) / (27 * c) ** 0.5).half()
+    bias = torch.randn(c, generator=g).half()
+    with torch.no_grad():
+        out, cache = spconv.sparse_submanifold_conv3d(feats.to(DEV), torch.from_numpy(coords_np).to(DEV), shape, weight.to(DEV), bias.to(DEV))
+    torch.cuda.synchronize()
+    K.check_status(DEV)
+    nbr = orc.neighbor_map(coords_np, shape)
+    assert np.array_equal(u32(cache["neighbor_map"]), nbr)
+    rows_np = np.random.default_rng(1).choice(n, 3000, replace=False)
+    sub = torch.from_numpy(nbr[rows_np].astype(np.int64))
+    ref = torch.einsum("rvc,ovc->ro", gathered(feats, sub, n), weight.double().reshape(c, 27, c)) + bias.double()
+    assert rel_err(out[torch.from_numpy(rows_np).to(DEV)], ref) <= 1e-2
