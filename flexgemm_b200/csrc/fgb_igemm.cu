@@ -255,10 +255,10 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  // Work distribution.  Row blocks are handed out dynamically, in descending
-  // cost order, from a global ticket counter: lane 0 of the first gather warp
-  // claims the ticket of the CTA's next block when the gather front is about to
-  // finish the current one, and publishes it (block x column tile, or "no more work") in a
+  // Work distribution.  Work items (row block x column tile x split-K share) are handed out
+  // dynamically, blocks in descending cost order, from a global ticket counter: lane 0 of the first gather warp
+  // claims the ticket of the CTA's next item when the gather front is about to
+  // finish the current one, and publishes it (or "no more work") in a
   // small shared-memory ring that every role reads in order.  So each role walks
   // the same sequence of work items, an SM that got cheap blocks simply takes
   // more of them, and within an item all roles enumerate the offsets of the
@@ -267,14 +267,18 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
   auto publish_work = [&](uint32_t k, uint32_t& pub_block, uint32_t& pub_ntile) {  // one thread
     const uint32_t slot = k % kSchedRing;
     mbar_wait(&ctl->sched_empty[slot], ((k / kSchedRing) & 1) ^ 1, abort_flag);
-    if (pub_block != kInvalid && ++pub_ntile >= static_cast<uint32_t>(p.items_per_block)) pub_ntile = 0;
-    if (pub_block == kInvalid || pub_ntile == 0) {
-      const uint32_t t = atomicAdd(p.ticket, 1u);
-      pub_block = t < p.num_blocks ? (p.block_order != nullptr ? __ldg(&p.block_order[t]) : t) : none;
-      pub_ntile = 0;
-      if (pub_block == kInvalid) pub_ntile = 0xFFFFFFFFu;  // stays "no more work"
+    // one ticket = one work item; the items of a block (its column tiles and split-K shares) have consecutive tickets,
+    // so they run at about the same time on different SMs and find the block's gathered rows in L2
+    const uint32_t ipb = static_cast<uint32_t>(p.items_per_block);
+    const uint32_t t = pub_block == none ? none : atomicAdd(p.ticket, 1u);
+    if (t == none || t / ipb >= p.num_blocks) {
+      pub_block = none;  // stays "no more work"
+    } else {
+      const uint32_t pos = ipb == 1 ? t : t / ipb;
+      pub_block = p.block_order != nullptr ? __ldg(&p.block_order[pos]) : pos;
+      pub_ntile = t - pos * ipb;
     }
-    ctl->sched_entry[slot] = (pub_block == none || *abort_flag) ? none : pub_block * p.items_per_block + pub_ntile;
+    ctl->sched_entry[slot] = (pub_block == none || *abort_flag) ? none : pub_block * ipb + pub_ntile;
     mbar_arrive(&ctl->sched_full[slot]);
   };
   // k-th work item of this CTA; every reader (a whole warp, or a single lane when
@@ -343,7 +347,7 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
     uint32_t m0 = 0, m1 = 0, nm0 = 0, nm1 = 0;
     uint32_t mblk = 0, ntile = 0;
     const bool publisher = warp == kGatherWarp0 && lane == 0;
-    uint32_t pub_block = kInvalid, pub_ntile = 0;
+    uint32_t pub_block = 0, pub_ntile = 0;  // pub_block turns `none` once the tickets are used up
     if (publisher) publish_work(0, pub_block, pub_ntile);
     bool has_work = work_of(0, mblk, ntile, false);
     if (has_work) {
