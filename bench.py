@@ -203,6 +203,7 @@ def run_reference_arm(args):
         return
     threads = os.cpu_count() or 1
     tflops, ms, sample = cpu_explicit_steps(args.steps, args.warmup, threads)
+    ref_map = reference_cuda_map_build()
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -212,8 +213,31 @@ def run_reference_arm(args):
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "reference_cuda_map_build": ref_map,
     }
     emit(line)
+
+
+def reference_cuda_map_build():
+    """The second half of the metric for the reference: its neighbour-cache build (its own hash table, neighbour-map
+    and post-processing kernels, compiled from its sources into oracle/_ref by oracle/build_reference_ext.py) on the
+    headline shell, on this machine's GPU.  None where the extension or a GPU is missing."""
+    try:
+        from oracle.build_reference_ext import load_reference_ext, reference_neighbor_cache
+        ref = load_reference_ext()
+        if ref is None or not torch.cuda.is_available():
+            return None
+        from oracle import submconv_oracle as orc
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        coords = torch.from_numpy(orc.shell_coords(RES)).to(dev)
+        shape = (1, CI, RES, RES, RES)
+        for _ in range(3):
+            reference_neighbor_cache(ref, coords, shape)
+        ms = time_loop(lambda: reference_neighbor_cache(ref, coords, shape), 20)
+        return {"ms": ms, "what": "the reference's compiled CUDA functions (init_hashmap + hashmap_build_submanifold_conv_neighbour_map + "
+                                  "neighbor_map_post_process_for_masked_implicit_gemm_1) on the RES=256 shell, rows in key order, 20 builds"}
+    except Exception as e:  # the CPU arm must not fail for lack of the optional GPU figure
+        return {"ms": None, "error": str(e)[:200]}
 
 
 # --------------------------------------------------------------------------- GPU helpers

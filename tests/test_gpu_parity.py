@@ -473,3 +473,28 @@ def test_sorted_input_with_long_columns(ksize, dil, K):
     coords = np.concatenate([np.concatenate([np.full((pts.shape[0], 1), b), pts], axis=1) for b in range(2)]).astype(np.int32)
     shape = (2, 0, W, H, D)
     check_cache(build_cache(coords, shape, ksize, dil), orc.neighbor_cache(coords, shape, ksize, dil), ksize[0] * ksize[1] * ksize[2])
+
+
+POST = np.load(os.path.join(GOLD, "postprocess.npz"))
+
+
+@pytest.mark.parametrize("name", sorted({k.split("/")[0] for k in POST.files}))
+def test_cache_vs_reference_cuda_output(name, K):
+    """The whole neighbour cache against what the reference's own compiled CUDA functions produced
+    for the same coordinates (fixture: tests/golden/make_golden_postprocess.py)."""
+    coords, shape = POST[name + "/coords"], tuple(int(x) for x in POST[name + "/shape"])
+    ks, dil = tuple(int(x) for x in POST[name + "/ksize"]), tuple(int(x) for x in POST[name + "/dilation"])
+    cache = build_cache(coords, shape, ks, dil)
+    assert np.array_equal(u32(cache["neighbor_map"]), POST[name + "/neighbor_map"])
+    assert np.array_equal(cache["gray_code"].cpu().numpy(), POST[name + "/gray_code"])
+    for key in ("valid_signal_i", "valid_signal_o", "valid_signal_seg"):
+        assert np.array_equal(u32(cache[key]), POST[f"{name}/{key}"]), key
+    # equal codes may be ordered differently (the reference's argsort is unstable): same codes along both orders,
+    # hence the same per-tile offset lists
+    gray = POST[name + "/gray_code"]
+    binary = orc.gray_binary_code(POST[name + "/neighbor_map"])[1]
+    ours, theirs = cache["sorted_idx"].cpu().numpy(), POST[name + "/sorted_idx"]
+    assert np.array_equal(binary[ours], binary[theirs])
+    for block in (128, 32):
+        assert np.array_equal(cache.valid_kernel_callback(block).cpu().numpy(), POST[f"{name}/valid_kernel_{block}"])
+        assert np.array_equal(cache.valid_kernel_seg_callback(block).cpu().numpy(), POST[f"{name}/valid_kernel_seg_{block}"])

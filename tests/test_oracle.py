@@ -131,3 +131,33 @@ def test_residual_block_epilogue_is_the_torch_sequence():
     assert torch.allclose(orc.silu_backward(y32.double(), gout), yd.grad, rtol=1e-12, atol=1e-12)
     with pytest.raises(ValueError):
         orc.residual_block_epilogue(y32, "gelu")
+
+
+# ----------------------------------------------------------------------------
+# the derived cache tensors against outputs of the reference's own CUDA functions
+# ----------------------------------------------------------------------------
+POST = np.load(os.path.join(GOLD, "postprocess.npz"))
+
+
+@pytest.mark.parametrize("name", sorted({k.split("/")[0] for k in POST.files}))
+def test_postprocessing_restatement_matches_reference_cuda_output(name):
+    """gray code, pair lists, segment table and per-tile valid-offset lists as the reference's
+    compiled hashmap_build_submanifold_conv_neighbour_map /
+    neighbor_map_post_process_for_masked_implicit_gemm_{1,2} produced them on a GPU
+    (fixture made by tests/golden/make_golden_postprocess.py): bit-exact, and the dtypes too.
+    sorted_idx comes from an unstable argsort there, so it is checked as a property and
+    the valid-offset lists are derived from the reference's own permutation."""
+    coords, shape = POST[name + "/coords"], tuple(int(x) for x in POST[name + "/shape"])
+    ks, dil = tuple(int(x) for x in POST[name + "/ksize"]), tuple(int(x) for x in POST[name + "/dilation"])
+    ours = orc.neighbor_cache(coords, shape, ks, dil)
+    for key in ("neighbor_map", "gray_code", "valid_signal_i", "valid_signal_o", "valid_signal_seg"):
+        assert ours[key].dtype == POST[f"{name}/{key}"].dtype, key
+        assert np.array_equal(ours[key], POST[f"{name}/{key}"]), key
+    sidx = POST[name + "/sorted_idx"]
+    assert sidx.dtype == np.int64
+    assert orc.is_valid_sorted_idx(sidx, ours["binary_code"])
+    for block in (128, 32):
+        vk, seg = orc.valid_kernel(ours["gray_code"], sidx, block)
+        assert vk.dtype == POST[f"{name}/valid_kernel_{block}"].dtype and seg.dtype == POST[f"{name}/valid_kernel_seg_{block}"].dtype
+        assert np.array_equal(vk, POST[f"{name}/valid_kernel_{block}"])
+        assert np.array_equal(seg, POST[f"{name}/valid_kernel_seg_{block}"])
