@@ -40,17 +40,22 @@ __global__ void __launch_bounds__(kSortThreads) sort_histogram_kernel(const int3
   const int lane = threadIdx.x & 31;
   const uint32_t per = (n + gridDim.x - 1) / gridDim.x;
   const uint32_t begin = blockIdx.x * per, end = min(n, begin + per);
-  // whole warps walk the range so that every lane takes part in the match
+  // whole warps walk the range so that every lane takes part in the votes
   for (uint32_t i0 = begin + (threadIdx.x & ~31u); i0 < end; i0 += kSortThreads) {
     const uint32_t i = i0 + lane;
     const bool ok = i < end;
     const uint32_t key = ok ? static_cast<uint32_t>(__ldg(&codes[i])) ^ flip : 0u;
-    const unsigned valid = __ballot_sync(0xffffffffu, ok);
-    for (int p = 0; p < passes; ++p) {
-      const uint32_t d = (key >> (p * kDigitBits)) & (kDigits - 1);
-      // neighbouring voxels mostly share their code: one shared-memory add per distinct digit of the warp
-      const unsigned peers = __match_any_sync(0xffffffffu, d) & valid;
-      if (ok && lane == __ffs(peers) - 1) atomicAdd(&s_h[p * kDigits + d], static_cast<uint32_t>(__popc(peers)));
+    const unsigned valid = __ballot_sync(0xffffffffu, ok);  // a prefix of the lanes
+    // neighbouring voxels mostly share their code: the warp's keys are cut into runs of equal keys, and the first
+    // lane of a run adds the run's length to the key's bin of every pass (equal keys share all their digits)
+    const uint32_t prev = __shfl_up_sync(0xffffffffu, key, 1);
+    const bool head = ok && (lane == 0 || key != prev);
+    const unsigned heads = __ballot_sync(0xffffffffu, head);
+    if (head) {
+      const unsigned later = heads & ~((2u << lane) - 1u);  // run heads above this lane
+      const int next = later != 0u ? __ffs(later) - 1 : __popc(valid);
+      const uint32_t len = static_cast<uint32_t>(next - lane);
+      for (int p = 0; p < passes; ++p) atomicAdd(&s_h[p * kDigits + ((key >> (p * kDigitBits)) & (kDigits - 1))], len);
     }
   }
   __syncthreads();
@@ -202,12 +207,13 @@ struct SortLayout {
   int items;
 };
 
-// Tiles of 4096 keys for long inputs (the per-tile bookkeeping -- 512 counters published and looked back -- is then
-// small beside the keys), of 1024 keys for short ones (more CTAs in flight).
+// Tiles of 4096 keys (the per-tile bookkeeping -- 512 counters published and looked back over the earlier tiles -- is
+// then small beside the keys, and the look-back chain of a 160k-key input is 40 tiles long); tiles of 1024 keys for
+// very short inputs, so that a few CTAs still share the work.
 static SortLayout sort_layout(int64_t n) {
   auto align = [](size_t x) { return (x + 255) & ~size_t(255); };
   SortLayout L;
-  L.items = n > (int64_t(1) << 20) ? 16 : 4;
+  L.items = n > (int64_t(1) << 15) ? 16 : 4;
   L.tiles = static_cast<uint32_t>(ceil_div(n > 0 ? n : 1, int64_t(kSortThreads) * L.items));
   const size_t arr = align(size_t(n) * 4);
   L.keys_a = 0, L.vals_a = arr, L.keys_b = 2 * arr, L.vals_b = 3 * arr;
