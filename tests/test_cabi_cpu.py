@@ -173,3 +173,24 @@ def test_explicit_algorithm_on_cpu_matches_golden():
     assert torch.allclose(f.grad, t["grad_feats"], atol=1e-5)
     assert torch.allclose(w.grad, t["grad_weight"], atol=1e-4)
     assert torch.allclose(b.grad, t["grad_bias"], atol=1e-4)
+
+
+def test_reference_module_paths_and_call_shapes():
+    """Names the reference's own scripts reach for: the TF32 switch under its Triton module path
+    (tests/submconv/inf_ablation.py:20 there) and init_hashmap's (keys, values) result (ops/utils.py:4-19)."""
+    from flexgemm_b200 import kernels
+    from flexgemm_b200.kernels import config
+    from flexgemm_b200.kernels.triton.spconv import config as ref_path
+    from flexgemm_b200.ops import utils
+    assert ref_path.allow_tf32 is config.allow_tf32
+    try:
+        ref_path.allow_tf32 = False
+        assert config.allow_tf32 is False and kernels.triton.spconv.config.allow_tf32 is False
+    finally:
+        config.allow_tf32 = True
+    assert ref_path.allow_tf32 is True
+    keys, vals = utils.init_hashmap((1, 8, 64, 64, 64), 100, "cpu")
+    assert keys.dtype == torch.uint32 and vals.dtype == torch.uint32 and keys.shape == vals.shape == (100,)
+    assert int(keys.view(torch.int32)[0]) == -1
+    only = utils.init_hashmap((8, 8, 1024, 1024, 1024), 10, "cpu", with_values=False)
+    assert only.dtype == torch.uint64 and only.shape == (10,)
