@@ -20,6 +20,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <atomic>
 #include <mutex>
 #include <type_traits>
@@ -167,7 +168,10 @@ __host__ __device__ __forceinline__ uint32_t wg_band_share(uint32_t nkb, uint32_
   return base + (q < rem ? 1u : 0u);
 }
 
-template <int kElem, int kRows>  // kRows = pairs of a stage / 32 = pair rows per gather thread
+// kRows = pairs of a stage / 32 = pair rows per gather thread.  kBanded: the CTA walks its share of every row band (see
+// above); otherwise one contiguous run of k-blocks of its offset's list, without the per-band tables in the gather loop
+// (that loop's bookkeeping alone costs 2-3 % where bands bring nothing).
+template <int kElem, int kRows, bool kBanded>
 __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradParams p) {
   constexpr bool kTF32 = (kElem == 4);
   constexpr int kUmmaK = 32 / kElem;      // 16 for 16-bit types, 8 for tf32
@@ -201,7 +205,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
       ctl->unit_v = v, ctl->unit_j = j, ctl->unit_kb = static_cast<int>(ukb);
     }
     v = __shfl_sync(0xffffffffu, v, 0), j = __shfl_sync(0xffffffffu, j, 0);
-    if (v >= 0) {
+    if (kBanded && v >= 0) {
       // this CTA's share of every row band (lane b looks at band b, 32 bands per round)
       const uint32_t K = wg_chunks_of(p.seg, v, p.kb, static_cast<int>(ukb));
       uint32_t rot = 0, total = 0;
@@ -239,7 +243,13 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
   if (v < 0) return;  // grid is sized for the worst case; also the no-op path after a soft error
   const int co0 = co_group * p.mt * 128;
   const int ci0 = ci_tile * p.bn;
-  const int total = ctl->total;  // may be 0 for a CTA of a very short offset: it writes a slab of zeros
+  // contiguous walk: k-blocks [k_begin, k_begin + total) of the offset's list, full units and a shorter last one
+  const uint32_t seg_begin = __ldg(&p.seg[v]);
+  const uint32_t seg_end = __ldg(&p.seg[v + 1]);
+  const uint32_t num_k = (seg_end - seg_begin + p.kb - 1) / p.kb;
+  const uint32_t k_begin = static_cast<uint32_t>(unit_j) * unit_kb;
+  // banded: may be 0 for a CTA of a very short offset, which then writes a slab of zeros
+  const int total = kBanded ? ctl->total : static_cast<int>(min(num_k, k_begin + unit_kb) - k_begin);
   volatile uint32_t* abort_flag = &ctl->abort_flag;
 
   if (tid == 0) {
@@ -281,8 +291,14 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
     auto skip_empty = [&]() {
       while (band < p.bands && blk >= ctl->band_cnt[band]) ++band, blk = 0;
     };
-    auto load_pairs = [&](uint32_t (&io)[kRows], uint32_t (&ii)[kRows]) {  // pairs of block (band, blk), then advance
-      const uint32_t first = ctl->band_begin[band] + blk * p.kb, end = ctl->band_end[band];
+    uint32_t next_kblk = k_begin;  // contiguous walk: the next k-block of the list
+    auto load_pairs = [&](uint32_t (&io)[kRows], uint32_t (&ii)[kRows]) {  // pairs of the next block, then advance
+      uint32_t first, end;
+      if constexpr (kBanded) {
+        first = ctl->band_begin[band] + blk * p.kb, end = ctl->band_end[band];
+      } else {
+        first = seg_begin + next_kblk * p.kb, end = seg_end;
+      }
 #pragma unroll
       for (int j = 0; j < kRows; ++j) {
         const uint32_t pp = first + g + 32 * j;
@@ -290,11 +306,15 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
         io[j] = ok ? __ldg(&p.vs_o[pp]) : kInvalid;
         ii[j] = ok ? __ldg(&p.vs_i[pp]) : kInvalid;
       }
-      ++blk;
-      skip_empty();
+      if constexpr (kBanded) {
+        ++blk;
+        skip_empty();
+      } else {
+        ++next_kblk;
+      }
     };
     uint32_t io[kRows], ii[kRows], nio[kRows], nii[kRows];
-    skip_empty();
+    if constexpr (kBanded) skip_empty();
     if (total > 0) load_pairs(nio, nii);
     int s = 0;
     uint32_t ph = 0;  // ring position and phase bit, advanced by hand (no division by the runtime stage count per stage)
@@ -570,15 +590,21 @@ static int target_units(const WgradPlan& w, int V, int splitk) {
 static std::atomic<int> g_row_bands{0};
 
 static void plan_bands(int64_t n_out, int64_t n_in, int64_t n_pairs, int Ci, int Co, int V, int eb, int kb, bool have_offsets,
-                       int* bands, uint32_t* nblk, uint32_t* band_blocks) {
+                       bool whole_channels, int* bands, uint32_t* nblk, uint32_t* band_blocks) {
   const int64_t blocks = ceil_div(n_out > 0 ? n_out : 1, kMapBlock);
   int64_t b = 1;
   if (have_offsets) {
     const int forced = g_row_bands.load(std::memory_order_relaxed);
     if (forced > 0) {
       b = forced;
+    } else if (!whole_channels) {
+      // several CTAs per unit (channel counts above 256): measured 2-4 % slower with bands (RES=64 x 4, C=512; RES=128,
+      // C=1024), so the lists are walked in one piece there
+      b = 1;
     } else {
-      b = (n_out * Co + n_in * Ci) * eb / (int64_t(8) << 20);
+      const int64_t row_bytes = (n_out * Co + n_in * Ci) * eb;
+      // rows that fit L2 (126 MB) are shared by the offsets anyway: bands only cost their partial blocks there
+      b = row_bytes > (int64_t(126) << 20) ? row_bytes / (int64_t(8) << 20) : 1;
       const int64_t waste_cap = n_pairs / (int64_t(25) * kb * V);  // 0.5 * V * bands <= 2 % of n_pairs / kb
       if (b > waste_cap) b = waste_cap;
     }
@@ -648,13 +674,17 @@ extern "C" int64_t fgb_sparse_conv_workspace_bytes(int pass, int64_t n_out, int6
 namespace fgb {
 // One launcher per kernel instance: the dynamic shared-memory limit is a property of (kernel, device), and all
 // instances share one function-pointer type, so the table must hang on the template arguments, not on the type.
+template <int kElem, int kRows, bool kBanded>
+static int launch_wgrad_instance(int64_t grid, size_t smem, const WgradParams& p, cudaStream_t s) {
+  static PerDeviceTable configured;
+  const int rc = ensure_dynamic_smem(configured, subm_wgrad_kernel<kElem, kRows, kBanded>, smem);
+  if (rc != FGB_OK) return rc;
+  subm_wgrad_kernel<kElem, kRows, kBanded><<<static_cast<unsigned>(grid), kWgThreads, smem, s>>>(p);
+  return launch_status();
+}
 template <int kElem, int kRows>
 static int launch_wgrad(int64_t grid, size_t smem, const WgradParams& p, cudaStream_t s) {
-  static PerDeviceTable configured;
-  const int rc = ensure_dynamic_smem(configured, subm_wgrad_kernel<kElem, kRows>, smem);
-  if (rc != FGB_OK) return rc;
-  subm_wgrad_kernel<kElem, kRows><<<static_cast<unsigned>(grid), kWgThreads, smem, s>>>(p);
-  return launch_status();
+  return p.bands > 1 ? launch_wgrad_instance<kElem, kRows, true>(grid, smem, p, s) : launch_wgrad_instance<kElem, kRows, false>(grid, smem, p, s);
 }
 
 // one wgrad pass over operands of element type `dtype` (never FGB_F32_IEEE): partial slabs, then the ordered sum
@@ -671,7 +701,8 @@ static int wgrad_pass(const void* grad_out, const void* feats, const uint32_t* v
   p.vs_o = vs_o;
   p.seg = seg;
   p.block_offsets = block_offsets;
-  plan_bands(n_out, n_in, n_pairs, Ci, Co, V, eb, w.kb, block_offsets != nullptr, &p.bands, &p.nblk, &p.band_blocks);
+  plan_bands(n_out, n_in, n_pairs, Ci, Co, V, eb, w.kb, block_offsets != nullptr, w.co_groups * w.ci_tiles == 1, &p.bands, &p.nblk,
+             &p.band_blocks);
   p.partial = slabs;
   p.Co = Co, p.Ci = Ci, p.V = V;
   p.target_units = target_units(w, V, splitk);
@@ -897,7 +928,7 @@ extern "C" int fgb_wgrad_plan_host(const uint32_t* seg, const uint32_t* block_of
   const int64_t n_pairs = seg[V];
   int bands = 1;
   uint32_t nblk = 0, band_blocks = 0;
-  plan_bands(n_out, n_in, n_pairs, Ci, Co, V, eb, w.kb, block_offsets != nullptr, &bands, &nblk, &band_blocks);
+  plan_bands(n_out, n_in, n_pairs, Ci, Co, V, eb, w.kb, block_offsets != nullptr, w.co_groups * w.ci_tiles == 1, &bands, &nblk, &band_blocks);
   // the kernel's bisection (wg_plan_unit_kb) with loops in place of warp reductions
   uint32_t nk[32], hi = 1;
   for (int v = 0; v < V; ++v) {
@@ -924,7 +955,13 @@ extern "C" int fgb_wgrad_plan_host(const uint32_t* seg, const uint32_t* block_of
         const uint32_t end = wg_band_pos(seg, block_offsets, nblk, band_blocks, bands, v, b + 1);
         const uint32_t nkb = (end - begin + w.kb - 1) / w.kb;
         uint32_t first = 0;
-        const uint32_t cnt = wg_band_share(nkb, K, k, rot, &first);
+        uint32_t cnt;
+        if (bands == 1) {
+          first = k * unit_kb;
+          cnt = first < nkb ? std::min(nkb - first, unit_kb) : 0u;
+        } else {
+          cnt = wg_band_share(nkb, K, k, rot, &first);
+        }
         rot += nkb % K;
         uint32_t* e = plan + (size_t(u) * bands + b) * 3;
         e[0] = begin + first * w.kb, e[1] = cnt, e[2] = end;

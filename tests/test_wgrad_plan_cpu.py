@@ -1,7 +1,8 @@
 """Host-side check of how the wgrad kernel splits the pair lists among its CTAs
 (row bands shared by all offsets): every pair is read by exactly one CTA of its
 offset, a CTA never reads past the end of a band, bands are cut at the same
-output rows for every offset, and the CTAs of an offset carry equal loads.
+output rows for every offset, and the CTAs of an offset carry equal loads
+(with a single band: equal units and a shorter last one).
 
 The split is replayed on the host by ``fgb_wgrad_plan_host`` from the same
 helper functions the kernel uses; no GPU is involved."""
@@ -83,7 +84,10 @@ def test_every_pair_is_read_once_and_loads_are_even(lib, res, c, forced):
             if u < p.shape[0] and p[u, 0, 0] == seg[v + 1] and seg[v + 1] < seg[-1]:
                 break
         assert loads, v
-        assert max(loads) - min(loads) <= 1, (v, loads)
+        if bands == 1:   # one band: full units and a shorter last one
+            assert len(set(loads[:-1])) <= 1 and loads[-1] <= loads[0], (v, loads)
+        else:            # several bands: the remainders are dealt round-robin, totals differ by at most one block
+            assert max(loads) - min(loads) <= 1, (v, loads)
     assert u == p.shape[0]
     assert (seen == 1).all()
 
