@@ -72,8 +72,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at the headline workload, copied from an ncu capture; the
 # capture is identified by the commit of the kernels it ran (the kernels may have changed since: compare with HEAD)
 NCU_DRAM_TRAFFIC = {
-    "commit": "7353131",
-    "bytes": {"fprop": 291.9e6, "dgrad": 291.4e6, "wgrad": 522.4e6},
+    "commit": "e76fbda",
+    "bytes": {"fprop": 290.0e6, "dgrad": 288.5e6, "wgrad": 184.9e6},
 }
 
 

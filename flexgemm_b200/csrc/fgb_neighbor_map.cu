@@ -194,6 +194,9 @@ template <int kKeyBits>
 __global__ void __launch_bounds__(256) column_index_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, uint64_t columns,
                                                           uint2* __restrict__ col_table, uint32_t* unsorted) {
   const uint32_t i = blockIdx.x * 256u + threadIdx.x;
+  // an earlier CTA found the rows out of order: the table will not be used.  (Lane 0's reading decides for the warp:
+  // the word may change between the lanes' loads, and the vote below needs the whole warp.)
+  if (__shfl_sync(0xffffffffu, *reinterpret_cast<volatile uint32_t*>(unsorted), 0) != 0u) return;
   bool bad = false;
   if (i < n) {
     const int4 b = __ldg(&coords[i]);
