@@ -31,7 +31,7 @@ Printed JSON (one line, rank 0): the metric and, beside it,
   local gradient recomputed on rank 0).
 
 --impl reference times the CPU algorithm alone, with all host threads.
---workload res1024_batch8 | res1024_map [--unsorted] | residual_stack [--fused]
+--workload res1024_batch8 | res1024_map [--unsorted] | residual_stack [--fused] | pipeline_microbench
 run one of the side workloads alone (what the ncu captures under profiles/ use).
 --quick skips the side workloads of the default run.
 """
@@ -913,6 +913,61 @@ def run_residual_stack(args):
         "gpu_launches": r["launches"], "clocks": clocks})
 
 
+def run_pipeline_microbench(args):
+    """What one SM sustains of an fprop stage's operand streams and MMAs (kernels.cuda.microbench_pipeline): the
+    numbers behind the tensor-pipe ceiling of fprop / dgrad."""
+    import torch
+    from flexgemm_b200.kernels import cuda as K
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    n_rows, c = 163736, 256                       # the headline workload's feature matrix (84 MB) and weights (3.5 MB)
+    rows = torch.zeros(n_rows, c, dtype=torch.float16, device=dev)
+    dense = torch.zeros(27 * c * c, dtype=torch.float16, device=dev)
+    iters = 2000
+    T, G, M, C, G4, P, L = K.MB_TMA, K.MB_GATHER, K.MB_MMA, K.MB_COUPLED, K.MB_GATHER4, K.MB_PAIR, K.MB_LEAN
+    cases = [("mma alone", M, 3, 3, 0), ("mma alone, 128 idle cycles before each stage", M, 3, 3, 128),
+             ("mma alone, 256 idle cycles before each stage", M, 3, 3, 256),
+             ("tma alone", T, 3, 3, 0), ("gather alone (cp.async)", G, 3, 3, 0), ("gather alone (TMA gather4)", G | G4, 3, 3, 0),
+             ("tma + gather, independent", T | G, 3, 3, 0), ("mma + tma + gather, independent", M | T | G, 3, 3, 0),
+             ("coupled: mma + tma + gather, 2 stages", C | M | T | G, 2, 2, 0), ("coupled: mma + tma + gather, 3 stages", C | M | T | G, 3, 3, 0),
+             ("coupled: mma + tma + gather, 5 + 2 stages", C | M | T | G, 5, 2, 0),
+             ("coupled, lean MMA lane: mma + tma", L | C | M | T, 3, 3, 0), ("coupled, lean MMA lane: mma + gather", L | C | M | G, 3, 3, 0),
+             ("coupled, lean MMA lane: mma + tma + gather, 2 stages", L | C | M | T | G, 2, 2, 0),
+             ("coupled, lean MMA lane: mma + tma + gather, 3 stages", L | C | M | T | G, 3, 3, 0),
+             ("coupled, lean MMA lane: mma + tma + gather, 5 + 2 stages", L | C | M | T | G, 5, 2, 0),
+             ("CTA pairs, 3 stages", P, 3, 3, 0), ("CTA pairs, 4 stages", P, 4, 4, 0)]
+    sampler = ClockSampler(dev.index).start()
+    out, launches = [], 0
+    for name, mode, sa, sb, delay in cases:
+        best, ctr = None, None
+        for _ in range(max(args.warmup, 1) + max(1, min(args.steps, 5))):
+            time.sleep(0.05)                       # every launch in the short-burst clock regime
+            ms, c8 = K.microbench_pipeline(mode, rows, dense, iters, sa, sb, delay)
+            launches += 1
+            if best is None or ms < best:
+                best, ctr = ms, c8
+        pair = bool(mode & P)
+        b_chunk = 16384 if pair else 32768
+        moved = ((32768 if mode & G or pair else 0) + (b_chunk if mode & T or pair else 0)) * iters
+        rec = {"case": name, "us_per_stage": round(best * 1e3 / iters, 4), "ingest_gbs_per_sm": round(moved / best * 1e-6, 1)}
+        if mode & M or pair:
+            rec["mma_frac_of_nominal"] = round(iters * 8 * 128 / 1.965e6 / best, 3)   # 8 MMAs x 128 cycles at 1965 MHz
+            if mode & C or pair:
+                rec["mma_lane"] = {"wait_dense_cycles": ctr[0], "waits_dense": ctr[1], "wait_gathered_cycles": ctr[2], "waits_gathered": ctr[3],
+                                   "loop_cycles": ctr[4], "stages": iters}
+        out.append(rec)
+    clocks = sampler.stop()
+    head = next(r for r in out if r["case"].startswith("coupled, lean MMA lane: mma + tma + gather, 3"))
+    emit({"metric": "pipeline microbenchmark: time per fprop stage on one SM (64 KB of operands in, 8 MMAs 128x256x16)",
+          "value": head["us_per_stage"], "unit": "us", "n_gpus": 1, "steps": iters, "warmup": max(args.warmup, 1), "ms_per_step": head["us_per_stage"] * 1e-3,
+          "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+          "config": {"workload": "per SM and stage: 256 random rows x 128 B gathered from an 84 MB matrix, 32 KB by TMA from a 3.5 MB buffer, "
+                                 "8 MMAs 128x256x16; all 148 SMs at once; best of a few launches per case",
+                     "l2": "the 84 MB matrix and the 3.5 MB buffer are L2-resident after the first launch (an upper bound for the conv kernel, whose "
+                           "gathers hit L2 78 % of the time)"},
+          "cases": out, "gpu_launches": launches, "clocks": clocks})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -923,10 +978,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="headline workload only: no sustained loop, sweep, residual stack, RES=1024 runs")
-    ap.add_argument("--workload", default="res256", choices=["res256", "res1024_batch8", "res1024_map", "residual_stack"],
+    ap.add_argument("--workload", default="res256", choices=["res256", "res1024_batch8", "res1024_map", "residual_stack", "pipeline_microbench"],
                     help="res256: the headline single-sample workload (default); res1024_batch8: the sharded high-resolution "
                          "batch; res1024_map: the neighbour-cache build alone at a size where HBM matters; residual_stack: 16 convs "
-                         "with SiLU and skip additions between them")
+                         "with SiLU and skip additions between them; pipeline_microbench: operand streams and MMAs of one fprop stage per SM")
     ap.add_argument("--unsorted", action="store_true", help="res1024_map: shuffle the rows (hash-table path)")
     ap.add_argument("--fused", action="store_true", help="residual_stack: SiLU and skip additions in the conv epilogues")
     args = ap.parse_args()
@@ -939,6 +994,8 @@ def main():
         run_map_build(args)
     elif args.workload == "residual_stack":
         run_residual_stack(args)
+    elif args.workload == "pipeline_microbench":
+        run_pipeline_microbench(args)
     else:
         run_gpu_arm(args)
 

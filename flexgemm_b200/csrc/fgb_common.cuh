@@ -1,6 +1,7 @@
 // Shared host/device helpers of the flexgemm_b200 library.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -60,5 +61,8 @@ __device__ __forceinline__ uint32_t fmix64_hi(uint64_t k) {
   return static_cast<uint32_t>(k >> 32) ^ static_cast<uint32_t>(k);
 }
 #endif
+
+// Tensor map over a row-major matrix of 16-bit elements whose box is 128 bytes of one row (fgb_igemm.cu).
+int make_rows_tmap(CUtensorMap* map, const void* rows, int64_t n_rows, int row_elems);
 
 }  // namespace fgb

@@ -654,6 +654,21 @@ int make_weight_tmap(CUtensorMap* map, const void* w, int nout, int V, int kc, i
   return r == CUDA_SUCCESS ? FGB_OK : FGB_E_DRIVER;
 }
 
+// 2-D map over rows[n_rows][row_elems] of 16-bit elements; box = 128 bytes of one row, 128B swizzle (the box TMA
+// tile::gather4 wants: it takes four row coordinates per instruction)
+int make_rows_tmap(CUtensorMap* map, const void* rows, int64_t n_rows, int row_elems) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return FGB_E_DRIVER;
+  cuuint64_t dims[2] = {cuuint64_t(row_elems), cuuint64_t(n_rows)};
+  cuuint64_t strides[1] = {cuuint64_t(row_elems) * 2};
+  cuuint32_t box[2] = {64u, 1u};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(rows), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FGB_OK : FGB_E_DRIVER;
+}
+
 static int pick_bn(int nout) {
   int bn = 32;
   while (bn < nout && bn < 256) bn <<= 1;

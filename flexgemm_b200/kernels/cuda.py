@@ -389,6 +389,29 @@ def set_conv_splitk(splits: int) -> int:
     return prev
 
 
+MB_TMA, MB_GATHER, MB_MMA, MB_COUPLED, MB_GATHER4, MB_PAIR, MB_LEAN = 1, 2, 4, 8, 16, 32, 64
+
+
+def microbench_pipeline(mode: int, rows: torch.Tensor, dense: torch.Tensor, iters: int = 2000, stages_a: int = 3, stages_b: int = 3,
+                        issue_delay: int = 0):
+    """One launch of the pipeline microbenchmark (``fgb_microbench_pipeline``): the operand streams and the MMAs of an
+    fprop stage on every SM.  ``rows`` [n, row_bytes / 2] 16-bit, ``dense`` any contiguous buffer.  Returns
+    ``(ms, counters)``; counters = the MMA lane's wait cycles / waits for the dense and the gathered operand and the
+    total cycles of its loop (CTA 0).  ``issue_delay``: cycles the MMA lane idles before each stage's MMAs."""
+    import ctypes
+    assert rows.is_cuda and rows.is_contiguous() and rows.element_size() == 2 and dense.is_cuda and dense.is_contiguous()
+    ms = ctypes.c_float(0.0)
+    counters = (ctypes.c_uint64 * 8)()
+    status = status_word(rows.device)
+    rc = _cabi.lib().fgb_microbench_pipeline(int(mode), int(stages_a), int(stages_b), int(iters), int(issue_delay), rows.data_ptr(), rows.shape[0],
+                                             rows.shape[1] * 2, dense.data_ptr(), dense.numel() * dense.element_size(),
+                                             ctypes.byref(ms), counters, status.data_ptr(), _stream(rows.device))
+    _count(1)
+    _cabi.check(rc, "fgb_microbench_pipeline")
+    check_status(rows.device)
+    return float(ms.value), [int(c) for c in counters]
+
+
 def set_conv_cta_limit(max_ctas: int) -> int:
     """Cap the CTAs (SMs) of the persistent fprop / dgrad kernels launched from now
     on (0 = no cap); returns the previous cap."""

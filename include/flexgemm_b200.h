@@ -283,8 +283,8 @@ int fgb_subm_conv_wgrad(const void* grad_out, const void* feats,
                         int32_t* status, void* stream);
 
 /* Number of row bands fgb_*_conv_wgrad cuts the pair lists into when it is given
- * block_offsets: 0 = chosen from the sizes (bands of about 8 MB of rows), 1 .. 64
- * = fixed.  Returns the previous value.  Process-wide tuning knob; read at launch. */
+ * block_offsets: 0 = chosen from the sizes (one band while grad_out and feats fit
+ * the L2 together, bands of about 8 MB of rows beyond that), 1 .. 64 = fixed.  Returns the previous value.  Process-wide tuning knob; read at launch. */
 int fgb_wgrad_set_row_bands(int bands);
 
 /* Host-side replay of how a wgrad launch splits the pair lists among its CTAs, for
@@ -500,6 +500,47 @@ int fgb_indice_weighted_sum_fwd(const void* feats, const uint32_t* indices, cons
  * in the feature dtype. */
 int fgb_indice_weighted_sum_bwd(const void* grad_out, const uint32_t* indices, const float* weight,
                                 float* grad_feats_f32, int64_t M, int64_t N, int C, int V, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Pipeline microbenchmark (no counterpart in the reference)
+ * --------------------------------------------------------------------- */
+
+/* What one SM sustains of the traffic and the MMAs of an fprop / dgrad stage
+ * (Ci = Co = 256, 16-bit), isolated from the conv kernel: per stage 32 KB of
+ * rows gathered at random from rows[n_rows][row_bytes] (row_bytes a multiple
+ * of 128), 32 KB of the dense operand from dense[dense_bytes] by TMA, and 8
+ * MMAs 128 x 256 x 16 on whatever the stage buffers hold.  `mode` is a sum of
+ *   FGB_MB_TMA      the dense-operand stream
+ *   FGB_MB_GATHER   the gathered stream (cp.async, 16 bytes per thread)
+ *   FGB_MB_MMA      the MMA stream
+ *   FGB_MB_COUPLED  MMAs wait for full stages and free them by tcgen05.commit,
+ *                   as in the conv kernel (else every stream runs by itself)
+ *   FGB_MB_GATHER4  gather by TMA tile::gather4 instead of cp.async
+ *   FGB_MB_PAIR     CTA pairs (tcgen05 cta_group::2, M = 256 over both CTAs,
+ *                   16 KB of the dense operand per CTA); implies the four above
+ *   FGB_MB_LEAN     coupled, without pairs: the MMA lane keeps the instructions
+ *                   between two stages' MMAs to a minimum (descriptors by one
+ *                   add, next stage probed in the shadow of the last MMAs)
+ * stages_a / stages_b: ring depths of the two operands (1..6, together within
+ * the shared memory of an SM).  issue_delay: cycles the MMA lane idles before
+ * it issues a stage's MMAs (0 = none): how much instruction time between two
+ * stages' MMAs the tensor pipe's queue hides.  One CTA per SM runs `iters` stages; *ms_out =
+ * the launch's duration (CUDA events on `stream`; the call synchronises).
+ * counters (host, [8], may be null) receive from CTA 0's MMA lane: cycles spent
+ * waiting for the dense operand, number of such waits, the same two for the
+ * gathered operand, total cycles of its loop.  The function allocates and frees
+ * a few bytes of device memory. */
+#define FGB_MB_TMA 1
+#define FGB_MB_GATHER 2
+#define FGB_MB_MMA 4
+#define FGB_MB_COUPLED 8
+#define FGB_MB_GATHER4 16
+#define FGB_MB_PAIR 32
+#define FGB_MB_LEAN 64
+int fgb_microbench_pipeline(int mode, int stages_a, int stages_b, int iters, int issue_delay,
+                            const void* rows, int64_t n_rows, int row_bytes,
+                            const void* dense, int64_t dense_bytes,
+                            float* ms_out, uint64_t* counters, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }
