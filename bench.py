@@ -925,7 +925,9 @@ def run_pipeline_microbench(args):
     dense = torch.zeros(27 * c * c, dtype=torch.float16, device=dev)
     iters = 2000
     T, G, M, C, G4, P, L = K.MB_TMA, K.MB_GATHER, K.MB_MMA, K.MB_COUPLED, K.MB_GATHER4, K.MB_PAIR, K.MB_LEAN
-    cases = [("mma alone", M, 3, 3, 0), ("mma alone, 128 idle cycles before each stage", M, 3, 3, 128),
+    M64, ST, SB128, SB512 = K.MB_M64, K.MB_STORE, K.MB_STORE_BULK128, K.MB_STORE_BULK512
+    cases = [("mma alone", M, 3, 3, 0), ("mma alone, 64 x 256 x 16 instead of 128 x 256 x 16", M | M64, 3, 3, 0),
+             ("mma alone, 128 idle cycles before each stage", M, 3, 3, 128),
              ("mma alone, 256 idle cycles before each stage", M, 3, 3, 256),
              ("tma alone", T, 3, 3, 0), ("gather alone (cp.async)", G, 3, 3, 0), ("gather alone (TMA gather4)", G | G4, 3, 3, 0),
              ("tma + gather, independent", T | G, 3, 3, 0), ("mma + tma + gather, independent", M | T | G, 3, 3, 0),
@@ -935,7 +937,11 @@ def run_pipeline_microbench(args):
              ("coupled, lean MMA lane: mma + tma + gather, 2 stages", L | C | M | T | G, 2, 2, 0),
              ("coupled, lean MMA lane: mma + tma + gather, 3 stages", L | C | M | T | G, 3, 3, 0),
              ("coupled, lean MMA lane: mma + tma + gather, 5 + 2 stages", L | C | M | T | G, 5, 2, 0),
-             ("CTA pairs, 3 stages", P, 3, 3, 0), ("CTA pairs, 4 stages", P, 4, 4, 0)]
+             ("CTA pairs, 3 stages", P, 3, 3, 0), ("CTA pairs, 4 stages", P, 4, 4, 0),
+             ("output stream alone: 16-byte stores, four 128-byte lines per warp instruction", ST, 3, 3, 0),
+             ("output stream alone: bulk async copies of 128 bytes", SB128, 3, 3, 0),
+             ("output stream alone: bulk async copies of 512-byte rows", SB512, 3, 3, 0),
+             ("mma + output stream (16-byte stores)", M | ST, 3, 3, 0)]
     sampler = ClockSampler(dev.index).start()
     out, launches = [], 0
     for name, mode, sa, sb, delay in cases:
@@ -948,8 +954,8 @@ def run_pipeline_microbench(args):
                 best, ctr = ms, c8
         pair = bool(mode & P)
         b_chunk = 16384 if pair else 32768
-        moved = ((32768 if mode & G or pair else 0) + (b_chunk if mode & T or pair else 0)) * iters
-        rec = {"case": name, "us_per_stage": round(best * 1e3 / iters, 4), "ingest_gbs_per_sm": round(moved / best * 1e-6, 1)}
+        moved = ((32768 if mode & (G | ST | SB128 | SB512) or pair else 0) + (b_chunk if mode & T or pair else 0)) * iters
+        rec = {"case": name, "us_per_stage": round(best * 1e3 / iters, 4), "moved_gbs_per_sm": round(moved / best * 1e-6, 1)}
         if mode & M or pair:
             rec["mma_frac_of_nominal"] = round(iters * 8 * 128 / 1.965e6 / best, 3)   # 8 MMAs x 128 cycles at 1965 MHz
             if mode & C or pair:

@@ -25,7 +25,14 @@ constexpr int kMbMaxStages = 6;
 constexpr int kMbAChunk = 32 * 1024;   // gathered rows per stage and CTA
 constexpr int kMbThreads = 352;        // warps 0-7 gather, 8 TMA lane, 9 consumer / relay, 10 MMA lane and TMEM owner
 
-enum : int { kMbTma = 1, kMbGather = 2, kMbMma = 4, kMbCoupled = 8, kMbGather4 = 16, kMbPair = 32, kMbLean = 64 };
+enum : int {
+  kMbTma = 1, kMbGather = 2, kMbMma = 4, kMbCoupled = 8, kMbGather4 = 16, kMbPair = 32, kMbLean = 64,
+  kMbM64 = 128,         // the MMAs are 64 x 256 x 16
+  kMbStore = 256,       // instead of the gather: the epilogue's output stream, 32 KB per stage to random rows of `rows`,
+                        // 16-byte stores that cover four 128-byte lines per warp instruction
+  kMbStoreBulk128 = 512,   // ... as bulk async copies shared -> global of 128 bytes (one per row piece and lane)
+  kMbStoreBulk512 = 1024,  // ... as bulk async copies of whole 512-byte rows
+};
 
 struct MbParams {
   const char* dense;
@@ -116,7 +123,49 @@ __global__ void __launch_bounds__(kMbThreads, 1) microbench_kernel(const __grid_
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  if (warp < 8) {
+  if (warp < 8 && (mode & (kMbStore | kMbStoreBulk128 | kMbStoreBulk512))) {
+    // ------------------------------------------------------------ output stream (what an epilogue writes)
+    // Every warp owns 4 KB of the first gathered stage as its staging buffer and writes it out p.iters times: 32 KB per
+    // "stage" and CTA.  The destination rows are random rows of `rows` (the benchmark's scratch).
+    uint32_t state = blockIdx.x * 2654435761u + tid * 40503u + 777u;
+    uint8_t* stage_out = gbuf + warp * 4096;
+    char* out = const_cast<char*>(p.rows);
+    const int pieces_per_row = p.row_bytes / 128;
+    for (int it = 0; it < p.iters; ++it) {
+      const int kb = it % pieces_per_row;
+      if (mode & kMbStore) {
+        // lane -> (row = 4 i + lane / 8, piece = lane % 8): eight lanes write one 128-byte line
+        state = state * 1664525u + 1013904223u;
+        const uint32_t my_row = (state >> 4) % p.n_rows;  // row of staging row `lane`
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = i * 4 + (lane >> 3), piece = lane & 7;
+          const uint32_t orow = __shfl_sync(0xffffffffu, my_row, row);
+          const uint4 val = *reinterpret_cast<const uint4*>(stage_out + row * 128 + ((piece ^ (row & 7)) << 4));
+          *reinterpret_cast<uint4*>(out + size_t(orow) * p.row_bytes + kb * 128 + piece * 16) = val;
+        }
+      } else if (mode & kMbStoreBulk128) {
+        state = state * 1664525u + 1013904223u;
+        const uint32_t orow = (state >> 4) % p.n_rows;
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 128;" ::"l"(out + size_t(orow) * p.row_bytes + kb * 128),
+                     "r"(smem_u32(stage_out + lane * 128))
+                     : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        if ((it & 3) == 3) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      } else {
+        // 4 KB per warp and stage = eight whole rows of 512 bytes: lanes 0-7 issue one copy each
+        state = state * 1664525u + 1013904223u;
+        const uint32_t orow = (state >> 4) % p.n_rows;
+        if (lane < 8 && p.row_bytes >= 512)
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 512;" ::"l"(out + size_t(orow) * p.row_bytes),
+                       "r"(smem_u32(stage_out + lane * 512))
+                       : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        if ((it & 3) == 3) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      }
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  } else if (warp < 8) {
     // ------------------------------------------------------------ gathered operand
     if ((mode & kMbGather) && (mode & kMbGather4)) {
       if (warp < 2) {  // lane l of warp h: rows 4l .. 4l+3 of half h, 512 bytes per instruction
@@ -251,7 +300,7 @@ __global__ void __launch_bounds__(kMbThreads, 1) microbench_kernel(const __grid_
         p.counters[4] = static_cast<unsigned long long>(clock64() - t_begin);
       }
     } else if ((mode & kMbMma) && lane == 0 && leader) {
-      const uint32_t idesc = make_idesc(kFmtF16, kPair ? 256 : 128, 256, 0, 0);
+      const uint32_t idesc = make_idesc(kFmtF16, kPair ? 256 : ((mode & kMbM64) ? 64 : 128), 256, 0, 0);
       unsigned long long cyc_t = 0, n_t = 0, cyc_g = 0, n_g = 0;
       const long long t_begin = clock64();
       // ring positions advanced by hand: a division by the run-time depth here would sit between two stages' MMAs
@@ -333,6 +382,8 @@ extern "C" int fgb_microbench_pipeline(int mode, int stages_a, int stages_b, int
   if (iters < 1 || n_rows < 1 || n_rows >= (int64_t(1) << 31) || row_bytes < 128 || row_bytes % 128 != 0) return FGB_E_SIZE;
   if (stages_a < 1 || stages_a > kMbMaxStages || stages_b < 1 || stages_b > kMbMaxStages) return FGB_E_SIZE;
   if ((mode & kMbCoupled) && !(mode & kMbMma)) return FGB_E_SIZE;
+  if ((mode & (kMbStore | kMbStoreBulk128 | kMbStoreBulk512)) && (mode & (kMbGather | kMbCoupled | kMbPair))) return FGB_E_SIZE;
+  if ((mode & kMbM64) && (mode & (kMbPair | kMbLean))) return FGB_E_SIZE;
   if ((reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(dense)) & 15u) return FGB_E_ALIGN;
   MbParams p{};
   p.b_chunk = pair ? 16 * 1024 : 32 * 1024;

@@ -390,6 +390,7 @@ def set_conv_splitk(splits: int) -> int:
 
 
 MB_TMA, MB_GATHER, MB_MMA, MB_COUPLED, MB_GATHER4, MB_PAIR, MB_LEAN = 1, 2, 4, 8, 16, 32, 64
+MB_M64, MB_STORE, MB_STORE_BULK128, MB_STORE_BULK512 = 128, 256, 512, 1024
 
 
 def microbench_pipeline(mode: int, rows: torch.Tensor, dense: torch.Tensor, iters: int = 2000, stages_a: int = 3, stages_b: int = 3,

@@ -521,6 +521,13 @@ int fgb_indice_weighted_sum_bwd(const void* grad_out, const uint32_t* indices, c
  *   FGB_MB_LEAN     coupled, without pairs: the MMA lane keeps the instructions
  *                   between two stages' MMAs to a minimum (descriptors by one
  *                   add, next stage probed in the shadow of the last MMAs)
+ *   FGB_MB_M64      the MMAs are 64 x 256 x 16 (MMA stream alone or independent)
+ *   FGB_MB_STORE, FGB_MB_STORE_BULK128, FGB_MB_STORE_BULK512   in place of
+ *                   the gather, the output stream of an epilogue: 32 KB per stage
+ *                   from shared memory to random rows of `rows` (which these
+ *                   modes overwrite), as 16-byte stores that cover four 128-byte
+ *                   lines per warp instruction, as bulk async copies of 128 bytes,
+ *                   or of whole 512-byte rows; not with GATHER, COUPLED or PAIR
  * stages_a / stages_b: ring depths of the two operands (1..6, together within
  * the shared memory of an SM).  issue_delay: cycles the MMA lane idles before
  * it issues a stage's MMAs (0 = none): how much instruction time between two
@@ -537,6 +544,10 @@ int fgb_indice_weighted_sum_bwd(const void* grad_out, const uint32_t* indices, c
 #define FGB_MB_GATHER4 16
 #define FGB_MB_PAIR 32
 #define FGB_MB_LEAN 64
+#define FGB_MB_M64 128
+#define FGB_MB_STORE 256
+#define FGB_MB_STORE_BULK128 512
+#define FGB_MB_STORE_BULK512 1024
 int fgb_microbench_pipeline(int mode, int stages_a, int stages_b, int iters, int issue_delay,
                             const void* rows, int64_t n_rows, int row_bytes,
                             const void* dense, int64_t dense_bytes,

@@ -17,6 +17,7 @@ def buffers():
 @pytest.mark.parametrize("name,mode,sa,sb", [
     ("mma", 4, 3, 3), ("tma", 1, 3, 3), ("gather", 2, 3, 3), ("gather4", 2 | 16, 3, 3), ("independent", 7, 3, 3),
     ("coupled", 15, 3, 3), ("coupled_deep", 15, 5, 2), ("lean", 15 | 64, 3, 3), ("lean_tma", 13 | 64, 3, 3), ("coupled_gather4", 15 | 16, 3, 3), ("pair", 32, 3, 3), ("pair4", 32, 4, 4),
+    ("m64", 4 | 128, 3, 3), ("store", 256, 3, 3), ("store_bulk128", 512, 3, 3), ("store_bulk512", 1024, 3, 3), ("mma_and_store", 4 | 256, 3, 3),
 ])
 def test_modes_run(buffers, name, mode, sa, sb):
     from flexgemm_b200.kernels import cuda as K
