@@ -26,7 +26,7 @@ _PROTOTYPES = {
                                             _P, c_int64, c_int, _P, _P, _P, _P, _P, _P, _P]),
     "fgb_pp_sorted_idx_workspace_bytes": (c_int64, [c_int64]),
     "fgb_pp_sorted_idx": (c_int, [_P, c_int64, c_int, _P, _P, c_int64, _P, _P]),
-    "fgb_pp_valid_signal": (c_int, [_P, _P, c_int64, c_int, _P, _P, _P, _P, _P]),
+    "fgb_pp_valid_signal": (c_int, [_P, _P, c_int64, c_int, _P, _P, _P, _P, _P, _P]),
     "fgb_pp_tile_masks": (c_int, [_P, _P, c_int64, c_int, _P, _P]),
     "fgb_pp_valid_kernel": (c_int, [_P, c_int64, _P, _P, _P]),
     "fgb_conv_tile_rows": (c_int, []),

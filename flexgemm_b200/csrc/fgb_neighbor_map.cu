@@ -351,15 +351,17 @@ static int build_impl(const int32_t* coords, uint32_t n, int B, Grid3 g, Stencil
   const size_t table_words = table_bytes / 4;
   const unsigned clear_grid = static_cast<unsigned>(std::min<size_t>(ceil_div(static_cast<int64_t>(table_words), 256 * 8), 148 * 16));
   // The sorted-input path needs one 8-byte entry per (b, x, y) column and keeps them in the caller's table memory; the
-  // map tile of a CTA must fit shared memory.  seg[0] (rewritten by the scan at the end) carries the device-side
-  // decision between the two paths.
+  // map tile of a CTA must fit shared memory.  seg[V + 1] carries the device-side decision between the two paths (0 =
+  // rows in key order, the table-free path built the map) and stays there for the pair-list kernel.
   const uint64_t columns = static_cast<uint64_t>(B > 0 ? B : 0) * g.W * g.H;
   const bool try_sorted = columns > 0 && columns * sizeof(uint2) <= table_bytes;
-  uint32_t* unsorted = try_sorted ? seg : nullptr;
-  if (try_sorted) {
-    cudaError_t e = cudaMemsetAsync(seg, 0, sizeof(uint32_t), s);
+  uint32_t* unsorted = try_sorted ? seg + st.V + 1 : nullptr;
+  {
+    cudaError_t e = cudaMemsetAsync(seg + st.V + 1, try_sorted ? 0 : 1, sizeof(uint32_t), s);
     if (e != cudaSuccess) return cuda_status(e);
-    e = cudaMemsetAsync(table, 0xFF, columns * sizeof(uint2), s);
+  }
+  if (try_sorted) {
+    cudaError_t e = cudaMemsetAsync(table, 0xFF, columns * sizeof(uint2), s);
     if (e != cudaSuccess) return cuda_status(e);
     column_index_kernel<kKeyBits><<<static_cast<unsigned>(ceil_div(n, 256)), 256, 0, s>>>(c4, n, g, columns, static_cast<uint2*>(table), unsorted);
   }

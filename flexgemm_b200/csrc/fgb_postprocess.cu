@@ -10,21 +10,33 @@ namespace fgb {
 // counts were scanned into block_offsets).  The CTA's slice of the map is
 // staged in shared memory with coalesced loads; rank inside the CTA comes from
 // warp ballots, so every offset's list keeps ascending row order.
+//
+// Rows in key order (submanifold map, *unsorted == 0) need no map at all: a translation keeps the key order, so the
+// neighbours of offset v's output rows, in list order, are exactly the output rows of the opposite offset V-1-v in
+// their list order -- valid_signal_i of offset v is valid_signal_o of offset V-1-v, and both follow from the masks.
 __global__ void __launch_bounds__(kMapBlock)
     valid_signal_kernel(const uint32_t* __restrict__ nbr, const int32_t* __restrict__ gray, uint32_t n, int V,
                         const uint32_t* __restrict__ block_offsets, uint32_t nblk, const uint32_t* __restrict__ seg,
-                        uint32_t* __restrict__ vs_i, uint32_t* __restrict__ vs_o) {
+                        uint32_t* __restrict__ vs_i, uint32_t* __restrict__ vs_o, const uint32_t* __restrict__ unsorted) {
   extern __shared__ uint32_t s_map[];     // [256 * V]
   __shared__ uint32_t s_wcount[32][8];    // valid rows per (offset, warp), then exclusive prefix
   __shared__ uint32_t s_base[32];         // list position of the CTA's first pair, per offset
+  __shared__ uint32_t s_base_opp[32];     // the same position in the opposite offset's list
   const uint32_t n0 = blockIdx.x * kMapBlock;
   const uint32_t nv = min(static_cast<uint32_t>(kMapBlock), n - n0);
   const int t = threadIdx.x, lane = t & 31, w = t >> 5;
-  const uint32_t words = nv * V;
-  const uint32_t* src = nbr + static_cast<size_t>(n0) * V;
-  for (uint32_t i = t; i < words; i += kMapBlock) s_map[i] = __ldg(&src[i]);
+  const bool mirror = unsorted != nullptr && __ldg(unsorted) == 0u;  // the same for every thread of the grid
+  if (!mirror) {
+    const uint32_t words = nv * V;
+    const uint32_t* src = nbr + static_cast<size_t>(n0) * V;
+    for (uint32_t i = t; i < words; i += kMapBlock) s_map[i] = __ldg(&src[i]);
+  }
   const uint32_t g = t < nv ? static_cast<uint32_t>(__ldg(&gray[n0 + t])) : 0u;
-  if (t < V) s_base[t] = seg[t] + block_offsets[static_cast<size_t>(t) * nblk + blockIdx.x];
+  if (t < V) {
+    const uint32_t in_list = block_offsets[static_cast<size_t>(t) * nblk + blockIdx.x];
+    s_base[t] = seg[t] + in_list;
+    s_base_opp[t] = seg[V - 1 - t] + in_list;
+  }
   for (int v = 0; v < V; ++v) {
     const uint32_t b = __ballot_sync(0xffffffffu, (g >> v) & 1u);
     if (lane == 0) s_wcount[v][w] = __popc(b);
@@ -43,9 +55,10 @@ __global__ void __launch_bounds__(kMapBlock)
     const bool ok = (g >> v) & 1u;
     const uint32_t b = __ballot_sync(0xffffffffu, ok);
     if (ok) {
-      const uint32_t pos = s_base[v] + s_wcount[v][w] + __popc(b & ((1u << lane) - 1u));
-      vs_o[pos] = n0 + t;
-      vs_i[pos] = s_map[t * V + v];
+      const uint32_t rank = s_wcount[v][w] + __popc(b & ((1u << lane) - 1u));
+      vs_o[s_base[v] + rank] = n0 + t;
+      if (mirror) vs_i[s_base_opp[v] + rank] = n0 + t;
+      else vs_i[s_base[v] + rank] = s_map[t * V + v];
     }
   }
 }
@@ -121,7 +134,7 @@ __global__ void __launch_bounds__(1024)
 
 extern "C" int fgb_pp_valid_signal(const uint32_t* neighbor_map, const int32_t* gray_code, int64_t n, int V,
                                    const uint32_t* block_offsets, const uint32_t* valid_signal_seg, uint32_t* valid_signal_i,
-                                   uint32_t* valid_signal_o, void* stream) {
+                                   uint32_t* valid_signal_o, const uint32_t* unsorted_flag, void* stream) {
   using namespace fgb;
   if (n < 0 || n >= (int64_t(1) << 32) - 1 || V < 1 || V > 32) return FGB_E_SIZE;
   if (n == 0) return FGB_OK;
@@ -129,7 +142,8 @@ extern "C" int fgb_pp_valid_signal(const uint32_t* neighbor_map, const int32_t* 
   const uint32_t nblk = static_cast<uint32_t>(ceil_div(n, kMapBlock));
   const size_t smem = size_t(kMapBlock) * V * sizeof(uint32_t);
   valid_signal_kernel<<<nblk, kMapBlock, smem, static_cast<cudaStream_t>(stream)>>>(
-      neighbor_map, gray_code, static_cast<uint32_t>(n), V, block_offsets, nblk, valid_signal_seg, valid_signal_i, valid_signal_o);
+      neighbor_map, gray_code, static_cast<uint32_t>(n), V, block_offsets, nblk, valid_signal_seg, valid_signal_i, valid_signal_o,
+      unsorted_flag);
   return launch_status();
 }
 

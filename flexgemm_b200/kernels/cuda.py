@@ -140,8 +140,9 @@ def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table:
                             slots: int) -> Dict[str, torch.Tensor]:
     """Hash build + lookup.  Returns neighbor_map [N,V] uint32, gray_code and
     binary_code [N] int32, block_offsets [V*nblk] uint32, valid_signal_seg [V+1]
-    uint32 and ``meta`` (uint32 [V+2]: the segment array followed by this call's
-    own status word, so that one device-to-host copy fetches both)."""
+    uint32 and ``meta`` (uint32 [V+3]: the segment array, the word that is 0 when
+    the rows were in key order -- ``order_flag`` -- and this call's own status
+    word, so that one device-to-host copy fetches all of them)."""
     _require_cuda(coords, "coords")
     lib = _cabi.lib()
     dev = coords.device
@@ -149,13 +150,14 @@ def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table:
     B, _, W, H, D = [int(s) for s in shape]
     V = int(ksize[0]) * int(ksize[1]) * int(ksize[2])
     nblk = _cabi.check_size(lib.fgb_map_num_blocks(n), "fgb_map_num_blocks")
-    meta = torch.zeros(V + 2, dtype=torch.uint32, device=dev)
+    meta = torch.zeros(V + 3, dtype=torch.uint32, device=dev)
     out = {
         "neighbor_map": torch.empty((n, V), dtype=torch.uint32, device=dev),
         "gray_code": torch.empty(n, dtype=torch.int32, device=dev),
         "binary_code": torch.empty(n, dtype=torch.int32, device=dev),
         "block_offsets": torch.empty(max(V * nblk, 1), dtype=torch.uint32, device=dev),
         "valid_signal_seg": meta[:V + 1],
+        "order_flag": meta[V + 1:V + 2],
         "meta": meta,
     }
     rc = lib.fgb_subm_build_neighbor_map(
@@ -164,7 +166,7 @@ def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table:
         table.data_ptr(), int(slots), int(key_bits),
         _ptr(out["neighbor_map"]), _ptr(out["gray_code"]), _ptr(out["binary_code"]),
         out["block_offsets"].data_ptr(), meta.data_ptr(),
-        meta.data_ptr() + 4 * (V + 1), _stream(dev))
+        meta.data_ptr() + 4 * (V + 2), _stream(dev))
     _cabi.check(rc, "fgb_subm_build_neighbor_map")
     # order check + column index, table clear, insert, hash lookup, column lookup, block scan, prefix
     _count(7)
@@ -313,15 +315,17 @@ def sorted_idx_from_binary(binary_code: torch.Tensor, key_bits: int) -> torch.Te
 
 
 def valid_signal(neighbor_map: torch.Tensor, gray_code: torch.Tensor, block_offsets: torch.Tensor,
-                 valid_signal_seg: torch.Tensor, num_pairs: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """(valid_signal_i, valid_signal_o), uint32 [num_pairs] each."""
+                 valid_signal_seg: torch.Tensor, num_pairs: int,
+                 order_flag: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(valid_signal_i, valid_signal_o), uint32 [num_pairs] each.  ``order_flag``: the submanifold build's word that is
+    0 when the rows were in key order (the lists then follow from the masks, the map is not read)."""
     lib = _cabi.lib()
     dev = neighbor_map.device
     n, V = neighbor_map.shape
     vs_i = torch.empty(num_pairs, dtype=torch.uint32, device=dev)
     vs_o = torch.empty(num_pairs, dtype=torch.uint32, device=dev)
     rc = lib.fgb_pp_valid_signal(_ptr(neighbor_map), _ptr(gray_code), n, V, block_offsets.data_ptr(),
-                                 valid_signal_seg.data_ptr(), _ptr(vs_i), _ptr(vs_o), _stream(dev))
+                                 valid_signal_seg.data_ptr(), _ptr(vs_i), _ptr(vs_o), _ptr(order_flag), _stream(dev))
     _cabi.check(rc, "fgb_pp_valid_signal")
     _count(1)
     return vs_i, vs_o

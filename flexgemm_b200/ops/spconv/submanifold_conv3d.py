@@ -112,7 +112,8 @@ class SubMConv3dFunction(Function):
             kernels.cuda.raise_for_status(int(meta_host[-1]))
             seg = built["valid_signal_seg"]
             num_pairs = int(meta_host[V])
-            vs_i, vs_o = kernels.cuda.valid_signal(built["neighbor_map"], built["gray_code"], built["block_offsets"], seg, num_pairs)
+            vs_i, vs_o = kernels.cuda.valid_signal(built["neighbor_map"], built["gray_code"], built["block_offsets"], seg, num_pairs,
+                                                   built["order_flag"])
             cache["valid_signal_seg"] = seg
             cache["valid_signal_i"] = vs_i
             cache["valid_signal_o"] = vs_o

@@ -77,8 +77,11 @@ int64_t fgb_map_num_blocks(int64_t n);
  * 0xffffffff.  Also writes the per-voxel validity mask gray_code[i] (bit v set
  * iff valid), its Gray-to-binary decode binary_code[i], block_offsets
  * [V * nblk] (for offset v and 256-voxel block k, the number of valid pairs of
- * offset v in the blocks before k) and valid_signal_seg[V + 1] (exclusive
- * prefix of the per-offset totals; its last entry is the pair count L).
+ * offset v in the blocks before k) and valid_signal_seg[V + 2]: V + 1 entries
+ * of the exclusive prefix of the per-offset totals (entry V is the pair count
+ * L), followed by one word that is 0 when the rows were found in key order (the
+ * table-free path built the map) and non-zero otherwise; fgb_pp_valid_signal
+ * takes a pointer to that word.
  *
  * Stands in for hashmap_build_submanifold_conv_neighbour_map
  * (flex_gemm/kernels/cuda/spconv/subm_neighbor_map.cu:104-162, with
@@ -133,6 +136,12 @@ int fgb_pp_sorted_idx(const int32_t* binary_code, int64_t n, int key_bits,
  * group: valid_signal_o[p] = row, valid_signal_i[p] = neighbor_map[row, v].
  * `block_offsets` and `valid_signal_seg` are the arrays written by
  * fgb_subm_build_neighbor_map.  The lists need valid_signal_seg[V] entries.
+ * unsorted_flag (device, may be null): &valid_signal_seg[V + 1] of a
+ * submanifold build.  When it holds 0 the rows are in key order; a translation
+ * keeps that order, so valid_signal_i of offset v equals valid_signal_o of the
+ * opposite offset V-1-v and both lists are written from the masks alone,
+ * without reading the map.  Null (the generic strided conv, whose map has no
+ * such symmetry) or non-zero: the lists are gathered from the map.
  * Stands in for the cumsum + gather_idx_val_seg_from_prefix_sum_kernel part of
  * neighbor_map_post_process_for_masked_implicit_gemm_1
  * (migemm_neighmap_pp.cu:157-178, 224-240). */
@@ -140,7 +149,7 @@ int fgb_pp_valid_signal(const uint32_t* neighbor_map, const int32_t* gray_code,
                         int64_t n, int V,
                         const uint32_t* block_offsets, const uint32_t* valid_signal_seg,
                         uint32_t* valid_signal_i, uint32_t* valid_signal_o,
-                        void* stream);
+                        const uint32_t* unsorted_flag, void* stream);
 
 /* tile_masks[t] = OR of gray_code[sorted_idx[r]] over the rows r of tile t
  * (tile = `block` consecutive sorted rows, a power of two in [8, 1024]).

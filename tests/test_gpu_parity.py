@@ -132,7 +132,9 @@ def test_sorted_and_hash_paths_agree(K):
     check_cache(build_cache(base, shape), ref, 27)                       # sorted
     perm = rng.permutation(base.shape[0])
     shuffled = np.ascontiguousarray(base[perm])
-    got = u32(build_cache(shuffled, shape)["neighbor_map"])              # hash path
+    shuffled_cache = build_cache(shuffled, shape)                        # hash path
+    check_cache(shuffled_cache, orc.neighbor_cache(shuffled, shape), 27)  # pair lists gathered from the map
+    got = u32(shuffled_cache["neighbor_map"])
     inv = np.empty_like(perm)
     inv[perm] = np.arange(perm.size)
     want = ref["neighbor_map"][perm]                                     # rows follow the voxels ...
