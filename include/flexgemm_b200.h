@@ -393,8 +393,10 @@ int fgb_sparse_out_coords_finalize(const void* keys, int64_t count, int key_bits
  * neighbor_map_bwd[i, v] = o for every hit (other entries 0xffffffff).  The
  * table (fgb_hash_table_bytes(slots, key_bits) bytes, slots >= n_in) is built
  * over the input voxels.  gray_code / binary_code / block_counts /
- * valid_signal_seg describe the FORWARD map exactly as in
- * fgb_subm_build_neighbor_map (block_counts sized by fgb_map_num_blocks(n_out)).
+ * valid_signal_seg describe the FORWARD map as in
+ * fgb_subm_build_neighbor_map (block_counts sized by fgb_map_num_blocks(n_out);
+ * valid_signal_seg has V + 1 entries here: there is no key-order word, pass a
+ * null unsorted_flag to fgb_pp_valid_signal).
  * Stands in for hashmap_build_sparse_conv_neighbour_map
  * (sparse_neighbor_map.cu:405-568). */
 int fgb_sparse_build_neighbor_map(const int32_t* in_coords, int64_t n_in,
