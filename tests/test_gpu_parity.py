@@ -148,6 +148,34 @@ def test_sorted_and_hash_paths_agree(K):
     check_cache(build_cache(far, big), orc.neighbor_cache(far, big), 27)
 
 
+def test_pair_lists_with_and_without_the_map(K):
+    """Rows in key order: the build leaves 0 in the word after the segment table and the pair lists then come from the
+    masks alone; the same call without that word gathers them from the map.  Both must be the oracle's lists.  Shuffled
+    rows leave a non-zero word."""
+    from flexgemm_b200.ops import spconv, utils
+    base = orc.shell_coords(48, batch=2, scales=(1.0, 0.7))
+    shape = (2, 0, 48, 48, 48)
+    for ksize, dil in (((3, 3, 3), (1, 1, 1)), ((3, 1, 5), (2, 1, 1))):
+        V = ksize[0] * ksize[1] * ksize[2]
+        ref = orc.neighbor_cache(base, shape, ksize, dil)
+        coords = torch.from_numpy(base).to(DEV)
+        n = coords.shape[0]
+        slots = max(int(spconv.HASHMAP_RATIO * n), n, 1)
+        table, key_bits = utils.init_table(torch.Size(shape), slots, coords.device)
+        built = K.subm_build_neighbor_map(coords, torch.Size(shape), ksize, dil, table, key_bits, slots)
+        assert int(built["order_flag"].cpu().view(torch.int32).item()) == 0
+        pairs = int(ref["valid_signal_seg"][V])
+        for flag in (built["order_flag"], None):
+            vs_i, vs_o = K.valid_signal(built["neighbor_map"], built["gray_code"], built["block_offsets"], built["valid_signal_seg"],
+                                        pairs, flag)
+            assert np.array_equal(u32(vs_i), ref["valid_signal_i"]) and np.array_equal(u32(vs_o), ref["valid_signal_o"])
+    rng = np.random.default_rng(5)
+    shuffled = torch.from_numpy(np.ascontiguousarray(base[rng.permutation(base.shape[0])])).to(DEV)
+    table, key_bits = utils.init_table(torch.Size(shape), slots, shuffled.device)
+    built = K.subm_build_neighbor_map(shuffled, torch.Size(shape), (3, 3, 3), (1, 1, 1), table, key_bits, slots)
+    assert int(built["order_flag"].cpu().view(torch.int32).item()) != 0
+
+
 def test_sorted_path_runs_much_longer_than_a_block(K):
     """A sparse plane between two dense ones: the 256 voxels of a block span the
     whole sparse plane, so the run of rows of the next plane that can hold their
