@@ -79,4 +79,35 @@ inline int ensure_dynamic_smem(PerDeviceTable& table, Kernel kernel, size_t byte
   });
 }
 
+// Chained launches (programmatic dependent launch).  A kernel started with launch_chained may be set up on the SMs
+// while the kernel before it in the stream is still running.  It must call chain_wait() before it touches global
+// memory: the call returns once the earlier kernel has completed and its writes are visible (at once when the kernel
+// was launched the ordinary way).  chain_release() lets the next chained kernel of the stream begin its own set-up; the
+// next kernel is not started before every CTA of this one has called it or exited, so a chain cannot starve itself.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// first error of a sequence of launches
+struct LaunchErrors {
+  cudaError_t first = cudaSuccess;
+  void add(cudaError_t e) {
+    if (e != cudaSuccess && first == cudaSuccess) first = e;
+  }
+};
+
 }  // namespace fgb

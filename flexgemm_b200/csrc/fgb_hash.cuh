@@ -12,6 +12,7 @@
 #pragma once
 
 #include "fgb_common.cuh"
+#include "fgb_device.cuh"
 
 namespace fgb {
 
@@ -108,6 +109,8 @@ template <int kKeyBits>
 __global__ void __launch_bounds__(kMapBlock) hash_insert_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g,
                                                                 void* table_mem, uint32_t slots, int32_t* status,
                                                                 const uint32_t* __restrict__ unsorted) {
+  chain_release();
+  chain_wait();
   if (unsorted != nullptr && *unsorted == 0u) return;
   const uint32_t i = blockIdx.x * kMapBlock + threadIdx.x;
   if (i >= n) return;

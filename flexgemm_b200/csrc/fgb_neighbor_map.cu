@@ -31,6 +31,7 @@
 #include <type_traits>
 
 #include "fgb_common.cuh"
+#include "fgb_device.cuh"
 #include "fgb_hash.cuh"
 
 namespace fgb {
@@ -58,6 +59,8 @@ __global__ void __launch_bounds__(kMapBlock)
                        uint32_t* __restrict__ nbr, uint32_t* __restrict__ nbr_bwd, int32_t* __restrict__ gray_out,
                        int32_t* __restrict__ binary_out, uint32_t* __restrict__ block_counts, uint32_t nblk,
                        const uint32_t* __restrict__ unsorted) {
+  chain_release();
+  chain_wait();
   if (unsorted != nullptr && *unsorted == 0u) return;  // the sorted-input kernel builds the map
   __shared__ int4 s_coord[kMapBlock];
   __shared__ uint32_t s_gray[kMapBlock];
@@ -133,8 +136,12 @@ __global__ void __launch_bounds__(kMapBlock)
 }
 
 // CTA v turns block_counts[v, :] into exclusive offsets in place and leaves the
-// total of offset v in seg[v + 1].
-__global__ void __launch_bounds__(1024) block_scan_kernel(uint32_t* __restrict__ block_counts, uint32_t nblk, uint32_t* __restrict__ seg) {
+// total of offset v in seg[v + 1].  With `finish` the CTA that ends last also turns the totals into the segment table
+// (what seg_prefix_kernel does as a launch of its own); seg[0] counts the finished CTAs and must be 0 on entry.
+__global__ void __launch_bounds__(1024) block_scan_kernel(uint32_t* __restrict__ block_counts, uint32_t nblk, uint32_t* __restrict__ seg,
+                                                          bool finish) {
+  chain_release();
+  chain_wait();
   __shared__ uint32_t s_warp[32];
   __shared__ uint32_t s_carry;
   uint32_t* row = block_counts + static_cast<size_t>(blockIdx.x) * nblk;
@@ -169,10 +176,26 @@ __global__ void __launch_bounds__(1024) block_scan_kernel(uint32_t* __restrict__
     if (t == 1023) s_carry = carry + s_warp[31];
     __syncthreads();
   }
-  if (t == 0) seg[blockIdx.x + 1] = s_carry;
+  if (t == 0) {
+    seg[blockIdx.x + 1] = s_carry;
+    if (finish) {
+      __threadfence();
+      if (atomicAdd(&seg[0], 1u) == gridDim.x - 1) {  // every total is written
+        __threadfence();
+        uint32_t acc = 0;
+        for (uint32_t v = 1; v <= gridDim.x; ++v) {
+          acc += *reinterpret_cast<volatile uint32_t*>(&seg[v]);
+          seg[v] = acc;
+        }
+        seg[0] = 0;
+      }
+    }
+  }
 }
 
 __global__ void seg_prefix_kernel(uint32_t* seg, int V) {
+  chain_release();
+  chain_wait();
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     uint32_t acc = 0;
     seg[0] = 0;
@@ -193,6 +216,8 @@ __global__ void seg_prefix_kernel(uint32_t* seg, int V) {
 template <int kKeyBits>
 __global__ void __launch_bounds__(256) column_index_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, uint64_t columns,
                                                           uint2* __restrict__ col_table, uint32_t* unsorted) {
+  chain_release();
+  chain_wait();
   const uint32_t i = blockIdx.x * 256u + threadIdx.x;
   // an earlier CTA found the rows out of order: the table will not be used.  (Lane 0's reading decides for the warp:
   // the word may change between the lanes' loads, and the vote below needs the whole warp.)
@@ -223,6 +248,8 @@ __global__ void __launch_bounds__(256) column_index_kernel(const int4* __restric
 
 // fills the table with the empty pattern unless the sorted-input path runs
 __global__ void __launch_bounds__(256) table_clear_kernel(uint32_t* __restrict__ words, size_t count, const uint32_t* __restrict__ unsorted) {
+  chain_release();
+  chain_wait();
   if (unsorted != nullptr && *unsorted == 0u) return;
   for (size_t i = blockIdx.x * size_t(256) + threadIdx.x; i < count; i += size_t(gridDim.x) * 256) words[i] = 0xFFFFFFFFu;
 }
@@ -240,6 +267,8 @@ __global__ void __launch_bounds__(kMapBlock)
     subm_column_lookup_kernel(const int4* __restrict__ coords, uint32_t n, Grid3 g, Stencil st, const uint2* __restrict__ col_table,
                               uint32_t* __restrict__ nbr, int32_t* __restrict__ gray_out, int32_t* __restrict__ binary_out,
                               uint32_t* __restrict__ block_counts, uint32_t nblk, const uint32_t* __restrict__ unsorted) {
+  chain_release();
+  chain_wait();
   if (*unsorted != 0u) return;  // the hash kernels build the map
   extern __shared__ __align__(16) uint32_t s_nbr[];  // [kMapBlock * V]
   __shared__ int4 s_coord[kMapBlock];                // (column index, x, y, z)
@@ -357,7 +386,9 @@ static int build_impl(const int32_t* coords, uint32_t n, int B, Grid3 g, Stencil
   const bool try_sorted = columns > 0 && columns * sizeof(uint2) <= table_bytes;
   uint32_t* unsorted = try_sorted ? seg + st.V + 1 : nullptr;
   {
-    cudaError_t e = cudaMemsetAsync(seg + st.V + 1, try_sorted ? 0 : 1, sizeof(uint32_t), s);
+    // seg[0] = 0: the scan's count of finished CTAs; seg[V + 1]: the key-order word
+    cudaError_t e = cudaMemsetAsync(seg, 0, (st.V + 2) * sizeof(uint32_t), s);
+    if (e == cudaSuccess && !try_sorted) e = cudaMemsetAsync(seg + st.V + 1, 1, sizeof(uint32_t), s);
     if (e != cudaSuccess) return cuda_status(e);
   }
   if (try_sorted) {
@@ -365,23 +396,25 @@ static int build_impl(const int32_t* coords, uint32_t n, int B, Grid3 g, Stencil
     if (e != cudaSuccess) return cuda_status(e);
     column_index_kernel<kKeyBits><<<static_cast<unsigned>(ceil_div(n, 256)), 256, 0, s>>>(c4, n, g, columns, static_cast<uint2*>(table), unsorted);
   }
-  table_clear_kernel<<<clear_grid > 0 ? clear_grid : 1, 256, 0, s>>>(static_cast<uint32_t*>(table), table_words, unsorted);
-  hash_insert_kernel<kKeyBits><<<nblk, kMapBlock, 0, s>>>(c4, n, g, table, slots, status, unsorted);
-  subm_lookup_kernel<kKeyBits, false><<<nblk, kMapBlock, 0, s>>>(c4, n, g, st, table, slots, nbr, nullptr, gray, binary, block_counts,
-                                                                nblk, unsorted);
+  // from here on every kernel is chained to the one before it (fgb_device.cuh): the launches overlap the kernels' tails
+  LaunchErrors chain;
+  chain.add(launch_chained(table_clear_kernel, dim3(clear_grid > 0 ? clear_grid : 1), dim3(256), 0, s, static_cast<uint32_t*>(table),
+                           table_words, unsorted));
+  chain.add(launch_chained(hash_insert_kernel<kKeyBits>, dim3(nblk), dim3(kMapBlock), 0, s, c4, n, g, table, slots, status, unsorted));
+  chain.add(launch_chained(subm_lookup_kernel<kKeyBits, false>, dim3(nblk), dim3(kMapBlock), 0, s, c4, n, g, st, table, slots, nbr,
+                           static_cast<uint32_t*>(nullptr), gray, binary, block_counts, nblk, unsorted));
   if (try_sorted) {
     const size_t smem = size_t(kMapBlock) * st.V * sizeof(uint32_t);
     const bool unit = st.Kw == 3 && st.Kh == 3 && st.Kd == 3 && st.Dw == 1 && st.Dh == 1 && st.Dd == 1;
     if (unit)
-      subm_column_lookup_kernel<kKeyBits, true><<<nblk, kMapBlock, smem, s>>>(c4, n, g, st, static_cast<const uint2*>(table), nbr, gray, binary,
-                                                                             block_counts, nblk, unsorted);
+      chain.add(launch_chained(subm_column_lookup_kernel<kKeyBits, true>, dim3(nblk), dim3(kMapBlock), smem, s, c4, n, g, st,
+                               static_cast<const uint2*>(table), nbr, gray, binary, block_counts, nblk, unsorted));
     else
-      subm_column_lookup_kernel<kKeyBits, false><<<nblk, kMapBlock, smem, s>>>(c4, n, g, st, static_cast<const uint2*>(table), nbr, gray,
-                                                                              binary, block_counts, nblk, unsorted);
+      chain.add(launch_chained(subm_column_lookup_kernel<kKeyBits, false>, dim3(nblk), dim3(kMapBlock), smem, s, c4, n, g, st,
+                               static_cast<const uint2*>(table), nbr, gray, binary, block_counts, nblk, unsorted));
   }
-  block_scan_kernel<<<st.V, 1024, 0, s>>>(block_counts, nblk, seg);
-  seg_prefix_kernel<<<1, 32, 0, s>>>(seg, st.V);
-  return launch_status();
+  chain.add(launch_chained(block_scan_kernel, dim3(st.V), dim3(1024), 0, s, block_counts, nblk, seg, true));
+  return chain.first != cudaSuccess ? cuda_status(chain.first) : launch_status();
 }
 
 // generic sparse conv: table over the input voxels, rows = output voxels
@@ -395,7 +428,7 @@ static int build_general_impl(const int32_t* in_coords, uint32_t n_in, const int
   const uint32_t nblk = static_cast<uint32_t>(ceil_div(n_out, kMapBlock));
   subm_lookup_kernel<kKeyBits, true><<<nblk, kMapBlock, 0, s>>>(reinterpret_cast<const int4*>(out_coords), n_out, g, st, table, slots,
                                                                nbr, nbr_bwd, gray, binary, block_counts, nblk, nullptr);
-  block_scan_kernel<<<st.V, 1024, 0, s>>>(block_counts, nblk, seg);
+  block_scan_kernel<<<st.V, 1024, 0, s>>>(block_counts, nblk, seg, false);
   seg_prefix_kernel<<<1, 32, 0, s>>>(seg, st.V);
   return launch_status();
 }

@@ -2,6 +2,7 @@
 // wgrad pair lists, per-tile offset masks and their list form (the sorted row
 // order is in fgb_sort.cu).
 #include "fgb_common.cuh"
+#include "fgb_device.cuh"
 
 namespace fgb {
 
@@ -25,6 +26,8 @@ __global__ void __launch_bounds__(kMapBlock)
   const uint32_t n0 = blockIdx.x * kMapBlock;
   const uint32_t nv = min(static_cast<uint32_t>(kMapBlock), n - n0);
   const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+  chain_release();
+  chain_wait();
   const bool mirror = unsorted != nullptr && __ldg(unsorted) == 0u;  // the same for every thread of the grid
   if (!mirror) {
     const uint32_t words = nv * V;
@@ -141,9 +144,10 @@ extern "C" int fgb_pp_valid_signal(const uint32_t* neighbor_map, const int32_t* 
   if (!neighbor_map || !gray_code || !block_offsets || !valid_signal_seg || !valid_signal_i || !valid_signal_o) return FGB_E_NULL;
   const uint32_t nblk = static_cast<uint32_t>(ceil_div(n, kMapBlock));
   const size_t smem = size_t(kMapBlock) * V * sizeof(uint32_t);
-  valid_signal_kernel<<<nblk, kMapBlock, smem, static_cast<cudaStream_t>(stream)>>>(
-      neighbor_map, gray_code, static_cast<uint32_t>(n), V, block_offsets, nblk, valid_signal_seg, valid_signal_i, valid_signal_o,
-      unsorted_flag);
+  const cudaError_t e = launch_chained(valid_signal_kernel, dim3(nblk), dim3(kMapBlock), smem, static_cast<cudaStream_t>(stream), neighbor_map,
+                                       gray_code, static_cast<uint32_t>(n), V, block_offsets, nblk, valid_signal_seg, valid_signal_i,
+                                       valid_signal_o, unsorted_flag);
+  if (e != cudaSuccess) return cuda_status(e);
   return launch_status();
 }
 

@@ -20,6 +20,7 @@
 #include <algorithm>
 
 #include "fgb_common.cuh"
+#include "fgb_device.cuh"
 
 namespace fgb {
 
@@ -35,7 +36,9 @@ constexpr uint32_t kLookbackPolls = 1u << 22;   // of >= 32 ns each: far beyond 
 __global__ void __launch_bounds__(kSortThreads) sort_histogram_kernel(const int32_t* __restrict__ codes, uint32_t n, int passes, uint32_t flip,
                                                                       uint32_t* __restrict__ hist) {
   __shared__ uint32_t s_h[kSortMaxPasses * kDigits];
+  chain_release();
   for (int i = threadIdx.x; i < passes * kDigits; i += kSortThreads) s_h[i] = 0;
+  chain_wait();  // set-up above overlaps the tail of the kernel before; global memory only from here on
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const uint32_t per = (n + gridDim.x - 1) / gridDim.x;
@@ -87,8 +90,10 @@ __global__ void __launch_bounds__(kSortThreads)
   __shared__ uint32_t s_scan[kSortWarps];
   __shared__ uint32_t s_tile;
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
-  if (tid == 0) s_tile = atomicAdd(ticket, 1u);
+  chain_release();
   for (int i = tid; i < kSortWarps * kDigits; i += kSortThreads) (&s_cnt[0][0])[i] = 0;
+  chain_wait();  // the pass before (or the histogram) has completed; global memory only from here on
+  if (tid == 0) s_tile = atomicAdd(ticket, 1u);
   __syncthreads();
   const uint32_t tile = s_tile;
   const uint32_t base = tile * (kSortThreads * kItems) + w * (32 * kItems);
@@ -224,7 +229,7 @@ static SortLayout sort_layout(int64_t n) {
 }
 
 template <int kItems>
-static void launch_pass(int pass, int passes, const int32_t* codes, char* ws, const SortLayout& L, uint32_t n, uint32_t flip, int64_t* out,
+static cudaError_t launch_pass(int pass, int passes, const int32_t* codes, char* ws, const SortLayout& L, uint32_t n, uint32_t flip, int64_t* out,
                         int32_t* err, cudaStream_t s) {
   uint32_t* ka = reinterpret_cast<uint32_t*>(ws + L.keys_a);
   uint32_t* va = reinterpret_cast<uint32_t*>(ws + L.vals_a);
@@ -240,14 +245,16 @@ static void launch_pass(int pass, int passes, const int32_t* codes, char* ws, co
   uint32_t* vout = (pass & 1) ? vb : va;
   const int shift = pass * kDigitBits;
   const bool first = pass == 0, last = pass == passes - 1;
+  cudaError_t rc;
   if (first && last)
-    sort_pass_kernel<kItems, true, true><<<L.tiles, kSortThreads, 0, s>>>(codes, kin, vin, kout, vout, out, n, shift, flip, hist, ticket, status, err);
+    rc = launch_chained(sort_pass_kernel<kItems, true, true>, dim3(L.tiles), dim3(kSortThreads), 0, s, codes, kin, vin, kout, vout, out, n, shift, flip, hist, ticket, status, err);
   else if (first)
-    sort_pass_kernel<kItems, true, false><<<L.tiles, kSortThreads, 0, s>>>(codes, kin, vin, kout, vout, out, n, shift, flip, hist, ticket, status, err);
+    rc = launch_chained(sort_pass_kernel<kItems, true, false>, dim3(L.tiles), dim3(kSortThreads), 0, s, codes, kin, vin, kout, vout, out, n, shift, flip, hist, ticket, status, err);
   else if (last)
-    sort_pass_kernel<kItems, false, true><<<L.tiles, kSortThreads, 0, s>>>(codes, kin, vin, kout, vout, out, n, shift, flip, hist, ticket, status, err);
+    rc = launch_chained(sort_pass_kernel<kItems, false, true>, dim3(L.tiles), dim3(kSortThreads), 0, s, codes, kin, vin, kout, vout, out, n, shift, flip, hist, ticket, status, err);
   else
-    sort_pass_kernel<kItems, false, false><<<L.tiles, kSortThreads, 0, s>>>(codes, kin, vin, kout, vout, out, n, shift, flip, hist, ticket, status, err);
+    rc = launch_chained(sort_pass_kernel<kItems, false, false>, dim3(L.tiles), dim3(kSortThreads), 0, s, codes, kin, vin, kout, vout, out, n, shift, flip, hist, ticket, status, err);
+  return rc;
 }
 
 }  // namespace fgb
@@ -280,9 +287,11 @@ extern "C" int fgb_pp_sorted_idx(const int32_t* binary_code, int64_t n, int key_
   sort_histogram_kernel<<<hist_grid, kSortThreads, 0, s>>>(binary_code, static_cast<uint32_t>(n), passes, flip,
                                                           reinterpret_cast<uint32_t*>(ws + L.control));
   for (int pass = 0; pass < passes; ++pass) {
-    if (L.items == 16) launch_pass<16>(pass, passes, binary_code, ws, L, static_cast<uint32_t>(n), flip, sorted_idx, status, s);
-    else if (L.items == 8) launch_pass<8>(pass, passes, binary_code, ws, L, static_cast<uint32_t>(n), flip, sorted_idx, status, s);
-    else launch_pass<4>(pass, passes, binary_code, ws, L, static_cast<uint32_t>(n), flip, sorted_idx, status, s);
+    cudaError_t e;
+    if (L.items == 16) e = launch_pass<16>(pass, passes, binary_code, ws, L, static_cast<uint32_t>(n), flip, sorted_idx, status, s);
+    else if (L.items == 8) e = launch_pass<8>(pass, passes, binary_code, ws, L, static_cast<uint32_t>(n), flip, sorted_idx, status, s);
+    else e = launch_pass<4>(pass, passes, binary_code, ws, L, static_cast<uint32_t>(n), flip, sorted_idx, status, s);
+    if (e != cudaSuccess) return cuda_status(e);
   }
   return launch_status();
 }

@@ -32,7 +32,15 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
     return 0 if t is None or t.numel() == 0 else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(device) -> int:
+    # the raw handle of torch's current stream on `device`; the direct binding avoids building a Stream object per call
+    # (every wrapper here asks for it, a cache build a dozen times)
+    if _raw_stream is not None:
+        idx = device.index if isinstance(device, torch.device) else device
+        return _raw_stream(torch.cuda.current_device() if idx is None else idx)
     return torch.cuda.current_stream(device).cuda_stream
 
 
@@ -168,8 +176,8 @@ def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table:
         out["block_offsets"].data_ptr(), meta.data_ptr(),
         meta.data_ptr() + 4 * (V + 2), _stream(dev))
     _cabi.check(rc, "fgb_subm_build_neighbor_map")
-    # order check + column index, table clear, insert, hash lookup, column lookup, block scan, prefix
-    _count(7)
+    # order check + column index, table clear, insert, hash lookup, column lookup, block scan (with the prefix)
+    _count(6)
     return out
 
 
@@ -283,11 +291,16 @@ def fetch_meta_async(meta: torch.Tensor):
     key = (dev.index, int(meta.numel()))
     entry = _meta_host.get(key)
     if entry is None:
-        entry = _meta_host[key] = (torch.empty(meta.shape, dtype=meta.dtype, pin_memory=True), torch.cuda.Event())
-    host, event = entry
+        host = torch.empty(meta.shape, dtype=meta.dtype, pin_memory=True)
+        # the numpy view shares the pinned memory: scalar reads without building tensors
+        entry = _meta_host[key] = (host, torch.cuda.Event(), host.view(torch.int32).numpy().view("uint32"))
+    host, event, host_np = entry
     host.copy_(meta, non_blocking=True)
-    event.record(torch.cuda.current_stream(dev))
-    return host, event
+    if dev.index is None or dev.index == torch.cuda.current_device():
+        event.record()  # torch's current stream of the current device, without building a Stream object
+    else:
+        event.record(torch.cuda.current_stream(dev))
+    return host_np, event
 
 
 def raise_for_status(code: int) -> None:
