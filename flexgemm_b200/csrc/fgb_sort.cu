@@ -283,7 +283,9 @@ extern "C" int fgb_pp_sorted_idx(const int32_t* binary_code, int64_t n, int key_
   // histograms, tickets and the look-back words start at zero
   int rc = cuda_status(cudaMemsetAsync(ws + L.control, 0, L.total - L.control, s));
   if (rc != FGB_OK) return rc;
-  const unsigned hist_grid = static_cast<unsigned>(std::min<int64_t>(ceil_div(n, 4096), 148 * 8));
+  // keys per CTA of the histogram: 1024 up to 400 k keys, 2048 beyond (measured: 42 / 43.5 / 46.5 us for the whole sort at
+  // 164 k keys with 1024 / 2048 / 4096; 70.5 / 68.7 / 70.6 us at 660 k), at most eight CTAs per SM
+  const unsigned hist_grid = static_cast<unsigned>(std::min<int64_t>(ceil_div(n, n <= 400000 ? 1024 : 2048), 148 * 8));
   sort_histogram_kernel<<<hist_grid, kSortThreads, 0, s>>>(binary_code, static_cast<uint32_t>(n), passes, flip,
                                                           reinterpret_cast<uint32_t*>(ws + L.control));
   for (int pass = 0; pass < passes; ++pass) {
