@@ -19,6 +19,7 @@ _PROTOTYPES = {
     "fgb_version": (c_char_p, []),
     "fgb_error_string": (c_char_p, [c_int]),
     "fgb_selftest_device_tables": (c_int, []),
+    "fgb_fetch_words_async": (c_int, [_P, _P, c_int64, _P]),
     "fgb_microbench_pipeline": (c_int, [c_int, c_int, c_int, c_int, c_int, _P, c_int64, c_int, _P, c_int64, _P, _P, _P, _P]),
     "fgb_hash_table_bytes": (c_int64, [c_int64, c_int]),
     "fgb_map_num_blocks": (c_int64, [c_int64]),

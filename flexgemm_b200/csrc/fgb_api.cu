@@ -59,3 +59,13 @@ extern "C" int fgb_selftest_device_tables(void) {
   if (limit.raise_to(0, 3000, a) != 0 || applied != 4) return 8;  // the failed raise left the old limit in place
   return 0;
 }
+
+// Device-to-host copy of a few words on `stream` (the neighbour-cache build fetches its pair count and status this way);
+// host_dst should be pinned memory, else the copy is not asynchronous.  (A one-warp kernel storing the words into the
+// pinned buffer was measured against this call: no difference for the build.)
+extern "C" int fgb_fetch_words_async(void* host_dst, const void* device_src, int64_t bytes, void* stream) {
+  if (bytes < 0) return FGB_E_SIZE;
+  if (bytes == 0) return FGB_OK;
+  if (!host_dst || !device_src) return FGB_E_NULL;
+  return fgb::cuda_status(cudaMemcpyAsync(host_dst, device_src, static_cast<size_t>(bytes), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+}

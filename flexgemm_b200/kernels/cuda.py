@@ -144,6 +144,24 @@ _status_host: Dict[int, torch.Tensor] = {}
 # --------------------------------------------------------------------------
 # neighbour map and post-processing
 # --------------------------------------------------------------------------
+_zero_pool: Dict[tuple, list] = {}
+
+
+def _zeroed_words(device: torch.device, count: int) -> torch.Tensor:
+    """``count`` zeroed uint32 words that nothing else uses: a slice of a pool that is zeroed 4096 words at a time, so
+    that a cache build does not launch a fill kernel of its own (the slices stay alive with the tensors that view
+    them; a pool is dropped when it is used up)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, _stream(device))      # zeroed on the stream that uses it
+    entry = _zero_pool.get(key)
+    words = (count + 7) & ~7          # 32-byte slices
+    if entry is None or entry[1] + words > entry[0].numel():
+        entry = _zero_pool[key] = [torch.zeros(max(4096, words), dtype=torch.uint32, device=device), 0]
+    out = entry[0][entry[1]:entry[1] + count]
+    entry[1] += words
+    return out
+
+
 def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table: torch.Tensor, key_bits: int,
                             slots: int) -> Dict[str, torch.Tensor]:
     """Hash build + lookup.  Returns neighbor_map [N,V] uint32, gray_code and
@@ -158,7 +176,7 @@ def subm_build_neighbor_map(coords: torch.Tensor, shape, ksize, dilation, table:
     B, _, W, H, D = [int(s) for s in shape]
     V = int(ksize[0]) * int(ksize[1]) * int(ksize[2])
     nblk = _cabi.check_size(lib.fgb_map_num_blocks(n), "fgb_map_num_blocks")
-    meta = torch.zeros(V + 3, dtype=torch.uint32, device=dev)
+    meta = _zeroed_words(dev, V + 3)
     out = {
         "neighbor_map": torch.empty((n, V), dtype=torch.uint32, device=dev),
         "gray_code": torch.empty(n, dtype=torch.int32, device=dev),
@@ -295,7 +313,8 @@ def fetch_meta_async(meta: torch.Tensor):
         # the numpy view shares the pinned memory: scalar reads without building tensors
         entry = _meta_host[key] = (host, torch.cuda.Event(), host.view(torch.int32).numpy().view("uint32"))
     host, event, host_np = entry
-    host.copy_(meta, non_blocking=True)
+    _cabi.check(_cabi.lib().fgb_fetch_words_async(host.data_ptr(), meta.data_ptr(), meta.numel() * meta.element_size(), _stream(dev)),
+                "fgb_fetch_words_async")
     if dev.index is None or dev.index == torch.cuda.current_device():
         event.record()  # torch's current stream of the current device, without building a Stream object
     else:

@@ -58,6 +58,12 @@ const char* fgb_error_string(int code);
  * or the number of the failed expectation.  (No counterpart in the reference.) */
 int fgb_selftest_device_tables(void);
 
+/* cudaMemcpyAsync(host_dst, device_src, bytes, device-to-host) on `stream`: how
+ * a caller fetches valid_signal_seg[V] (the pair count) and its status word
+ * after fgb_subm_build_neighbor_map without leaving the stream.  host_dst
+ * should be pinned. */
+int fgb_fetch_words_async(void* host_dst, const void* device_src, int64_t bytes, void* stream);
+
 /* ------------------------------------------------------------------------
  * Hash table + neighbour map
  * --------------------------------------------------------------------- */
