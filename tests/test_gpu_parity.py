@@ -528,3 +528,24 @@ def test_cache_vs_reference_cuda_output(name, K):
     for block in (128, 32):
         assert np.array_equal(cache.valid_kernel_callback(block).cpu().numpy(), POST[f"{name}/valid_kernel_{block}"])
         assert np.array_equal(cache.valid_kernel_seg_callback(block).cpu().numpy(), POST[f"{name}/valid_kernel_seg_{block}"])
+
+
+def test_meta_word_helpers(K):
+    """The pooled zeroed words handed to a build are zero, disjoint and survive the pool's renewal; the word fetch brings
+    device words into pinned memory on the stream."""
+    from flexgemm_b200 import _cabi
+    seen = []
+    for _ in range(200):                       # more than one pool of 4096 words
+        w = K._zeroed_words(DEV, 30)
+        assert w.shape == (30,) and int(w.view(torch.int32).abs().sum().item()) == 0
+        seen.append(w)
+        w.view(torch.int32).fill_(7)           # a build overwrites its words; later slices must stay zero
+    ptrs = sorted(t.data_ptr() for t in seen)
+    assert all(b - a >= 120 for a, b in zip(ptrs, ptrs[1:]))
+    src = torch.arange(30, dtype=torch.int32, device=DEV)
+    dst = torch.zeros(30, dtype=torch.int32).pin_memory()
+    rc = _cabi.lib().fgb_fetch_words_async(dst.data_ptr(), src.data_ptr(), 120, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src.cpu())
+    assert _cabi.lib().fgb_fetch_words_async(0, src.data_ptr(), 8, 0) == -1
