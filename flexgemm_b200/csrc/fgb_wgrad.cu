@@ -184,6 +184,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) subm_wgrad_kernel(const WgradPa
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   WgradSmem* ctl = reinterpret_cast<WgradSmem*>(smem);
   uint8_t* stages = smem + 1024;
+  chain_release();  // the ordered sum that follows is launched chained: its CTAs plan their slabs while this kernel runs
   const int chunk_bytes = p.kb * 128;
   const int a_bytes = p.a_chunks * chunk_bytes;
   const int stage_bytes = (p.a_chunks + p.b_chunks) * chunk_bytes;
@@ -430,6 +431,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
                                                             int target_units, int Co, int V, int Ci, T* __restrict__ out,
                                                             float* __restrict__ out_f32, int accumulate) {
   __shared__ int s_unit_kb;
+  chain_release();
+  // the plan depends on the segment table only (written by the cache build): it is made while the wgrad kernel runs
   if (threadIdx.x < 32) {
     const uint32_t ukb = wg_plan_unit_kb(seg, V, kb, static_cast<uint32_t>(target_units), threadIdx.x);
     if (threadIdx.x == 0) s_unit_kb = static_cast<int>(ukb);
@@ -438,12 +441,26 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
   const int unit_kb = s_unit_kb;
   const int v = blockIdx.y;
   const int64_t e = (blockIdx.x * int64_t(256) + threadIdx.x) * 4;  // element of the [Co, Ci] slab
-  if (e >= int64_t(Co) * Ci) return;
   const uint32_t first = wg_slab_of(seg, kb, unit_kb, v, 0);
   const uint32_t count = wg_chunks_of(seg, v, kb, unit_kb);
+  chain_wait();  // the slabs are complete
+  if (e >= int64_t(Co) * Ci) return;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (uint32_t s = 0; s < count; ++s) {
-    const float4 t = __ldg(reinterpret_cast<const float4*>(partial + (size_t(first) + s) * Co * Ci + e));
+  const float* src = partial + size_t(first) * Co * Ci + e;
+  const size_t slab = size_t(Co) * Ci;
+  uint32_t s = 0;
+  for (; s + 4 <= count; s += 4) {  // four loads in flight, added in slab order
+    const float4 t0 = __ldg(reinterpret_cast<const float4*>(src + (s + 0) * slab));
+    const float4 t1 = __ldg(reinterpret_cast<const float4*>(src + (s + 1) * slab));
+    const float4 t2 = __ldg(reinterpret_cast<const float4*>(src + (s + 2) * slab));
+    const float4 t3 = __ldg(reinterpret_cast<const float4*>(src + (s + 3) * slab));
+    acc.x += t0.x, acc.y += t0.y, acc.z += t0.z, acc.w += t0.w;
+    acc.x += t1.x, acc.y += t1.y, acc.z += t1.z, acc.w += t1.w;
+    acc.x += t2.x, acc.y += t2.y, acc.z += t2.z, acc.w += t2.w;
+    acc.x += t3.x, acc.y += t3.y, acc.z += t3.z, acc.w += t3.w;
+  }
+  for (; s < count; ++s) {
+    const float4 t = __ldg(reinterpret_cast<const float4*>(src + s * slab));
     acc.x += t.x, acc.y += t.y, acc.z += t.z, acc.w += t.w;
   }
   const int co = static_cast<int>(e / Ci), ci = static_cast<int>(e % Ci);
@@ -724,15 +741,18 @@ static int wgrad_pass(const void* grad_out, const void* feats, const uint32_t* v
   const dim3 rgrid(static_cast<unsigned>(ceil_div(int64_t(Co) * Ci, 1024)), static_cast<unsigned>(V));
   switch (dtype) {
     case FGB_F16:
-      splitk_reduce_kernel<__half><<<rgrid, 256, 0, s>>>(slabs, seg, p.kb, p.target_units, Co, V, Ci, static_cast<__half*>(grad_weight), grad_weight_f32, 0);
+      rc = cuda_status(launch_chained(splitk_reduce_kernel<__half>, rgrid, dim3(256), 0, s, static_cast<const float*>(slabs), seg, p.kb,
+                                      p.target_units, Co, V, Ci, static_cast<__half*>(grad_weight), grad_weight_f32, 0));
       break;
     case FGB_BF16:
-      splitk_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, s>>>(slabs, seg, p.kb, p.target_units, Co, V, Ci, static_cast<__nv_bfloat16*>(grad_weight), grad_weight_f32, 0);
+      rc = cuda_status(launch_chained(splitk_reduce_kernel<__nv_bfloat16>, rgrid, dim3(256), 0, s, static_cast<const float*>(slabs), seg,
+                                      p.kb, p.target_units, Co, V, Ci, static_cast<__nv_bfloat16*>(grad_weight), grad_weight_f32, 0));
       break;
     default:
-      splitk_reduce_kernel<float><<<rgrid, 256, 0, s>>>(slabs, seg, p.kb, p.target_units, Co, V, Ci, static_cast<float*>(grad_weight), grad_weight_f32, accumulate);
+      rc = cuda_status(launch_chained(splitk_reduce_kernel<float>, rgrid, dim3(256), 0, s, static_cast<const float*>(slabs), seg, p.kb,
+                                      p.target_units, Co, V, Ci, static_cast<float*>(grad_weight), grad_weight_f32, accumulate));
   }
-  return launch_status();
+  return rc != FGB_OK ? rc : launch_status();
 }
 }  // namespace fgb
 
