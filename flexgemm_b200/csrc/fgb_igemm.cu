@@ -219,6 +219,9 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
   const int stage_bytes = 2 * kATileBytes + p.bn * 128;  // A half 0 | A half 1 | B
   const int S = p.stages;
 
+  // Launched chained (fgb_device.cuh): the CTA may be on its SM before the kernel ahead in the stream has finished.
+  chain_release();
+  chain_wait();
   // A kernel that already reported a soft error makes the rest of the grid a
   // no-op.  One thread reads the word so that the whole CTA takes the same branch.
   __shared__ int s_skip;
@@ -607,6 +610,7 @@ __global__ void __launch_bounds__(1024) block_schedule_kernel(const uint32_t* __
 template <typename T>
 __global__ void __launch_bounds__(256) weight_transpose_kernel(const T* __restrict__ src, T* __restrict__ dst, int Co, int V, int Ci) {
   __shared__ T tile[32][33];
+  chain_release();  // the conv kernel that reads dst is launched chained
   const int v = blockIdx.z;
   const int ci0 = blockIdx.x * 32, co0 = blockIdx.y * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -691,8 +695,8 @@ static int launch_igemm_variant(const CUtensorMap& tmap, const IgemmParams& p, c
   const int limit = g_cta_limit.load(std::memory_order_relaxed);
   if (limit > 0 && limit < ctas) ctas = limit;
   const unsigned grid = static_cast<unsigned>(work < ctas ? work : ctas);
-  subm_igemm_kernel<kDtype, kMode><<<grid, kIgemmThreads, smem, s>>>(tmap, p, fe);
-  return launch_status();
+  const cudaError_t e = launch_chained(subm_igemm_kernel<kDtype, kMode>, dim3(grid), dim3(kIgemmThreads), smem, s, tmap, p, fe);
+  return e != cudaSuccess ? cuda_status(e) : launch_status();
 }
 
 // the plain kernel carries no trace of the fused epilogue (its register allocation is the tuned one)
@@ -754,7 +758,8 @@ __global__ void __launch_bounds__(256) splitk_rows_reduce_kernel(const float* __
 // x [n, kc] gathered through nbr; w [nout, V, kc]; out [n, nout]
 int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nbr, const int64_t* sorted_idx,
               const uint32_t* tile_masks, const uint32_t* block_order, uint32_t* ticket, void* out, int64_t n, int kc, int nout, int V, int dtype, int flip, int32_t* status,
-              cudaStream_t s, float* partial = nullptr, int act = FGB_ACT_NONE, const void* residual = nullptr, void* preact = nullptr) {
+              cudaStream_t s, float* partial = nullptr, int act = FGB_ACT_NONE, const void* residual = nullptr, void* preact = nullptr,
+              bool ticket_zeroed = false) {
   const int eb = elem_bytes(dtype);
   if (eb == 0 || dtype == FGB_F32_IEEE) return FGB_E_DTYPE;  // callers expand fp32-accurate mode to TF32 operands
   if (n < 0 || n >= (int64_t(1) << 32) - 1 || kc <= 0 || nout <= 0 || V < 1 || V > 32) return FGB_E_SIZE;
@@ -802,7 +807,9 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   p.idesc = make_idesc(fmt, kTileM, p.bn, 0, 0);
   p.status = status;
   if (!ticket) return FGB_E_NULL;
-  int rc = cuda_status(cudaMemsetAsync(ticket, 0, sizeof(uint32_t), s));
+  // the work counter starts at zero; a caller that launches kernels of its own right before this one zeroes it ahead of
+  // them, so that the conv kernel follows a kernel in the stream and its chained launch takes effect
+  int rc = ticket_zeroed ? FGB_OK : cuda_status(cudaMemsetAsync(ticket, 0, sizeof(uint32_t), s));
   if (rc != FGB_OK) return rc;
   CUtensorMap tmap;
   rc = make_weight_tmap(&tmap, w, nout, V, kc, p.bn, dtype);
@@ -952,6 +959,10 @@ static int dgrad_impl(const void* grad_out, const void* weight, const uint32_t* 
   uint32_t* ticket = static_cast<uint32_t*>(workspace);
   char* wt = static_cast<char*>(workspace) + kWsHeader;
   dim3 grid(static_cast<unsigned>(ceil_div(Ci, 32)), static_cast<unsigned>(ceil_div(Co, 32)), V);
+  {
+    const cudaError_t e = cudaMemsetAsync(ticket, 0, sizeof(uint32_t), s);  // ahead of the re-layout: see run_igemm
+    if (e != cudaSuccess) return cuda_status(e);
+  }
   if (eb == 2)
     weight_transpose_kernel<uint16_t><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(weight), reinterpret_cast<uint16_t*>(wt), Co, V, Ci);
   else
@@ -960,7 +971,7 @@ static int dgrad_impl(const void* grad_out, const void* weight, const uint32_t* 
   if (rc != FGB_OK) return rc;
   if (!ieee)
     return run_igemm(grad_out, wt, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, ticket, grad_feats, n, Co, Ci, V, dtype,
-                     mirror, status, s, part);
+                     mirror, status, s, part, FGB_ACT_NONE, nullptr, nullptr, true);
   if (!grad_out) return FGB_E_NULL;
   float* w3 = reinterpret_cast<float*>(wt + wt_bytes);
   float* g3 = reinterpret_cast<float*>(wt + wt_bytes + w3_bytes);
@@ -969,7 +980,7 @@ static int dgrad_impl(const void* grad_out, const void* weight, const uint32_t* 
   if (n_src > 0) rc = launch_split3(static_cast<const float*>(grad_out), g3, n_src, Co, kSplitActivations, s);
   if (rc != FGB_OK) return rc;
   return run_igemm(g3, w3, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, ticket, grad_feats, n, 3 * Co, Ci, V, FGB_F32_TF32,
-                   mirror, status, s, part);
+                   mirror, status, s, part, FGB_ACT_NONE, nullptr, nullptr, true);
 }
 
 }  // namespace fgb
