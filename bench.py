@@ -275,7 +275,8 @@ def time_map_build(coords, shape, iters: int, warmup: int = 3):
     cache = None
     for _ in range(warmup):
         cache = build()
-    return time_loop(build, iters), cache
+    # the host is part of a build (one round trip): the median of three regions keeps a host stall out of the figure
+    return statistics.median(time_loop(build, iters) for _ in range(3)), cache
 
 
 def map_build_report(coords_sorted, shape, peaks, iters: int):
