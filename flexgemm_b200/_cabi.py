@@ -34,6 +34,7 @@ _PROTOTYPES = {
     "fgb_conv_block_schedule": (c_int, [_P, c_int64, _P, _P]),
     "fgb_conv_set_cta_limit": (c_int, [c_int]),
     "fgb_conv_set_splitk": (c_int, [c_int]),
+    "fgb_conv_set_dgrad_relayout": (c_int, [c_int]),
     "fgb_subm_conv_fprop": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P]),
     "fgb_subm_conv_fprop_fused": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int, _P, c_int64,
                                           _P, _P]),

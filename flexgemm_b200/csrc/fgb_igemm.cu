@@ -81,7 +81,7 @@ struct IgemmParams {
   int items_per_block;       // n_tiles_n * splits
   int row_bytes;             // kc * element size
   int num_kb;                // 128-byte slices per row
-  int flip;                  // weight slot = flip ? V-1-v : v
+  int flip;                  // bit 0: weight slot = V-1-v instead of v; bit 1: the weight operand is MN-major (below)
   int stages;
   int acc_sets;              // accumulator pairs that fit in TMEM (1 or 2)
   uint32_t idesc;
@@ -427,11 +427,18 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
         while (un) {
           const int v = __ffs(un) - 1;
           un &= un - 1;
-          const int wv = p.flip ? V - 1 - v : v;
+          const int wv = (p.flip & 1) ? V - 1 - v : v;
           for (int kb = 0; kb < p.num_kb; ++kb) {
             mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag);
             mbar_arrive_expect_tx(&ctl->full[s], static_cast<uint32_t>(p.bn) * 128u);
-            tma_load_3d(smem_u32(stages + size_t(s) * stage_bytes + 2 * kATileBytes), &tmap_w, &ctl->full[s], kb * (128 / kElem), wv, n0);
+            const uint32_t b_dst = smem_u32(stages + size_t(s) * stage_bytes + 2 * kATileBytes);
+            if (p.flip & 2) {
+              // MN-major weights (dgrad of 16-bit types reads the weight as stored, [Co][V][Ci]): rows of the stage are
+              // reduction channels, 128 bytes = 64 output channels per row, one 8 KB chunk per 64 output channels
+              for (int c = 0; c < p.bn / 64; ++c) tma_load_3d(b_dst + c * 8192, &tmap_w, &ctl->full[s], n0 + c * 64, wv, kb * 64);
+            } else {
+              tma_load_3d(b_dst, &tmap_w, &ctl->full[s], kb * (128 / kElem), wv, n0);
+            }
             if (++s == static_cast<uint32_t>(S)) s = 0, ph ^= 1;
           }
         }
@@ -464,16 +471,19 @@ __global__ void __launch_bounds__(kIgemmThreads, 1)
             const uint32_t a_addr = smem_u32(stages + size_t(s) * stage_bytes);
             const uint64_t da0 = make_smem_desc(a_addr, 16, 1024);
             const uint64_t da1 = make_smem_desc(a_addr + kATileBytes, 16, 1024);
-            const uint64_t db = make_smem_desc(a_addr + 2 * kATileBytes, 16, 1024);
+            // K-major weights: a k-step is 32 bytes along the row; MN-major: 16 rows of 128 bytes, chunks 8 KB apart
+            const bool b_mn = (p.flip & 2) != 0;
+            const uint64_t db = make_smem_desc(a_addr + 2 * kATileBytes, b_mn ? 8192 : 16, 1024);
+            const uint32_t b_step = b_mn ? 128u : 2u;
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4) {
               if (kb * 128 + k4 * 32 < p.row_bytes) {
                 if (need0) {
-                  umma_ss<kTF32>(acc_tmem, da0 + uint64_t(k4 * 2), db + uint64_t(k4 * 2), p.idesc, acc0);
+                  umma_ss<kTF32>(acc_tmem, da0 + uint64_t(k4 * 2), db + uint64_t(k4 * b_step), p.idesc, acc0);
                   acc0 = 1;
                 }
                 if (need1) {
-                  umma_ss<kTF32>(acc_tmem + p.bn, da1 + uint64_t(k4 * 2), db + uint64_t(k4 * 2), p.idesc, acc1);
+                  umma_ss<kTF32>(acc_tmem + p.bn, da1 + uint64_t(k4 * 2), db + uint64_t(k4 * b_step), p.idesc, acc1);
                   acc1 = 1;
                 }
               }
@@ -658,6 +668,21 @@ int make_weight_tmap(CUtensorMap* map, const void* w, int nout, int V, int kc, i
   return r == CUDA_SUCCESS ? FGB_OK : FGB_E_DRIVER;
 }
 
+// 3-D map over the weight as stored, w[Co][V][Ci] of 16-bit elements, for dgrad: box = 64 input channels (128 bytes) x 1
+// offset x 64 output channels -- one MN-major chunk of a stage (rows = reduction channels), 128B swizzle
+int make_weight_tmap_mn(CUtensorMap* map, const void* w, int Co, int V, int Ci, int dtype) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return FGB_E_DRIVER;
+  const CUtensorMapDataType dt = dtype == FGB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  cuuint64_t dims[3] = {cuuint64_t(Ci), cuuint64_t(V), cuuint64_t(Co)};
+  cuuint64_t strides[2] = {cuuint64_t(Ci) * 2, cuuint64_t(V) * Ci * 2};
+  cuuint32_t box[3] = {64u, 1u, 64u};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dt, 3, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FGB_OK : FGB_E_DRIVER;
+}
+
 // 2-D map over rows[n_rows][row_elems] of 16-bit elements; box = 128 bytes of one row, 128B swizzle (the box TMA
 // tile::gather4 wants: it takes four row coordinates per instruction)
 int make_rows_tmap(CUtensorMap* map, const void* rows, int64_t n_rows, int row_elems) {
@@ -713,6 +738,7 @@ static int launch_igemm(const CUtensorMap& tmap, const IgemmParams& p, const Fus
 // run as separate work items into fp32 slabs, and a second kernel adds the slabs in a fixed order, adds the bias and
 // converts.  (The reference splits the same way when tiles * SPLITK < number of SMs:
 // sparse_submanifold_conv_fwd_masked_implicit_gemm_splitk.py:109-121.)
+static std::atomic<int> g_dgrad_relayout{0};  // 1 = dgrad always works on the re-laid-out copy of the weight (measurement / test knob)
 static std::atomic<int> g_force_splits{0};  // 0 = by the rule below, 1 = never split, k = k shares (capped at V)
 
 int igemm_splits(int64_t n, int nout, int V) {
@@ -804,7 +830,8 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   if (p.stages > kMaxStages) p.stages = kMaxStages;
   p.acc_sets = 2 * p.bn * 2 <= 512 ? 2 : 1;
   const uint32_t fmt = dtype == FGB_F16 ? kFmtF16 : dtype == FGB_BF16 ? kFmtBF16 : kFmtTF32;
-  p.idesc = make_idesc(fmt, kTileM, p.bn, 0, 0);
+  const bool b_mn = (flip & 2) != 0;  // the weight operand as stored for the other direction: w [kc, V, nout]
+  p.idesc = make_idesc(fmt, kTileM, p.bn, 0, b_mn ? 1 : 0);
   p.status = status;
   if (!ticket) return FGB_E_NULL;
   // the work counter starts at zero; a caller that launches kernels of its own right before this one zeroes it ahead of
@@ -812,7 +839,7 @@ int run_igemm(const void* x, const void* w, const void* bias, const uint32_t* nb
   int rc = ticket_zeroed ? FGB_OK : cuda_status(cudaMemsetAsync(ticket, 0, sizeof(uint32_t), s));
   if (rc != FGB_OK) return rc;
   CUtensorMap tmap;
-  rc = make_weight_tmap(&tmap, w, nout, V, kc, p.bn, dtype);
+  rc = b_mn ? make_weight_tmap_mn(&tmap, w, kc, V, nout, dtype) : make_weight_tmap(&tmap, w, nout, V, kc, p.bn, dtype);
   if (rc != FGB_OK) return rc;
   switch (dtype) {
     case FGB_F16:
@@ -853,6 +880,11 @@ extern "C" int fgb_conv_set_cta_limit(int max_ctas) {
 extern "C" int fgb_conv_set_splitk(int splits) {
   if (splits < 0 || splits > 32) return FGB_E_SIZE;
   return fgb::g_force_splits.exchange(splits, std::memory_order_relaxed);
+}
+
+extern "C" int fgb_conv_set_dgrad_relayout(int on) {
+  if (on != 0 && on != 1) return FGB_E_SIZE;
+  return fgb::g_dgrad_relayout.exchange(on, std::memory_order_relaxed);
 }
 
 extern "C" int fgb_conv_block_schedule(const uint32_t* tile_masks, int64_t num_tiles, uint32_t* block_order, void* stream) {
@@ -958,6 +990,12 @@ static int dgrad_impl(const void* grad_out, const void* weight, const uint32_t* 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint32_t* ticket = static_cast<uint32_t*>(workspace);
   char* wt = static_cast<char*>(workspace) + kWsHeader;
+  // 16-bit types read the weight as it is stored, [Co][V][Ci], as an MN-major operand (rows = reduction channels): no
+  // re-layout pass.  Column tiles narrower than one 64-channel chunk, and the 32-bit types (whose MN-major layout TMA
+  // does not produce), go through the re-laid-out copy.
+  if (eb == 2 && !g_dgrad_relayout.load(std::memory_order_relaxed) && pick_bn(Ci) % 64 == 0)
+    return run_igemm(grad_out, weight, nullptr, neighbor_map, sorted_idx, tile_masks, block_order, ticket, grad_feats, n, Co, Ci, V, dtype,
+                     mirror | 2, status, s, part);
   dim3 grid(static_cast<unsigned>(ceil_div(Ci, 32)), static_cast<unsigned>(ceil_div(Co, 32)), V);
   {
     const cudaError_t e = cudaMemsetAsync(ticket, 0, sizeof(uint32_t), s);  // ahead of the re-layout: see run_igemm

@@ -449,6 +449,15 @@ def microbench_pipeline(mode: int, rows: torch.Tensor, dense: torch.Tensor, iter
     return float(ms.value), [int(c) for c in counters]
 
 
+def set_conv_dgrad_relayout(on: bool) -> bool:
+    """Force dgrad onto the re-laid-out copy of the weight (the path of the 32-bit types) for every type; returns the
+    previous setting.  The default reads 16-bit weights as stored."""
+    prev = _cabi.lib().fgb_conv_set_dgrad_relayout(1 if on else 0)
+    if prev < 0:
+        _cabi.check(prev, "fgb_conv_set_dgrad_relayout")
+    return bool(prev)
+
+
 def set_conv_cta_limit(max_ctas: int) -> int:
     """Cap the CTAs (SMs) of the persistent fprop / dgrad kernels launched from now
     on (0 = no cap); returns the previous cap."""

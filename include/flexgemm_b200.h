@@ -200,6 +200,13 @@ int fgb_conv_set_cta_limit(int max_ctas);
  * (sparse_submanifold_conv_fwd_masked_implicit_gemm_splitk.py:109-121). */
 int fgb_conv_set_splitk(int splits);
 
+/* dgrad of 16-bit types reads the weight as it is stored ([Co][V][Ci]) as an
+ * MN-major tensor-core operand; 32-bit types and column tiles under 64 channels
+ * work on a re-laid-out copy ([Ci][V][Co]) made by a kernel of the call.  on = 1
+ * forces the copy for every type (0 = default); returns the previous setting.
+ * The results are the same bit for bit.  Process-wide; read at launch. */
+int fgb_conv_set_dgrad_relayout(int on);
+
 /* block_order (uint32 [ceil(num_tiles / 2)]) = the 256-row blocks (pairs of
  * consecutive 128-row tiles) in descending order of work, computed from the tile
  * masks.  The persistent conv kernels deal blocks to the SMs from this list so

@@ -353,3 +353,41 @@ def test_reference_first_forward_case_res8_c1024_batch256():
     sub = torch.from_numpy(nbr[rows_np].astype(np.int64))
     ref = torch.einsum("rvc,ovc->ro", gathered(feats, sub, n), weight.double().reshape(c, 27, c)) + bias.double()
     assert rel_err(out[torch.from_numpy(rows_np).to(DEV)], ref) <= 1e-2
+
+
+@pytest.mark.parametrize("dtype,C", [(torch.float16, 256), (torch.bfloat16, 192), (torch.float16, 64), (torch.float16, 1024)])
+def test_dgrad_reads_the_weight_as_stored(dtype, C):
+    """dgrad of 16-bit types multiplies by the weight as stored (an MN-major operand); forcing the re-laid-out copy must
+    give the same bits, and both must match the oracle."""
+    from flexgemm_b200.kernels import cuda as K
+    from flexgemm_b200.ops.spconv import SubMConv3dFunction as F
+    coords = torch.from_numpy(orc.shell_coords(40)).to(DEV)
+    n = coords.shape[0]
+    shape = torch.Size((1, C, 40, 40, 40))
+    g = torch.Generator(device="cpu").manual_seed(9)
+    gout = torch.randn(n, C, generator=g).to(dtype).to(DEV)
+    w = (torch.randn(C, 27, C, generator=g) / (27 * C) ** 0.5).to(dtype).to(DEV)
+    cache = F._compute_neighbor_cache(coords, shape, (3, 3, 3), (1, 1, 1), True)
+    tile = K.conv_tile_rows()
+    args = (gout, w, cache["neighbor_map"], cache["sorted_idx"], cache.tile_masks(tile), cache.block_order(tile))
+    prev = K.set_conv_dgrad_relayout(False)
+    try:
+        direct = K.conv_dgrad(*args)
+        K.set_conv_dgrad_relayout(True)
+        relaid = K.conv_dgrad(*args)
+    finally:
+        K.set_conv_dgrad_relayout(prev)
+    K.check_status(DEV)
+    assert torch.equal(direct.view(torch.int16), relaid.view(torch.int16))
+    nbr = cache["neighbor_map"].cpu().view(torch.int32).numpy().view(np.uint32)
+    rows = np.random.default_rng(3).choice(n, size=300, replace=False)
+    wf = w.float().cpu().numpy().astype(np.float64)
+    gf = gout.float().cpu().numpy().astype(np.float64)
+    ref = np.zeros((rows.size, C))
+    for k, r in enumerate(rows):
+        for v in range(27):
+            j = nbr[r, 26 - v]          # the row whose offset v is r
+            if j != 0xFFFFFFFF:
+                ref[k] += gf[j] @ wf[:, v, :]
+    got = direct.float().cpu().numpy()[rows]
+    assert np.abs(got - ref).max() <= 2e-2 * max(np.abs(ref).max(), 1e-6)
