@@ -326,7 +326,7 @@ def sweep_report(dev, peaks, iters: int = 8):
 
             for _ in range(3):
                 step()
-            ms = time_loop(step, iters)
+            ms = statistics.median(time_loop(step, iters) for _ in range(3))
             tf = 6.0 * pairs * c * c / (ms * 1e-3) / 1e12
             eb = feats.element_size()
             gathered = 4.0 * pairs * c * eb            # fprop + dgrad one gathered operand each, wgrad two
@@ -380,6 +380,8 @@ def residual_stack_steps(dev, fused: bool, steps: int, warmup: int = 3):
     launches0 = K.launch_count
     ms = time_loop(step, steps)
     launches = K.launch_count - launches0
+    # the median of three regions: a stall of the host (it launches ~100 kernels per step) would otherwise own the figure
+    ms = statistics.median([ms, time_loop(step, steps), time_loop(step, steps)])
     K.check_status(dev)
     flops = 2 * blocks * 6.0 * pairs * C * C
     return {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "flops_per_step": flops, "n_voxels": int(coords.shape[0]), "pairs": pairs,
